@@ -1,0 +1,260 @@
+"""Benchmark of the EXL3 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (`config.workload`): the dense 27B-shape decode layer set at K = 3 bpw, 3INST codebook, batch 1 --
+64 layers x (q|k|v 5120->7168, o 5120->5120, gate|up 5120->34816, down 17408->5120) = 7.93 GB of packed
+trellis, uniform-random bits, random +-1 suh/svh, fp16 N(0,1) activations.  One step = every linear of the stack
+once (the linear work of one decoded token).  The weights are distinct per layer and far larger than L2, so no
+L2 flush is needed between steps.
+
+Printed metric: achieved HBM GB/s on packed-weight bytes, whole job (all ranks), plus tokens/s.  With N > 1 the
+stack is tensor-parallel (column-parallel q/k/v/gate/up, row-parallel o/down with an all-reduce), total work
+fixed: "strong" scaling.
+
+`--impl reference` times the CPU implementation of the same path (the oracle port of the reference decoder,
+multi-threaded C) on a bounded sample: the seven matrices of one layer.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "exl3_gemv_hbm_gbs_packed_bytes_batch1_27b_k3"
+UNIT = "GB/s"
+WORKLOAD = "27B-shape decode layer set, K=3 3INST, batch 1, 64 layers x (qkv, o, gate_up, down), inputs > L2 (no flush)"
+
+
+def measured_peak_hbm() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(K: int, codebook: int, min_seconds: float = 8.0, max_reps: int = 4, threads: int | None = None) -> dict:
+    """Oracle forward (decode + multiply fused, OpenMP) on the seven matrices of one 27B-shape layer, batch 1."""
+    import numpy as np
+    from oracle import exl3_oracle as orc
+    if threads:
+        orc.set_threads(threads)
+    shapes = [(5120, 5120), (5120, 1024), (5120, 1024), (5120, 5120), (5120, 17408), (5120, 17408), (17408, 5120)]
+    rng = np.random.default_rng(100)
+    mats = []
+    for k, n in shapes:
+        tr = rng.integers(0, 65536, size=(k // 16, n // 16, 16 * K), dtype=np.uint16)
+        suh = (rng.integers(0, 2, size=k) * 2 - 1).astype(np.float16)
+        svh = (rng.integers(0, 2, size=n) * 2 - 1).astype(np.float16)
+        x = rng.standard_normal((1, k)).astype(np.float16)
+        mats.append((x, tr, suh, svh))
+    nbytes = sum(k * n * K // 8 for k, n in shapes)
+    orc.c_linear_forward(*mats[1], K, codebook)                      # warm the thread pool
+    times = []
+    t_all = time.perf_counter()
+    while len(times) < max_reps and (time.perf_counter() - t_all < min_seconds or not times):
+        t0 = time.perf_counter()
+        for m in mats:
+            orc.c_linear_forward(*m, K, codebook)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+            "sample": f"one 27B-shape layer (7 matrices, {nbytes / 1e6:.2f} MB packed, K={K}, batch 1), best of {len(times)} passes, "
+                      f"{best:.3f} s per pass; multi-threaded C port of the reference decoder (the reference itself is Python)",
+            "seconds_per_layer": best, "tok_s": 1.0 / (best * 64)}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    K, cb = args.bits, 0
+    runs = []
+    for _ in range(args.warmup):
+        cpu_sample(K, cb, min_seconds=0.0, max_reps=1)
+    for _ in range(args.steps):
+        runs.append(cpu_sample(K, cb, min_seconds=0.0, max_reps=1))
+    best = max(runs, key=lambda r: r["value"])
+    ms = best["seconds_per_layer"] * 1e3
+    line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": "one layer of the 64 per step"},
+            "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "tok_s": best["tok_s"], "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--bits", type=int, default=3)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    from trellis_serve_b200.kernels import linear as lin
+    from trellis_serve_b200.runtime.layerset import DecodeLayerSet
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the EXL3 kernels have no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    K, cb = args.bits, 0
+    ls = DecodeLayerSet(args.layers, K, cb, args.rows, tp_rank=rank, tp_size=world, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7 + rank)
+    for buf in (ls.x_hidden, ls.x_attn, ls.x_ffn):
+        buf.copy_(torch.randn(buf.shape, device=dev, generator=gen).to(buf.dtype))
+    ls.capture(warmup=2)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing: inputs already in HBM, K replays of the captured step
+    for _ in range(args.warmup):
+        ls.replay()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            ls.replay()
+        stop.record()
+        barrier()
+    ms_total = start.elapsed_time(stop)
+    lin.device_error(dev)
+
+    # ---- end to end: pinned host inputs -> device, step, result -> host, every step
+    hx = [torch.randn(b.shape).to(b.dtype).pin_memory() for b in (ls.x_hidden, ls.x_attn, ls.x_ffn)]
+    hy = torch.empty(ls.y_down.shape, dtype=ls.y_down.dtype).pin_memory()
+    for _ in range(args.warmup):
+        ls.forward_host(*hx, hy)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ls.forward_host(*hx, hy)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    nbytes = torch.tensor([float(ls.packed_bytes)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)
+    ms_total, ms_e2e = t.tolist()
+    total_bytes = nbytes.item()
+    if rank == 0:
+        ms_step = ms_total / args.steps
+        value = total_bytes / (ms_step * 1e-3) / 1e9
+        e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+        peak, peak_kind = measured_peak_hbm()
+        gemv_launches = args.layers * 4
+        per_rank_bytes = ls.packed_bytes
+        # Roofline of the dominant kernel (the decode GEMV): algorithmic bytes = packed-weight bytes of a launch.
+        # Its average duration is bounded from above by the whole step time divided by the number of GEMV launches
+        # (the step also contains the small activation-rotation kernels), so `achieved` is a lower bound.
+        avg_launch_ms = ms_step / gemv_launches
+        achieved = per_rank_bytes / gemv_launches / (avg_launch_ms * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic",
+                "config": {"workload": WORKLOAD, "layers": args.layers, "bits": K, "codebook": "3inst", "rows": args.rows,
+                           "parallelism": f"tp{world}", "l2": "inputs larger than L2, no flush",
+                           "packed_bytes_per_step": total_bytes},
+                "tok_s": 1e3 / ms_step,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "gemv_kernel",
+                             "launches_per_step": gemv_launches, "avg_launch_ms_upper_bound": avg_launch_ms},
+                "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                        "h2d_bytes_per_step": sum(h.numel() * h.element_size() for h in hx),
+                        "d2h_bytes_per_step": hy.numel() * hy.element_size(), "tok_s": 1e3 / (ms_e2e / args.steps)},
+                "gpu_launches": ls.launches_per_step * args.steps,
+                "clocks": clocks.summary()}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = {k: v for k, v in cpu_sample(K, cb).items() if k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,114 @@
+/*
+ * exl3_b200 -- C ABI of the B200 (sm_100a) EXL3 quantized-linear kernels.
+ *
+ * This is the boundary a host plugin binds (ctypes, cffi, pybind, cgo ...).  It replaces the pybind/ATen
+ * modules of 0xSero/trellis-serve, `trellis_exl3_kernels` (cuda/csrc/exl3_marlin.cu:562-585) and
+ * `trellis_exl3_moe_kernels` (cuda/csrc/exl3_marlin_moe.cu:620-646).  Conventions:
+ *
+ *   - every pointer is a DEVICE pointer owned by the caller unless a comment says "host";
+ *   - nothing here allocates device memory; scratch comes in through `workspace`;
+ *   - every function returns a status (0 = ok); shape or argument errors are reported before any launch;
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it;
+ *   - tensors are contiguous; fp16 / bf16 are passed as raw 16-bit storage;
+ *   - rows == 0 is a no-op that returns EXL3_OK (cuda/csrc/exl3_marlin.cu:499);
+ *   - one host thread per device at a time (the reference's model: cuda/csrc/exl3_marlin.cu:84-100).
+ *
+ * EXL3 linear:  y = Had128( Had128(x * suh) @ W_inner ) * svh, W_inner decoded from the trellis
+ * (core/src/trellis_core/reference.py:1-17, :145-153).
+ */
+#ifndef EXL3_B200_H
+#define EXL3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int exl3_status;
+
+enum {
+    EXL3_OK = 0,
+    EXL3_ERR_BAD_SHAPE = 1,          /* k or n not a multiple of 128, negative sizes, shard ends out of order */
+    EXL3_ERR_UNSUPPORTED_K = 2,      /* bits per weight outside 2..8 */
+    EXL3_ERR_UNSUPPORTED_CODEBOOK = 3,
+    EXL3_ERR_BAD_POINTER = 4,        /* null or misaligned pointer */
+    EXL3_ERR_WORKSPACE = 5,          /* workspace missing or smaller than exl3_linear_workspace_bytes() */
+    EXL3_ERR_CUDA = 6,               /* a CUDA runtime call failed; exl3_last_cuda_error() has the code */
+    EXL3_ERR_DEVICE_WAIT = 7,        /* a bounded device-side wait gave up (reported by exl3_device_error) */
+    EXL3_ERR_NOT_INITIALISED = 8,    /* exl3_init_device() was not called for the current device */
+    EXL3_ERR_UNSUPPORTED_ROWS = 9,
+    EXL3_ERR_UNSUPPORTED_DTYPE = 10
+};
+
+enum { EXL3_CB_3INST = 0, EXL3_CB_MCG = 1, EXL3_CB_MUL1 = 2 };      /* core/src/trellis_core/reference.py:27 */
+enum { EXL3_F16 = 0, EXL3_BF16 = 1, EXL3_F32 = 2 };
+
+const char *exl3_status_str(exl3_status status);
+int exl3_last_cuda_error(void);
+int exl3_version(void);
+
+/* Per-device state (SM count, kernel attributes).  Call once per device before any other entry point and
+ * before any CUDA-graph capture.  Replaces init_device (cuda/csrc/exl3_marlin.cu:99-112, :537). */
+exl3_status exl3_init_device(int device);
+
+/* ---- resident layout ------------------------------------------------------------------------------------
+ * Stored trellis: int16 [k/16, n/16, 16K].  Resident layout: uint32, same number of bytes, a permutation of
+ * the stored bits.  Replaces repack_trellis / unpack_trellis (cuda/csrc/exl3_marlin.cu:344-408). */
+size_t exl3_packed_bytes(int k, int n, int K);
+exl3_status exl3_repack(const uint16_t *trellis, int k, int n, int K, uint32_t *packed, void *stream);
+exl3_status exl3_unpack(const uint32_t *packed, int k, int n, int K, uint16_t *trellis, void *stream);
+
+/* ---- decode to dense ------------------------------------------------------------------------------------
+ * fp16 W_inner [k, n] row-major, bit-identical to reconstruct_inner (core/src/trellis_core/reference.py:102-115).
+ * Stands in for exllamav3_ext.reconstruct (cuda/src/sglang_exl3/kernels/reference.py:71-80).
+ * The stored form accepts any tile counts (k, n multiples of 16); the resident form needs multiples of 128. */
+exl3_status exl3_reconstruct(const uint16_t *trellis, int k, int n, int K, int codebook, uint16_t *w_f16, void *stream);
+exl3_status exl3_reconstruct_packed(const uint32_t *packed, int k, int n, int K, int codebook, uint16_t *w_f16,
+                                    void *stream);
+
+/* ---- Hadamard rotations ---------------------------------------------------------------------------------
+ * xh[s*rows + r, :] = Had128(fp16(x[r, :]) * suh[s, :]), fp16, for every shard s.  suh may be NULL (no scale).
+ * Replaces had_in_group_marlin (cuda/csrc/exl3_marlin.cu:283-290). */
+exl3_status exl3_had_in(const void *x, int x_dtype, const uint16_t *suh, int shards, int rows, int k, uint16_t *xh,
+                        void *stream);
+/* out[r, j] = Had128(y[r, :])[j] * svh[j] for j < n, written with row stride out_stride (elements) so a fused
+ * group can fill adjacent column spans.  y_dtype EXL3_F16 or EXL3_F32; out_dtype EXL3_F16 or EXL3_BF16.
+ * Replaces had_out_into_marlin (cuda/csrc/exl3_marlin.cu:292-306). */
+exl3_status exl3_had_out(const void *y, int y_dtype, const uint16_t *svh, int rows, int n, void *out, int64_t out_stride,
+                         int out_dtype, void *stream);
+
+/* ---- fused linear (decode path, any row count; rows are processed 16 at a time) -------------------------
+ * One fused group: `n_shards` matrices that share the input x [rows, k] and write adjacent column spans of
+ * y [rows, n_total].  packed = the matrices' resident layouts concatenated along n; suh_cat [n_shards, k];
+ * svh_cat [n_total]; shard_ends (host, n_shards - 1 ints) = column where each matrix but the last ends,
+ * multiples of 128.  x_dtype: EXL3_F16 or EXL3_BF16; y_dtype: EXL3_F16, EXL3_BF16 (the fp16 result converted) or
+ * EXL3_F32 (the fp32 accumulators unrounded, for accuracy measurements).  y must be 16-byte aligned.
+ * Replaces exl3_linear_marlin_out / exl3_linear_marlin_multi_out (cuda/csrc/exl3_marlin.cu:489-527).
+ * The workspace must be zero-filled once after allocation; every call leaves it reusable. */
+size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards);
+exl3_status exl3_linear(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
+                        const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
+                        int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Rotated-basis product without the Hadamards: out[r, :] = xh[s(col)*rows + r, :] @ W_inner, fp16 out.
+ * Identity rows of xh read the decoded weights out exactly.  Replaces exl3_gemm_marlin / exl3_gemm_marlin_multi
+ * (cuda/csrc/exl3_marlin.cu:410-487). */
+exl3_status exl3_gemm_rotated(const uint16_t *xh, const uint32_t *packed, int K, int codebook, const int *shard_ends,
+                              int n_shards, int rows, int k, int n_total, uint16_t *out, void *workspace,
+                              size_t workspace_bytes, void *stream);
+
+/* Reads and clears the device-side error word kept in a workspace (set when a bounded wait in a kernel gave up).
+ * Synchronises `stream`.  Returns EXL3_OK or EXL3_ERR_DEVICE_WAIT. */
+exl3_status exl3_device_error(void *workspace, size_t workspace_bytes, void *stream);
+
+/* Measurement / test knob: how weights of the 3INST and MCG codebooks enter the tensor-core product.
+ * -1 = library default, 0 = split (each weight as its two fp16 summands, added exactly by the fp32 accumulator),
+ * 1 = paired (weights rounded to fp16 first, as the reference decoder's table).  No counterpart in the reference. */
+void exl3_set_gemv_mode(int mode);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXL3_B200_H */

@@ -1,0 +1,257 @@
+// extern "C" entry points of libexl3_b200 (declared in include/exl3_b200.h): argument checks, workspace
+// carving, launches.  No entry point allocates device memory.
+#include <cstdio>
+#include <cstring>
+
+#include "exl3_internal.h"
+
+namespace exl3 {
+
+static int g_last_cuda_error = 0;
+static DeviceInfo g_devices[64];
+
+int cuda_status(cudaError_t e)
+{
+    if (e == cudaSuccess) return EXL3_OK;
+    g_last_cuda_error = (int)e;
+    return EXL3_ERR_CUDA;
+}
+
+const DeviceInfo* current_device_info()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return g_devices[dev].ready ? &g_devices[dev] : nullptr;
+}
+
+static bool aligned(const void* p, size_t a) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+static int check_matrix(int k, int n, int K, int cb)
+{
+    if (k < 0 || n < 0 || (k % 128) || (n % 128)) return EXL3_ERR_BAD_SHAPE;
+    if (K < 2 || K > 8) return EXL3_ERR_UNSUPPORTED_K;
+    if (cb < 0 || cb > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    return EXL3_OK;
+}
+
+static int fill_shards(GemvArgs& a, const int* shard_ends, int n_shards, int n_total)
+{
+    if (n_shards < 1 || n_shards > GEMV_MAX_SHARDS) return EXL3_ERR_BAD_SHAPE;
+    if (n_shards > 1 && shard_ends == nullptr) return EXL3_ERR_BAD_POINTER;
+    int prev = 0;
+    for (int s = 0; s < n_shards - 1; s++) {
+        int e = shard_ends[s];
+        if (e <= prev || e >= n_total || (e % 128)) return EXL3_ERR_BAD_SHAPE;
+        a.shard_end_blocks[s] = e / 128;
+        prev = e;
+    }
+    for (int s = n_shards - 1; s < GEMV_MAX_SHARDS; s++) a.shard_end_blocks[s] = n_total / 128;
+    a.n_shards = n_shards;
+    return EXL3_OK;
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" {
+
+const char* exl3_status_str(exl3_status s)
+{
+    switch (s) {
+        case EXL3_OK: return "ok";
+        case EXL3_ERR_BAD_SHAPE: return "bad shape: k and n must be non-negative multiples of 128, shard ends increasing multiples of 128";
+        case EXL3_ERR_UNSUPPORTED_K: return "unsupported bit rate: K must be an integer in 2..8";
+        case EXL3_ERR_UNSUPPORTED_CODEBOOK: return "unsupported codebook: 0 (3inst), 1 (mcg) or 2 (mul1)";
+        case EXL3_ERR_BAD_POINTER: return "null or misaligned pointer";
+        case EXL3_ERR_WORKSPACE: return "workspace missing or too small";
+        case EXL3_ERR_CUDA: return "CUDA runtime error";
+        case EXL3_ERR_DEVICE_WAIT: return "a bounded device-side wait gave up";
+        case EXL3_ERR_NOT_INITIALISED: return "exl3_init_device was not called for the current device";
+        case EXL3_ERR_UNSUPPORTED_ROWS: return "unsupported row count";
+        case EXL3_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype";
+    }
+    return "unknown status";
+}
+
+int exl3_last_cuda_error(void) { return g_last_cuda_error; }
+int exl3_version(void) { return 100; }
+
+exl3_status exl3_init_device(int device)
+{
+    if (device < 0 || device >= 64) return EXL3_ERR_BAD_SHAPE;
+    int prev = -1;
+    if (int rc = cuda_status(cudaGetDevice(&prev))) return rc;
+    if (int rc = cuda_status(cudaSetDevice(device))) return rc;
+    DeviceInfo& d = g_devices[device];
+    int rc = EXL3_OK;
+    if (!d.ready) {
+        rc = cuda_status(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+        if (rc == EXL3_OK) rc = cuda_status(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        if (rc == EXL3_OK) {
+            d.ready = true;
+            rc = gemv_init_device();
+            if (rc != EXL3_OK) d.ready = false;
+        }
+    }
+    cudaSetDevice(prev);
+    return rc;
+}
+
+size_t exl3_packed_bytes(int k, int n, int K)
+{
+    if (k < 0 || n < 0 || K < 2 || K > 8) return 0;
+    return (size_t)k * (size_t)n * (size_t)K / 8;
+}
+
+exl3_status exl3_repack(const uint16_t* trellis, int k, int n, int K, uint32_t* packed, void* stream)
+{
+    if (int rc = check_matrix(k, n, K, 0)) return rc;
+    if ((long long)k * n == 0) return EXL3_OK;
+    if (!aligned(trellis, 4) || !aligned(packed, 16)) return EXL3_ERR_BAD_POINTER;
+    return launch_repack(trellis, k, n, K, packed, (cudaStream_t)stream);
+}
+
+exl3_status exl3_unpack(const uint32_t* packed, int k, int n, int K, uint16_t* trellis, void* stream)
+{
+    if (int rc = check_matrix(k, n, K, 0)) return rc;
+    if ((long long)k * n == 0) return EXL3_OK;
+    if (!aligned(trellis, 4) || !aligned(packed, 16)) return EXL3_ERR_BAD_POINTER;
+    return launch_unpack(packed, k, n, K, trellis, (cudaStream_t)stream);
+}
+
+exl3_status exl3_reconstruct(const uint16_t* trellis, int k, int n, int K, int codebook, uint16_t* w, void* stream)
+{
+    if (k < 0 || n < 0 || (k % 16) || (n % 16)) return EXL3_ERR_BAD_SHAPE;
+    if (K < 2 || K > 8) return EXL3_ERR_UNSUPPORTED_K;
+    if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    if ((long long)k * n == 0) return EXL3_OK;
+    if (!aligned(trellis, 4) || !aligned(w, 2)) return EXL3_ERR_BAD_POINTER;
+    return launch_reconstruct_stored(trellis, k / 16, n / 16, K, codebook, reinterpret_cast<__half*>(w), (cudaStream_t)stream);
+}
+
+exl3_status exl3_reconstruct_packed(const uint32_t* packed, int k, int n, int K, int codebook, uint16_t* w, void* stream)
+{
+    if (int rc = check_matrix(k, n, K, codebook)) return rc;
+    if ((long long)k * n == 0) return EXL3_OK;
+    if (!aligned(packed, 16) || !aligned(w, 2)) return EXL3_ERR_BAD_POINTER;
+    return launch_reconstruct_packed(packed, k, n, K, codebook, reinterpret_cast<__half*>(w), (cudaStream_t)stream);
+}
+
+exl3_status exl3_had_in(const void* x, int x_dtype, const uint16_t* suh, int shards, int rows, int k, uint16_t* xh, void* stream)
+{
+    if (rows < 0 || shards < 1 || k < 0 || (k % 128)) return EXL3_ERR_BAD_SHAPE;
+    if (x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows == 0 || k == 0) return EXL3_OK;
+    if (!aligned(x, 2) || !aligned(xh, 8) || (suh && !aligned(suh, 2))) return EXL3_ERR_BAD_POINTER;
+    return launch_had_in(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh), shards, rows, k, xh, 0, (cudaStream_t)stream);
+}
+
+exl3_status exl3_had_out(const void* y, int y_dtype, const uint16_t* svh, int rows, int n, void* out, int64_t out_stride,
+                         int out_dtype, void* stream)
+{
+    if (rows < 0 || n < 0 || (n % 128) || out_stride < n || (out_stride % 4)) return EXL3_ERR_BAD_SHAPE;
+    if ((y_dtype != EXL3_F16 && y_dtype != EXL3_F32) || (out_dtype != EXL3_F16 && out_dtype != EXL3_BF16))
+        return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows == 0 || n == 0) return EXL3_OK;
+    if (!aligned(y, 2) || !aligned(out, 8)) return EXL3_ERR_BAD_POINTER;
+    return launch_had_out(y, y_dtype == EXL3_F32, reinterpret_cast<const __half*>(svh), rows, n, out, out_stride,
+                          out_dtype == EXL3_BF16, (cudaStream_t)stream);
+}
+
+size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards)
+{
+    if (k < 0 || n_total < 0 || n_shards < 1) return 0;
+    return workspace_layout(rows, k, n_total, n_shards).total;
+}
+
+static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor, const uint32_t* packed, int K, int codebook,
+                         const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k,
+                         int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated)
+{
+    if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
+    if (rows < 0) return EXL3_ERR_BAD_SHAPE;
+    GemvArgs a;
+    memset(&a, 0, sizeof(a));
+    if (int rc = fill_shards(a, shard_ends, n_shards, n_total)) return rc;
+    if (!rotated && x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16 && !(y_dtype == EXL3_F32 && !rotated)) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
+    if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
+    if (!aligned(packed, 16) || !aligned(y, 16)) return EXL3_ERR_BAD_POINTER;
+    if (rotated ? !aligned(xh_rowmajor, 2) : (!aligned(x, 2) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8)))
+        return EXL3_ERR_BAD_POINTER;
+    const WorkspaceLayout wl = workspace_layout(rows, k, n_total, n_shards);
+    if (!aligned(workspace, 256) || workspace_bytes < wl.total) return EXL3_ERR_WORKSPACE;
+    unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+
+    a.packed = packed;
+    a.xf = reinterpret_cast<const uint32_t*>(ws + wl.xf_off);
+    a.svh = reinterpret_cast<const __half*>(svh_cat);
+    a.partials = reinterpret_cast<float*>(ws + wl.partials_off);
+    a.counters = reinterpret_cast<int*>(ws + wl.counters_off);
+    a.err = reinterpret_cast<int*>(ws + wl.err_off);
+    a.K = K;
+    a.codebook = codebook;
+    a.mode = gemv_default_mode(codebook);
+    a.k = k;
+    a.n_total = n_total;
+    a.out_dtype = y_dtype;
+    a.rotated = rotated ? 1 : 0;
+    const size_t esz = 2, osz = y_dtype == EXL3_F32 ? 4 : 2;
+    for (int r0 = 0; r0 < rows; r0 += GEMV_MAX_ROWS) {
+        const int r = rows - r0 < GEMV_MAX_ROWS ? rows - r0 : GEMV_MAX_ROWS;
+        a.rows = r;
+        a.out = reinterpret_cast<unsigned char*>(y) + (size_t)r0 * n_total * osz;
+        int rc;
+        if (rotated) {
+            // shard s reads slab s of xh: rows [s*rows + r0, s*rows + r0 + r)
+            for (int s = 0; s < n_shards; s++) {
+                const __half* src = reinterpret_cast<const __half*>(xh_rowmajor) + ((size_t)s * rows + r0) * k;
+                uint32_t* dst = const_cast<uint32_t*>(a.xf) + (size_t)s * (k / 16) * r * 4 * gemv_frag_words(a.mode);
+                rc = launch_to_fragments(src, 1, r, k, dst, a.mode == GEMV_SPLIT ? 1 : 2, st);
+                if (rc) return rc;
+            }
+        } else {
+            const unsigned char* xr = reinterpret_cast<const unsigned char*>(x) + (size_t)r0 * k * esz;
+            rc = launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
+                               const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
+            if (rc) return rc;
+        }
+        rc = launch_gemv(a, st);
+        if (rc) return rc;
+    }
+    return EXL3_OK;
+}
+
+exl3_status exl3_linear(const void* x, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat,
+                        const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y,
+                        int y_dtype, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
+                         y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false);
+}
+
+exl3_status exl3_gemm_rotated(const uint16_t* xh, const uint32_t* packed, int K, int codebook, const int* shard_ends, int n_shards,
+                              int rows, int k, int n_total, uint16_t* out, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return linear_common(nullptr, EXL3_F16, xh, packed, K, codebook, nullptr, nullptr, shard_ends, n_shards, rows, k, n_total, out,
+                         EXL3_F16, workspace, workspace_bytes, (cudaStream_t)stream, true);
+}
+
+exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (!aligned(workspace, 256) || workspace_bytes < 256) return EXL3_ERR_WORKSPACE;
+    int code = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (int rc = cuda_status(cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, st))) return rc;
+    if (int rc = cuda_status(cudaStreamSynchronize(st))) return rc;
+    if (code == 0) return EXL3_OK;
+    if (int rc = cuda_status(cudaMemsetAsync(workspace, 0, sizeof(int), st))) return rc;
+    return EXL3_ERR_DEVICE_WAIT;
+}
+
+/* Test / measurement knob: force how hash-codebook weights enter the MMA (-1 default, 0 split, 1 paired). */
+void exl3_set_gemv_mode(int mode) { gemv_set_mode_override(mode); }
+
+}  // extern "C"

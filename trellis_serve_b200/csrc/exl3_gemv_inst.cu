@@ -1,0 +1,53 @@
+// Instantiates the decode GEMV for one bit rate.  Compiled once per K with -DEXL3_GEMV_K=<2..8>.
+#include "exl3_gemv_kernel.cuh"
+
+#ifndef EXL3_GEMV_K
+#error "compile with -DEXL3_GEMV_K=<2..8>"
+#endif
+
+namespace exl3 {
+
+template <int K, int MODE, int FAM, int MB>
+static int launch_one(const GemvLaunch& l, size_t smem, cudaStream_t st)
+{
+    gemv_kernel<K, MODE, FAM, MB><<<l.grid, GEMV_THREADS, smem, st>>>(l);
+    return cuda_status(cudaGetLastError());
+}
+
+template <int K, int MODE, int FAM, int MB>
+static int set_attr(int max_smem)
+{
+    return cuda_status(cudaFuncSetAttribute(gemv_kernel<K, MODE, FAM, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+}
+
+size_t gemv_smem_bytes(const GemvLaunch& l);
+
+template <>
+int launch_gemv_for_k<EXL3_GEMV_K>(const GemvLaunch& l, cudaStream_t st)
+{
+    constexpr int K = EXL3_GEMV_K;
+    const size_t smem = gemv_smem_bytes(l);
+    const bool two = l.a.rows > 8;
+    const int fam = codebook_family(l.a.codebook);
+    if (l.a.mode == GEMV_SPLIT && fam == FAM_HASH)
+        return two ? launch_one<K, GEMV_SPLIT, FAM_HASH, 2>(l, smem, st) : launch_one<K, GEMV_SPLIT, FAM_HASH, 1>(l, smem, st);
+    if (fam == FAM_HASH)
+        return two ? launch_one<K, GEMV_PAIRED, FAM_HASH, 2>(l, smem, st) : launch_one<K, GEMV_PAIRED, FAM_HASH, 1>(l, smem, st);
+    return two ? launch_one<K, GEMV_PAIRED, FAM_MUL1, 2>(l, smem, st) : launch_one<K, GEMV_PAIRED, FAM_MUL1, 1>(l, smem, st);
+}
+
+template <>
+int gemv_set_attributes_for_k<EXL3_GEMV_K>(int max_smem)
+{
+    constexpr int K = EXL3_GEMV_K;
+    int rc = EXL3_OK;
+    if (rc == EXL3_OK) rc = set_attr<K, GEMV_SPLIT, FAM_HASH, 1>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, GEMV_SPLIT, FAM_HASH, 2>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_HASH, 1>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_HASH, 2>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_MUL1, 1>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_MUL1, 2>(max_smem);
+    return rc;
+}
+
+}  // namespace exl3

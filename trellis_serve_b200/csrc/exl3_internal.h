@@ -1,0 +1,78 @@
+// Internal declarations shared by the .cu files of libexl3_b200 (not part of the C ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <type_traits>
+
+#include "../../include/exl3_b200.h"
+#include "exl3_decode.cuh"
+
+namespace exl3 {
+
+// Records a CUDA runtime error for exl3_last_cuda_error() and maps it to a status.
+int cuda_status(cudaError_t e);
+
+struct DeviceInfo {
+    bool ready = false;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+};
+// State of the current device, or nullptr if exl3_init_device() has not run for it.
+const DeviceInfo* current_device_info();
+
+// exl3_kernels.cu
+int launch_repack(const uint16_t* trellis, int k, int n, int K, uint32_t* packed, cudaStream_t st);
+int launch_unpack(const uint32_t* packed, int k, int n, int K, uint16_t* trellis, cudaStream_t st);
+int launch_reconstruct_stored(const uint16_t* trellis, int kt, int nt, int K, int cb, __half* w, cudaStream_t st);
+int launch_reconstruct_packed(const uint32_t* packed, int k, int n, int K, int cb, __half* w, cudaStream_t st);
+int launch_had_in(const void* x, int x_bf16, const __half* suh, int shards, int rows, int k, void* out, int mode, cudaStream_t st);
+int launch_to_fragments(const __half* xh, int shards, int rows, int k, uint32_t* out, int mode, cudaStream_t st);
+int launch_had_out(const void* y, int y_f32, const __half* svh, int rows, int n, void* out, long long out_stride, int out_bf16,
+                   cudaStream_t st);
+
+// exl3_gemv.cu -------------------------------------------------------------------------------------------
+
+// How decoded weights enter the tensor-core product.
+//   GEMV_SPLIT   hash codebooks: each weight occupies two k slots of the MMA as its two fp16 summands, the
+//                activation is duplicated; the fp32 accumulator adds them exactly (no fp16 add, no packing).
+//   GEMV_PAIRED  any codebook: weights are rounded to fp16 and packed two per register.
+enum { GEMV_SPLIT = 0, GEMV_PAIRED = 1 };
+
+constexpr int GEMV_MAX_ROWS = 16;          // rows per launch
+constexpr int GEMV_MAX_GRID = 256;         // upper bound of persistent CTAs assumed when sizing workspaces
+constexpr int GEMV_MAX_SHARDS = 4;
+
+// Words per lane of one activation fragment (four k values of a 16-row tile) in each mode.
+__host__ __device__ constexpr int gemv_frag_words(int mode) { return mode == GEMV_SPLIT ? 4 : 2; }
+
+struct GemvArgs {
+    const uint32_t* packed;     // resident weights, n-blocks of all shards concatenated
+    const uint32_t* xf;         // activation fragments [shard][k/16][rows][4][frag_words]
+    const __half* svh;          // [n_total]; unused when rotated
+    void* out;                  // [rows, n_total]
+    float* partials;            // [(grid + NB)][rows][128]
+    int* counters;              // [NB], zero between launches
+    int* err;                   // device error word
+    int K, codebook, mode;
+    int rows, k, n_total;
+    int n_shards;
+    int shard_end_blocks[GEMV_MAX_SHARDS];   // n-block index where shard s ends (last = NB)
+    int out_dtype;              // EXL3_F16 / EXL3_BF16 / EXL3_F32 (fp32 only with the output Hadamard)
+    int rotated;                // 1: store the rotated-basis product as fp16, no output Hadamard
+};
+
+// Preferred mode for a codebook (split for the hash codebooks, paired for MUL1).
+int gemv_default_mode(int codebook);
+void gemv_set_mode_override(int mode);      // -1 = default; test / measurement knob
+int launch_gemv(const GemvArgs& a, cudaStream_t st);
+int gemv_init_device();
+
+// Workspace carved up identically by every entry point that takes one.
+struct WorkspaceLayout {
+    size_t err_off, counters_off, xf_off, partials_off, total;
+};
+WorkspaceLayout workspace_layout(int rows, int k, int n_total, int n_shards);
+
+}  // namespace exl3
