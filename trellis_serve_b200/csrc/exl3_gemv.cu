@@ -4,6 +4,8 @@
 namespace exl3 {
 
 static int g_mode_override = -1;
+static int g_probe = 0;
+void gemv_set_probe(int v) { g_probe = v; }
 
 int gemv_default_mode(int codebook)
 {
@@ -15,6 +17,7 @@ void gemv_set_mode_override(int mode) { g_mode_override = mode; }
 
 constexpr size_t GEMV_FIXED_SMEM = 256 + GEMV_MAX_ROWS * 128 * 4;
 constexpr size_t GEMV_RING_TARGET = 96 * 1024;
+constexpr size_t GEMV_STAGE_TARGET = 24 * 1024;
 
 size_t gemv_smem_bytes(const GemvLaunch& l) { return GEMV_FIXED_SMEM + (size_t)l.stages * l.stage_stride; }
 
@@ -57,16 +60,23 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     l.NB = a.n_total / 128;
     const long long units = (long long)l.KG * l.NB;
     if (units == 0) return EXL3_OK;
-    int grid = d->sm_count < GEMV_MAX_GRID ? d->sm_count : GEMV_MAX_GRID;
+    int grid = d->sm_count * GEMV_CTAS_PER_SM;
+    if (grid > GEMV_MAX_GRID) grid = GEMV_MAX_GRID;
     if (units < grid) grid = (int)units;
     l.grid = grid;
     l.units_q = (int)(units / grid);
     l.units_r = (int)(units % grid);
     const int fw = gemv_frag_words(a.mode);
-    l.xf_bytes = (uint32_t)(128 * fw * a.rows);
-    l.stage_stride = (uint32_t)((2048u * a.K + l.xf_bytes + 127u) & ~127u);
+    // Stage = as many whole units as make one bulk copy of about 24-32 KB; at least 3 stages in flight.
+    const uint32_t unit_bytes = 2048u * a.K;
+    int ups = (int)((GEMV_STAGE_TARGET + unit_bytes - 1) / unit_bytes);
+    if (ups < 1) ups = 1;
+    const long long per_cta = units / grid;
+    if (per_cta < 3ll * ups) ups = (int)(per_cta / 3 > 0 ? per_cta / 3 : 1);      // short ranges: keep several copies in flight
+    l.units_per_stage = ups;
+    l.stage_stride = (uint32_t)ups * unit_bytes;
     int stages = (int)(GEMV_RING_TARGET / l.stage_stride);
-    const int cap = (int)((d->max_smem_optin - GEMV_FIXED_SMEM) / l.stage_stride);
+    const int cap = (int)((d->max_smem_optin / GEMV_CTAS_PER_SM - 2048 - GEMV_FIXED_SMEM) / l.stage_stride);
     if (stages > cap) stages = cap;
     if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
     if (stages < 2) return EXL3_ERR_UNSUPPORTED_ROWS;
@@ -75,6 +85,9 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     l.mul = c.mul;
     l.add = c.add;
     l.xf_shard_stride = (long long)(a.k / 16) * a.rows * 4 * fw;
+    for (int c = 0; c <= 16; c++) l.pw.v[c] = 1u << c;
+    l.probe = g_probe;
+    l.zeros = reinterpret_cast<const unsigned char*>(a.err) + 64;      // the workspace header stays zero past the error word
     switch (a.K) {
         case 2: return launch_gemv_for_k<2>(l, st);
         case 3: return launch_gemv_for_k<3>(l, st);

@@ -27,6 +27,7 @@ namespace exl3 {
 constexpr int GEMV_CONSUMER_WARPS = 16;
 constexpr int GEMV_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;
 constexpr int GEMV_MAX_STAGES = 12;
+constexpr int GEMV_CTAS_PER_SM = 2;         // two resident CTAs per SM: twice the warps to hide instruction latency
 
 enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2 };
 
@@ -36,9 +37,12 @@ struct GemvLaunch {
     int units_q, units_r;       // units per CTA: the first units_r CTAs take units_q + 1
     int stages;
     uint32_t stage_stride;      // bytes
-    uint32_t xf_bytes;          // activation fragment bytes per unit
+    int units_per_stage;        // units covered by one bulk copy
+    const void* zeros;          // at least 16 bytes of zeros in global memory
     uint32_t mul, add;
     long long xf_shard_stride;  // words between shards in xf
+    int probe;
+    Pow2 pw;                    // powers of two for the multiply that cuts a window out (constant bank)
 };
 
 __host__ __device__ inline long long gemv_first_unit(int cta, int q, int r) { return (long long)cta * q + (cta < r ? cta : r); }
@@ -50,11 +54,11 @@ __device__ __forceinline__ int gemv_cta_of_unit(long long u, int q, int r)
 }
 
 template <int K, int MODE, int FAM>
-__device__ __forceinline__ void decode_tile_regs(const LaneTile<K>& lt, CodebookConst cbc, uint32_t (&w)[8])
+__device__ __forceinline__ void decode_tile_regs(const LaneRegs<K>& R, const Pow2& pw, CodebookConst cbc, uint32_t (&w)[8])
 {
     uint32_t s[8];
-    s[0] = window<K, 0>(lt); s[1] = window<K, 1>(lt); s[2] = window<K, 2>(lt); s[3] = window<K, 3>(lt);
-    s[4] = window<K, 4>(lt); s[5] = window<K, 5>(lt); s[6] = window<K, 6>(lt); s[7] = window<K, 7>(lt);
+    s[0] = window_mul<K, 0>(R, pw); s[1] = window_mul<K, 1>(R, pw); s[2] = window_mul<K, 2>(R, pw); s[3] = window_mul<K, 3>(R, pw);
+    s[4] = window_mul<K, 4>(R, pw); s[5] = window_mul<K, 5>(R, pw); s[6] = window_mul<K, 6>(R, pw); s[7] = window_mul<K, 7>(R, pw);
     if constexpr (MODE == GEMV_SPLIT) {
 #pragma unroll
         for (int j = 0; j < 8; j++) w[j] = hash_pair(s[j], cbc);
@@ -69,7 +73,7 @@ __device__ __forceinline__ void decode_tile_regs(const LaneTile<K>& lt, Codebook
 
 // MODE: GEMV_SPLIT / GEMV_PAIRED.  FAM: FAM_HASH / FAM_MUL1 (split implies hash).  MB: 8-row groups (1 or 2).
 template <int K, int MODE, int FAM, int MB>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvLaunch p)
+__global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(const GemvLaunch p)
 {
     constexpr int FW = gemv_frag_words(MODE);
     constexpr uint32_t W_BYTES = 2048u * K;
@@ -99,28 +103,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvLaunch 
 
     if (warp == GEMV_CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer
+        // One bulk copy per stage and stages of several units: the copy engine has a fixed cost of a few hundred
+        // nanoseconds per bulk copy, so small copies cap the stream far below HBM speed.  The CTA's units are
+        // contiguous in memory, so a stage is simply the next `units_per_stage` units.  One thread issues the
+        // copies in ring order and sleeps between polls while it waits for the oldest stage to be released.
         if (lane == 0) {
-            int nb = (int)(u0 / p.KG), kg = (int)(u0 % p.KG);
-            int shard = 0;
-            while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
-            int it = 0;
-            for (long long u = u0; u < u1; u++, it++) {
-                const int s = it % p.stages;
-                if (it >= p.stages) {
-                    if (!ptx::mbar_wait(&empty[s], ((it / p.stages) & 1) ^ 1)) {
-                        atomicExch(p.a.err, GEMV_ERR_EMPTY_WAIT);
-                        break;
-                    }
+            int s = 0;
+            uint32_t wait_parity = 1;              // parity of the empty-barrier phase awaited in the current lap
+            bool first_lap = true;
+            for (long long u = u0; u < u1; u += p.units_per_stage) {
+                if (!first_lap && !ptx::mbar_wait_relaxed(&empty[s], wait_parity)) {
+                    atomicExch(p.a.err, GEMV_ERR_EMPTY_WAIT);
+                    break;
                 }
-                unsigned char* dst = stage0 + (size_t)s * p.stage_stride;
-                ptx::mbar_arrive_expect_tx(&full[s], W_BYTES + p.xf_bytes);
-                ptx::bulk_g2s(dst, p.a.packed + u * (512ll * K), W_BYTES, &full[s]);
-                const uint32_t* xsrc = p.a.xf + shard * p.xf_shard_stride + (long long)kg * 8 * rows * 4 * FW;
-                ptx::bulk_g2s(dst + W_BYTES, xsrc, p.xf_bytes, &full[s]);
-                if (++kg == p.KG) {
-                    kg = 0;
-                    nb++;
-                    while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
+                const long long left = u1 - u;
+                const uint32_t bytes = (uint32_t)(left < p.units_per_stage ? left : p.units_per_stage) * W_BYTES;
+                ptx::mbar_arrive_expect_tx(&full[s], bytes);
+                ptx::bulk_g2s(stage0 + (size_t)s * p.stage_stride, p.a.packed + u * (512ll * K), bytes, &full[s]);
+                if (++s == p.stages) {
+                    s = 0;
+                    if (first_lap) { first_lap = false; wait_parity = 0; } else wait_parity ^= 1;
                 }
             }
         }
@@ -139,13 +141,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvLaunch 
 
     const uint32_t stage0_addr = ptx::smem_addr(stage0);
     const uint32_t w_off = (uint32_t)((nt * 2 + kq) * K) * 128u + lane * 4u;
-    bool row_ok[MB];
-#pragma unroll
-    for (int mb = 0; mb < MB; mb++) row_ok[mb] = (g + 8 * mb) < rows;
-
     int nb = (int)(u0 / p.KG), kg = (int)(u0 % p.KG);
     bool dirty = false;
-    int it = 0;
 
     auto flush = [&](int fnb) {
         // acc -> P (the two k-halves of a column tile add up), then either finish the block here or hand the
@@ -239,58 +236,111 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvLaunch 
             for (int e = 0; e < 4; e++) acc[mb][e] = 0.f;
     };
 
-    for (long long u = u0; u < u1; u++, it++) {
-        const int s = it % p.stages;
-        if (!ptx::mbar_wait(&full[s], (it / p.stages) & 1)) {
+    // Activation fragments come straight from global memory (they are tiny and stay in L1/L2).  Lanes whose batch
+    // row does not exist read a block of zeros instead, so no select is needed per tile.
+    // Fragment elements are FW words: element index = (k-tile * rows + row) * 4 + q.
+    using Frag = typename std::conditional<FW == 4, uint4, uint2>::type;
+    const Frag* x_base[MB];
+    uint32_t x_lane[MB], x_tile[MB], x_unit[MB];      // element offsets: lane, per 16-row tile, per unit (8 tiles)
+#pragma unroll
+    for (int mb = 0; mb < MB; mb++) {
+        const bool ok = (g + 8 * mb) < rows;
+        x_base[mb] = reinterpret_cast<const Frag*>(ok ? static_cast<const void*>(p.a.xf) : p.zeros);
+        x_lane[mb] = ok ? (uint32_t)((g + 8 * mb) * 4 + q + kq * 4 * rows * 4) : 0u;
+        x_tile[mb] = ok ? (uint32_t)(rows * 4) : 0u;
+        x_unit[mb] = ok ? (uint32_t)(8 * rows * 4) : 0u;
+    }
+    const uint32_t x_shard_elems = (uint32_t)(p.xf_shard_stride / FW);
+    bool aborted = false;
+    const int ups = p.units_per_stage;
+
+    auto wait_stage = [&](int slot, uint32_t phase) {
+        if (!aborted && !ptx::mbar_wait(&full[slot], phase)) {
             // Give up on the data but keep the control flow of every warp identical, so nothing deadlocks.
+            aborted = true;
             if (lane == 0) atomicExch(p.a.err, GEMV_ERR_FULL_WAIT);
         }
-        const uint32_t sbase = stage0_addr + (uint32_t)s * p.stage_stride;
+    };
+
+    int shard = 0;
+    while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
+    // Everything that changes from unit to unit is kept as a running value (no division, no 64-bit arithmetic
+    // in the steady state): shared-memory address of the warp's words, fragment offsets, unit-in-stage counter.
+    int slot = 0, in_stage = 0;
+    uint32_t phase = 0;
+    uint32_t waddr = stage0_addr + w_off;
+    uint32_t xu[MB];
+#pragma unroll
+    for (int mb = 0; mb < MB; mb++)
+        xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems + (uint32_t)kg * x_unit[mb] : 0u);
+    int remaining = (int)(u1 - u0);
+    if (remaining > 0) wait_stage(0, 0);
+
+    while (remaining > 0) {
         uint32_t L[K];
 #pragma unroll
-        for (int i = 0; i < K; i++) L[i] = ptx::lds32(sbase + w_off + i * 128u);
-        const uint32_t xbase = sbase + W_BYTES;
+        for (int i = 0; i < K; i++) L[i] = ptx::lds32(waddr + i * 128u);
+        // All activation fragments of the unit are requested up front so that their latency hides behind the decode.
+        Frag bfrag[MB][4];
+#pragma unroll
+        for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+            for (int T = 0; T < 4; T++) bfrag[mb][T] = __ldg(x_base[mb] + (xu[mb] + T * x_tile[mb]));
 
         auto tile = [&](auto tconst) {
             constexpr int T = decltype(tconst)::value;
             uint32_t own[2];
             own_words<K, T>(L, own);
             const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
-            const LaneTile<K> lt = assemble<K>(own, prev0);
+            const LaneRegs<K> R = lane_regs<K>(own, prev0);
             uint32_t w[8];
-            decode_tile_regs<K, MODE, FAM>(lt, cbc, w);
-            const int ktl = kq * 4 + T;
+            decode_tile_regs<K, MODE, FAM>(R, p.pw, cbc, w);
 #pragma unroll
             for (int mb = 0; mb < MB; mb++) {
-                const uint32_t xaddr = xbase + (uint32_t)(((ktl * rows + g + 8 * mb) * 4 + q) * FW) * 4u;
                 if constexpr (MODE == GEMV_SPLIT) {
-                    uint4 b = make_uint4(0, 0, 0, 0);
-                    if (row_ok[mb]) b = ptx::lds128(xaddr);
+                    const uint4 b = bfrag[mb][T];
                     ptx::mma_m16n8k16(acc[mb], w[0], w[4], w[1], w[5], b.x, b.y);
                     ptx::mma_m16n8k16(acc[mb], w[2], w[6], w[3], w[7], b.z, b.w);
                 } else {
-                    uint2 b = make_uint2(0, 0);
-                    if (row_ok[mb]) b = ptx::lds64(xaddr);
+                    const uint2 b = bfrag[mb][T];
                     ptx::mma_m16n8k16(acc[mb], w[0], w[2], w[1], w[3], b.x, b.y);
                 }
             }
         };
-        tile(std::integral_constant<int, 0>{});
-        tile(std::integral_constant<int, 1>{});
-        tile(std::integral_constant<int, 2>{});
-        tile(std::integral_constant<int, 3>{});
+        if (!(p.probe & 1)) {
+            tile(std::integral_constant<int, 0>{});
+            tile(std::integral_constant<int, 1>{});
+            tile(std::integral_constant<int, 2>{});
+            tile(std::integral_constant<int, 3>{});
+        }
 
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&empty[s]);
+        remaining--;
+        waddr += W_BYTES;
+#pragma unroll
+        for (int mb = 0; mb < MB; mb++) xu[mb] += x_unit[mb];
+        if (++in_stage == ups || remaining == 0) {          // stage finished: hand it back, move to the next one
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+            in_stage = 0;
+            if (++slot == p.stages) {
+                slot = 0;
+                phase ^= 1;
+            }
+            waddr = stage0_addr + (uint32_t)slot * p.stage_stride + w_off;
+            if (remaining > 0) wait_stage(slot, phase);
+        }
         dirty = true;
-        if (++kg == p.KG) {
-            flush(nb);
+        if (++kg == p.KG) {                                  // column block finished
+            if (!(p.probe & 2)) flush(nb);
             dirty = false;
             kg = 0;
             nb++;
+            while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
+#pragma unroll
+            for (int mb = 0; mb < MB; mb++) xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems : 0u);
         }
     }
-    if (dirty) flush(nb);
+    if (dirty && !(p.probe & 2)) flush(nb);
 }
 
 template <int K>

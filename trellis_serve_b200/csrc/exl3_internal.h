@@ -41,7 +41,7 @@ int launch_had_out(const void* y, int y_f32, const __half* svh, int rows, int n,
 enum { GEMV_SPLIT = 0, GEMV_PAIRED = 1 };
 
 constexpr int GEMV_MAX_ROWS = 16;          // rows per launch
-constexpr int GEMV_MAX_GRID = 256;         // upper bound of persistent CTAs assumed when sizing workspaces
+constexpr int GEMV_MAX_GRID = 512;         // upper bound of persistent CTAs assumed when sizing workspaces
 constexpr int GEMV_MAX_SHARDS = 4;
 
 // Words per lane of one activation fragment (four k values of a 16-row tile) in each mode.
@@ -67,6 +67,7 @@ struct GemvArgs {
 int gemv_default_mode(int codebook);
 void gemv_set_mode_override(int mode);      // -1 = default; test / measurement knob
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
+void gemv_set_probe(int v);
 int gemv_init_device();
 
 // Workspace carved up identically by every entry point that takes one.

@@ -30,24 +30,38 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
+// A waiting warp is suspended by the hardware for up to this many nanoseconds per poll instead of burning issue slots.
+constexpr uint32_t MBAR_SUSPEND_NS = 20000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
         : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(MBAR_SUSPEND_NS)
         : "memory");
     return ok != 0;
 }
 
 // Bounded wait: about a second of polling at most, then gives up.
-constexpr uint32_t MBAR_MAX_POLLS = 1u << 22;
+constexpr uint32_t MBAR_MAX_POLLS = 1u << 20;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {
     for (uint32_t i = 0; i < MBAR_MAX_POLLS; i++)
         if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// Bounded wait for a thread that is in no hurry (a copy producer far ahead of its consumers): sleeps between polls
+// so that it does not take issue slots from the warps doing the work.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < MBAR_MAX_POLLS; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(256);
+    }
     return false;
 }
 
@@ -68,7 +82,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads)
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
 {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));

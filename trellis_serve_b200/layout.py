@@ -89,10 +89,11 @@ def _prmt(a: np.ndarray, b: np.ndarray, sel: int) -> np.ndarray:
     return out
 
 
-def lane_states(packed: np.ndarray, K: int) -> np.ndarray:
+def lane_states(packed: np.ndarray, K: int, pipe_balanced: bool = False) -> np.ndarray:
     """packed [NB, KG, 8, 2, K, 32] -> states uint16 [NB, KG, 8, 2, 4 (tile), 32 (lane), 8 (element)],
     computed exactly as a warp does it: per-tile right-aligned own words, the previous lane's low word, a byte
-    merge, then eight 16-bit windows."""
+    merge, then eight 16-bit windows.  `pipe_balanced` replays the GEMV's variant: 32-bit registers at 16-bit
+    offsets of the merged bits, one multiply by a power of two and one shift right by 16 per window."""
     L = np.ascontiguousarray(packed).transpose(0, 1, 2, 3, 5, 4).astype(np.uint32)          # [..., lane, K]
     out = np.empty(L.shape[:-1][:-1] + (4, 32, 8), dtype=np.uint16)
     zero = np.zeros(L.shape[:-1], dtype=np.uint32)
@@ -115,6 +116,23 @@ def lane_states(packed: np.ndarray, K: int) -> np.ndarray:
             e = [own0, _prmt(own1, prev0, 0x4210), prev0 >> np.uint32(8)]
         else:
             e = [own0, own1, prev0]
+        if pipe_balanced:
+            if K == 2:
+                R = [_prmt(own0, prev0, 0x5410)]
+            elif K == 3:
+                R = [_prmt(own0, prev0, 0x4210), _prmt(own0, prev0, 0x6542)]
+            elif K == 4:
+                R = [own0, _prmt(own0, prev0, 0x5432)]
+            else:
+                R = [e[0], _prmt(e[0], e[1], 0x5432), e[1], _prmt(e[1], e[2], 0x5432)]
+            for P in range(8):
+                j, sh = divmod(K * (7 - P), 16)
+                if sh == 0:
+                    s = R[j] & 0xFFFF
+                else:
+                    s = ((R[j].astype(np.uint64) << np.uint64(16 - sh)) & 0xFFFFFFFF).astype(np.uint32) >> np.uint32(16)
+                out[..., T, :, P] = s.astype(np.uint16)
+            continue
         for P in range(8):
             lo = K * (7 - P)
             wi, sh = divmod(lo, 32)
