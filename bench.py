@@ -139,7 +139,10 @@ def run_reference(args) -> None:
     ms = best["seconds_per_layer"] * 1e3
     line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": "one layer of the 64 per step"},
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": args.layers, "bits": K, "codebook": "3inst", "rows": args.rows,
+                       "parallelism": f"tp{args.gpus}", "l2": "inputs larger than L2, no flush",
+                       "packed_bytes_per_step": 64 * 123863040.0 if K == 3 else None},
             "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "tok_s": best["tok_s"], "gpu_launches": 0}
@@ -149,7 +152,7 @@ def run_reference(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=64)

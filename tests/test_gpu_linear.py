@@ -231,17 +231,22 @@ def test_bf16_boundary_equals_explicit_casts():
 
 
 def test_adversarial_inputs_stay_finite_and_accurate():
-    """Large magnitudes (outputs near 1e4, inside fp16 range) and activations in the fp16 denormal range."""
+    """Large magnitudes (outputs near 1e4, inside fp16 range), small ones, and activations in the fp16 denormal
+    range.  The rotated activations are fp16 (as in the reference's kernels, cuda/csrc/exl3_had.cuh:60-62), so inputs
+    that land in the denormal range keep only a few significant bits: there the result must stay finite and close
+    in norm, not meet the 2e-3 bound."""
     K, cb, k, n = 4, 0, 512, 256
     tr, suh, svh, _ = _case(1300, k, n, K, 1)
     rng = np.random.default_rng(3)
     big = (rng.standard_normal((2, k)) * 300.0).astype(np.float16)
+    small = (rng.standard_normal((2, k)) * 1e-2).astype(np.float16)
+    for x in (big, small):
+        _check_forward(tr, suh, svh, x, K, cb)
     tiny = (rng.standard_normal((2, k)) * 3e-6).astype(np.float16)
-    for x in (big, tiny):
-        y = _forward(tr, suh, svh, x, K, cb).float().cpu().numpy()
-        ref = orc.c_linear_forward(x, tr, suh, svh, K, cb)
-        assert np.isfinite(y).all()
-        assert orc.max_over_rms(y, ref) <= 4e-3           # fp16 rounding of tiny activations dominates here
+    y = _forward(tr, suh, svh, tiny, K, cb).float().cpu().numpy()
+    ref = orc.c_linear_forward(tiny, tr, suh, svh, K, cb)
+    assert np.isfinite(y).all()
+    assert orc.rel_norm(y, ref) <= 5e-2
 
 
 def test_had_in_and_had_out_building_blocks():

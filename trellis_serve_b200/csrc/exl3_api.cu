@@ -253,6 +253,5 @@ exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* str
 
 /* Test / measurement knob: force how hash-codebook weights enter the MMA (-1 default, 0 split, 1 paired). */
 void exl3_set_gemv_mode(int mode) { gemv_set_mode_override(mode); }
-void exl3_set_probe(int v) { gemv_set_probe(v); }
 
 }  // extern "C"

@@ -4,8 +4,7 @@
 namespace exl3 {
 
 static int g_mode_override = -1;
-static int g_probe = 0;
-void gemv_set_probe(int v) { g_probe = v; }
+
 
 int gemv_default_mode(int codebook)
 {
@@ -86,7 +85,6 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     l.add = c.add;
     l.xf_shard_stride = (long long)(a.k / 16) * a.rows * 4 * fw;
     for (int c = 0; c <= 16; c++) l.pw.v[c] = 1u << c;
-    l.probe = g_probe;
     l.zeros = reinterpret_cast<const unsigned char*>(a.err) + 64;      // the workspace header stays zero past the error word
     switch (a.K) {
         case 2: return launch_gemv_for_k<2>(l, st);

@@ -41,7 +41,6 @@ struct GemvLaunch {
     const void* zeros;          // at least 16 bytes of zeros in global memory
     uint32_t mul, add;
     long long xf_shard_stride;  // words between shards in xf
-    int probe;
     Pow2 pw;                    // powers of two for the multiply that cuts a window out (constant bank)
 };
 
@@ -307,12 +306,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 }
             }
         };
-        if (!(p.probe & 1)) {
-            tile(std::integral_constant<int, 0>{});
-            tile(std::integral_constant<int, 1>{});
-            tile(std::integral_constant<int, 2>{});
-            tile(std::integral_constant<int, 3>{});
-        }
+        tile(std::integral_constant<int, 0>{});
+        tile(std::integral_constant<int, 1>{});
+        tile(std::integral_constant<int, 2>{});
+        tile(std::integral_constant<int, 3>{});
 
         remaining--;
         waddr += W_BYTES;
@@ -331,7 +328,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         }
         dirty = true;
         if (++kg == p.KG) {                                  // column block finished
-            if (!(p.probe & 2)) flush(nb);
+            flush(nb);
             dirty = false;
             kg = 0;
             nb++;
@@ -340,7 +337,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             for (int mb = 0; mb < MB; mb++) xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems : 0u);
         }
     }
-    if (dirty && !(p.probe & 2)) flush(nb);
+    if (dirty) flush(nb);
 }
 
 template <int K>

@@ -67,7 +67,6 @@ struct GemvArgs {
 int gemv_default_mode(int codebook);
 void gemv_set_mode_override(int mode);      // -1 = default; test / measurement knob
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
-void gemv_set_probe(int v);
 int gemv_init_device();
 
 // Workspace carved up identically by every entry point that takes one.
