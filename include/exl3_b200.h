@@ -39,7 +39,8 @@ enum {
     EXL3_ERR_DEVICE_WAIT = 7,        /* a bounded device-side wait gave up (reported by exl3_device_error) */
     EXL3_ERR_NOT_INITIALISED = 8,    /* exl3_init_device() was not called for the current device */
     EXL3_ERR_UNSUPPORTED_ROWS = 9,
-    EXL3_ERR_UNSUPPORTED_DTYPE = 10
+    EXL3_ERR_UNSUPPORTED_DTYPE = 10,
+    EXL3_ERR_STATIC_WORKSPACE = 11   /* exl3_linear_static: the problem needs more scratch than the built-in array holds */
 };
 
 enum { EXL3_CB_3INST = 0, EXL3_CB_MCG = 1, EXL3_CB_MUL1 = 2 };      /* core/src/trellis_core/reference.py:27 */
@@ -91,6 +92,24 @@ size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards);
 exl3_status exl3_linear(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
                         const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
                         int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/* The same fused linear for callers that can neither allocate device memory nor carry a workspace around: code
+ * running inside another framework's captured or memory-pool-managed region, plugin hooks that only receive the
+ * tensors of the call, hosts that hand out device memory once at start-up.  Its scratch is a fixed array of
+ * EXL3_STATIC_WORKSPACE_BYTES that lives inside the library (every GPU that loads the library holds it until the
+ * process exits); the entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - Problems whose scratch does not fit (see exl3_linear_workspace_bytes) are refused with EXL3_ERR_STATIC_WORKSPACE.
+ *   - The first call on each device looks the array's device address up; make that first call before any stream
+ *     capture on that device.
+ *   - All calls on a device share the one array, which keeps what the previous call left there (the library keeps
+ *     the parts that must be zero at zero).  Two calls that overlap on the GPU (different streams) race on it:
+ *     keep calls to this entry point in one stream order per device.
+ * Results are identical to exl3_linear.  No counterpart in the reference. */
+#define EXL3_STATIC_WORKSPACE_BYTES (8u << 20)
+exl3_status exl3_linear_static(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook,
+                               const uint16_t *suh_cat, const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows,
+                               int k, int n_total, void *y, int y_dtype, void *stream);
+size_t exl3_static_workspace_bytes(void);
 
 /* Rotated-basis product without the Hadamards: out[r, :] = xh[s(col)*rows + r, :] @ W_inner, fp16 out.
  * Identity rows of xh read the decoded weights out exactly.  Replaces exl3_gemm_marlin / exl3_gemm_marlin_multi

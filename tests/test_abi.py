@@ -36,7 +36,7 @@ def test_library_exports_every_declared_symbol():
 def test_status_strings_and_pure_functions():
     lib = _lib.load()
     assert lib.exl3_status_str(0) == b"ok"
-    for code in range(1, 11):
+    for code in range(1, 12):
         assert lib.exl3_status_str(code) not in (b"", b"unknown status")
     assert lib.exl3_status_str(999) == b"unknown status"
     assert lib.exl3_packed_bytes(4096, 4096, 4) == 8388608            # k*n*K/8: the stored size, no padding

@@ -70,6 +70,7 @@ const char* exl3_status_str(exl3_status s)
         case EXL3_ERR_NOT_INITIALISED: return "exl3_init_device was not called for the current device";
         case EXL3_ERR_UNSUPPORTED_ROWS: return "unsupported row count";
         case EXL3_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype";
+        case EXL3_ERR_STATIC_WORKSPACE: return "problem too large for the built-in scratch of exl3_linear_static: use exl3_linear with a workspace";
     }
     return "unknown status";
 }
@@ -250,6 +251,36 @@ exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* str
     if (int rc = cuda_status(cudaMemsetAsync(workspace, 0, sizeof(int), st))) return rc;
     return EXL3_ERR_DEVICE_WAIT;
 }
+
+/* ---- exl3_linear_static: the fused linear for callers that cannot bring a workspace ---------------------------
+ * Scratch (activation fragments, split-k partial sums, block counters, error word) lives in this file-scope device
+ * array instead of a caller buffer.  Every GPU that loads the library holds the array until the process exits. */
+static __device__ __align__(256) unsigned char g_static_workspace[EXL3_STATIC_WORKSPACE_BYTES];
+static void* g_static_workspace_ptr[64];
+
+exl3_status exl3_linear_static(const void* x, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat,
+                               const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y,
+                               int y_dtype, void* stream)
+{
+    if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
+    if (rows < 0 || n_shards < 1) return EXL3_ERR_BAD_SHAPE;
+    if (workspace_layout(rows, k, n_total, n_shards).total > EXL3_STATIC_WORKSPACE_BYTES) return EXL3_ERR_STATIC_WORKSPACE;
+    int dev = -1;
+    if (int rc = cuda_status(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= 64) return EXL3_ERR_BAD_SHAPE;
+    if (g_static_workspace_ptr[dev] == nullptr) {
+        // In host code the array's name is only a handle, not a device address: the address has to be asked for,
+        // once per device, with that device current.
+        void* ptr = nullptr;
+        if (int rc = cuda_status(cudaGetSymbolAddress(&ptr, g_static_workspace))) return rc;
+        if (ptr == nullptr) return EXL3_ERR_CUDA;
+        g_static_workspace_ptr[dev] = ptr;
+    }
+    return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
+                         y_dtype, g_static_workspace_ptr[dev], EXL3_STATIC_WORKSPACE_BYTES, (cudaStream_t)stream, false);
+}
+
+size_t exl3_static_workspace_bytes(void) { return EXL3_STATIC_WORKSPACE_BYTES; }
 
 /* Test / measurement knob: force how hash-codebook weights enter the MMA (-1 default, 0 split, 1 paired). */
 void exl3_set_gemv_mode(int mode) { gemv_set_mode_override(mode); }
