@@ -260,8 +260,12 @@ def main() -> None:
             line["cpu_baseline"] = {k: v for k, v in cpu_sample(K, cb).items() if k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
     if dist is not None:
+        # The captured step holds NCCL work; tearing the communicator down under it can block for minutes.
+        # All results are out, so synchronise, meet once more and leave without the teardown.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
