@@ -118,6 +118,43 @@ exl3_status exl3_gemm_rotated(const uint16_t *xh, const uint32_t *packed, int K,
                               int n_shards, int rows, int k, int n_total, uint16_t *out, void *workspace,
                               size_t workspace_bytes, void *stream);
 
+/* ---- MoE layer (routed experts) ------------------------------------------------------------------------
+ * One layer = align -> had_in (gate, up) -> grouped GEMV gate|up -> glu_had_in -> grouped GEMV down -> combine, the
+ * launch structure of cuda/src/sglang_exl3/kernels/marlin_moe.py:272-294.  Slots are (token, k) pairs, slot = t*top_k+j.
+ * Routing is consumed on the device (sorted_ids / expert_ids / num_post), so a captured CUDA graph replays with fresh
+ * routing.  Blocks are 8 rows of one expert; padding rows carry slot id >= slots.
+ *
+ * exl3_moe_align       replaces moe_align_decode (cuda/csrc/exl3_marlin_moe.cu:542-594) and the engine's
+ *                      moe_align_block_size: sorted_ids [cap] (padding = slots), expert_ids [cap/8] (-1 past the
+ *                      end), num_post [1] = padded row count.  cap >= exl3_moe_sorted_capacity().
+ * exl3_moe_had_in      replaces moe_had_in (exl3_marlin_moe.cu:210-225): per position Had128(fp16(x[token]) * suh[e, s])
+ *                      for `shards` input rotations (gate and up), written as MMA fragments.  suh is [E, shards, hidden].
+ * exl3_moe_gemm        replaces moe_gemm (exl3_marlin_moe.cu:376-408): per moe block, rows @ W[e] -> Had128 * svh[e] ->
+ *                      out[slot, :] fp16.  packed = [E] resident matrices; svh [E, n_total] (NULL: rotated basis, no
+ *                      output transform); shard_end: first column fed by input rotation 1 (0 = single rotation).
+ * exl3_moe_glu_had_in  replaces moe_glu_had_in (exl3_marlin_moe.cu:237-258): Had128(fp16(silu(g) * u) * suh2[e]);
+ *                      gu is [slots, 2*inter] fp16 (gate | up).
+ * exl3_moe_combine     replaces moe_combine (exl3_marlin_moe.cu:262-292): y[t] = sum_j w[t,j] * yd[t*top_k+j] in fp32,
+ *                      slot order, one rounding; expert ids outside [0, E) are skipped.
+ * The fragment buffers hold exl3_moe_fragment_bytes(); the GEMV workspace holds exl3_moe_workspace_bytes() and must be
+ * zero-filled once. */
+int exl3_moe_block_rows(void);
+size_t exl3_moe_sorted_capacity(int slots, int num_experts);
+exl3_status exl3_moe_align(const int32_t *topk_ids, int slots, int num_experts, int32_t *sorted_ids, int cap, int32_t *expert_ids,
+                           int32_t *num_post, void *stream);
+size_t exl3_moe_fragment_bytes(int cap, int k, int shards, int codebook);
+exl3_status exl3_moe_had_in(const void *x, int x_dtype, const uint16_t *suh, int shards, int hidden, int top_k, int slots,
+                            const int32_t *sorted_ids, int cap, const int32_t *expert_ids, const int32_t *num_post, int codebook,
+                            uint32_t *xf, void *stream);
+exl3_status exl3_moe_glu_had_in(const uint16_t *gu, const uint16_t *suh2, int inter, int slots, const int32_t *sorted_ids, int cap,
+                                const int32_t *expert_ids, const int32_t *num_post, int codebook, uint32_t *xf, void *stream);
+size_t exl3_moe_workspace_bytes(int cap, int n_total);
+exl3_status exl3_moe_gemm(const uint32_t *xf, const uint32_t *packed, int K, int codebook, const uint16_t *svh,
+                          const int32_t *sorted_ids, const int32_t *expert_ids, const int32_t *num_post, int cap, int slots, int k,
+                          int n_total, int shard_end, uint16_t *out, void *workspace, size_t workspace_bytes, void *stream);
+exl3_status exl3_moe_combine(const uint16_t *yd, const float *topk_weights, const int32_t *topk_ids, int tokens, int top_k,
+                             int hidden, int num_experts, void *y, int y_dtype, void *stream);
+
 /* Reads and clears the device-side error word kept in a workspace (set when a bounded wait in a kernel gave up).
  * Synchronises `stream`.  Returns EXL3_OK or EXL3_ERR_DEVICE_WAIT. */
 exl3_status exl3_device_error(void *workspace, size_t workspace_bytes, void *stream);

@@ -37,6 +37,15 @@ SIGNATURES = {
     "exl3_linear_static": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp]),
     "exl3_static_workspace_bytes": (_sz, []),
     "exl3_gemm_rotated": (_i, [_vp, _vp, _i, _i, _ip, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "exl3_moe_block_rows": (_i, []),
+    "exl3_moe_sorted_capacity": (_sz, [_i, _i]),
+    "exl3_moe_align": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp]),
+    "exl3_moe_fragment_bytes": (_sz, [_i, _i, _i, _i]),
+    "exl3_moe_had_in": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp]),
+    "exl3_moe_glu_had_in": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp]),
+    "exl3_moe_workspace_bytes": (_sz, [_i, _i]),
+    "exl3_moe_gemm": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "exl3_moe_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "exl3_device_error": (_i, [_vp, _sz, _vp]),
     "exl3_set_gemv_mode": (None, [_i]),
 }

@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "exl3_internal.h"
+#include "exl3_moe_kernel.cuh"
 
 namespace exl3 {
 
@@ -92,6 +93,7 @@ exl3_status exl3_init_device(int device)
         if (rc == EXL3_OK) {
             d.ready = true;
             rc = gemv_init_device();
+            if (rc == EXL3_OK) rc = moe_init_device();
             if (rc != EXL3_OK) d.ready = false;
         }
     }
@@ -250,6 +252,131 @@ exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* str
     if (code == 0) return EXL3_OK;
     if (int rc = cuda_status(cudaMemsetAsync(workspace, 0, sizeof(int), st))) return rc;
     return EXL3_ERR_DEVICE_WAIT;
+}
+
+/* ---- MoE ------------------------------------------------------------------------------------------------------ */
+
+namespace exl3 {
+struct MoeWorkspace {
+    size_t counters_off, partials_off, total;
+};
+static MoeWorkspace moe_workspace(int cap, int n_total)
+{
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t col_blocks = (size_t)(cap / MOE_BLOCK_ROWS) * (n_total / 128);
+    MoeWorkspace w;
+    w.counters_off = 256;
+    w.partials_off = up(w.counters_off + col_blocks * sizeof(int));
+    w.total = up(w.partials_off + (GEMV_MAX_GRID + col_blocks) * MOE_BLOCK_ROWS * 128 * sizeof(float));
+    return w;
+}
+}  // namespace exl3
+
+int exl3_moe_block_rows(void) { return MOE_BLOCK_ROWS; }
+
+size_t exl3_moe_sorted_capacity(int slots, int num_experts)
+{
+    if (slots < 0 || num_experts < 1) return 0;
+    size_t cap = (size_t)slots + (size_t)num_experts * (MOE_BLOCK_ROWS - 1);
+    cap = (cap + MOE_BLOCK_ROWS - 1) / MOE_BLOCK_ROWS * MOE_BLOCK_ROWS;
+    if (slots < num_experts && (size_t)slots * MOE_BLOCK_ROWS < cap) cap = (size_t)slots * MOE_BLOCK_ROWS;
+    return cap;
+}
+
+exl3_status exl3_moe_align(const int32_t* topk_ids, int slots, int num_experts, int32_t* sorted_ids, int cap, int32_t* expert_ids,
+                           int32_t* num_post, void* stream)
+{
+    if (slots < 0 || num_experts < 1 || num_experts > 4096 || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
+    if ((size_t)cap < exl3_moe_sorted_capacity(slots, num_experts)) return EXL3_ERR_BAD_SHAPE;
+    if (!aligned(num_post, 4) || (slots > 0 && !aligned(topk_ids, 4)) || (cap > 0 && (!aligned(sorted_ids, 4) || !aligned(expert_ids, 4))))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_moe_align(topk_ids, slots, num_experts, MOE_BLOCK_ROWS, cap, sorted_ids, expert_ids, num_post, (cudaStream_t)stream);
+}
+
+size_t exl3_moe_fragment_bytes(int cap, int k, int shards, int codebook)
+{
+    if (cap < 0 || k < 0 || shards < 1) return 0;
+    return (size_t)shards * cap * (k / 16) * 4 * gemv_frag_words(gemv_default_mode(codebook)) * sizeof(uint32_t);
+}
+
+exl3_status exl3_moe_had_in(const void* x, int x_dtype, const uint16_t* suh, int shards, int hidden, int top_k, int slots,
+                            const int32_t* sorted_ids, int cap, const int32_t* expert_ids, const int32_t* num_post, int codebook,
+                            uint32_t* xf, void* stream)
+{
+    if (hidden < 0 || (hidden % 128) || shards < 1 || top_k < 1 || slots < 0 || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
+    if (x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    if (cap == 0 || hidden == 0) return EXL3_OK;
+    if (!aligned(x, 2) || !aligned(suh, 2) || !aligned(xf, 16) || !aligned(sorted_ids, 4) || !aligned(expert_ids, 4) || !aligned(num_post, 4))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_moe_had_in(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh), shards, hidden, top_k, slots, cap, sorted_ids,
+                             expert_ids, num_post, xf, gemv_default_mode(codebook), (cudaStream_t)stream);
+}
+
+exl3_status exl3_moe_glu_had_in(const uint16_t* gu, const uint16_t* suh2, int inter, int slots, const int32_t* sorted_ids, int cap,
+                                const int32_t* expert_ids, const int32_t* num_post, int codebook, uint32_t* xf, void* stream)
+{
+    if (inter < 0 || (inter % 128) || slots < 0 || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
+    if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    if (cap == 0 || inter == 0) return EXL3_OK;
+    if (!aligned(gu, 2) || !aligned(suh2, 2) || !aligned(xf, 16) || !aligned(sorted_ids, 4) || !aligned(expert_ids, 4) || !aligned(num_post, 4))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_moe_glu_had_in(reinterpret_cast<const __half*>(gu), reinterpret_cast<const __half*>(suh2), inter, slots, cap, sorted_ids,
+                                 expert_ids, num_post, xf, gemv_default_mode(codebook), (cudaStream_t)stream);
+}
+
+size_t exl3_moe_workspace_bytes(int cap, int n_total)
+{
+    if (cap < 0 || n_total < 0) return 0;
+    return moe_workspace(cap, n_total).total;
+}
+
+exl3_status exl3_moe_gemm(const uint32_t* xf, const uint32_t* packed, int K, int codebook, const uint16_t* svh, const int32_t* sorted_ids,
+                          const int32_t* expert_ids, const int32_t* num_post, int cap, int slots, int k, int n_total, int shard_end,
+                          uint16_t* out, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
+    if (cap < 0 || (cap % MOE_BLOCK_ROWS) || slots < 0 || shard_end < 0 || shard_end > n_total || (shard_end % 128)) return EXL3_ERR_BAD_SHAPE;
+    if (cap == 0 || k == 0 || n_total == 0) return EXL3_OK;
+    if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
+    if (!aligned(xf, 16) || !aligned(packed, 16) || !aligned(out, 8) || (svh && !aligned(svh, 8)) || !aligned(sorted_ids, 4) ||
+        !aligned(expert_ids, 4) || !aligned(num_post, 4))
+        return EXL3_ERR_BAD_POINTER;
+    const MoeWorkspace wl = moe_workspace(cap, n_total);
+    if (!aligned(workspace, 256) || workspace_bytes < wl.total) return EXL3_ERR_WORKSPACE;
+    unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+    MoeGemmLaunch l;
+    memset(&l, 0, sizeof(l));
+    l.packed = packed;
+    l.expert_stride = (long long)k * n_total * K / 32;
+    l.xf = xf;
+    l.xf_shard_stride = (long long)(cap / MOE_BLOCK_ROWS) * (k / 16) * 32;
+    l.svh = reinterpret_cast<const __half*>(svh);
+    l.out = reinterpret_cast<__half*>(out);
+    l.sorted_ids = sorted_ids;
+    l.expert_ids = expert_ids;
+    l.num_post = num_post;
+    l.partials = reinterpret_cast<float*>(ws + wl.partials_off);
+    l.counters = reinterpret_cast<int*>(ws + wl.counters_off);
+    l.err = reinterpret_cast<int*>(ws);
+    l.KG = k / 128;
+    l.NB = n_total / 128;
+    l.n_total = n_total;
+    l.numel = slots;
+    l.shard_end_block = shard_end == 0 ? l.NB : shard_end / 128;
+    l.rotated = svh == nullptr;
+    return launch_moe_gemm(l, K, codebook, gemv_default_mode(codebook), (cudaStream_t)stream);
+}
+
+exl3_status exl3_moe_combine(const uint16_t* yd, const float* topk_weights, const int32_t* topk_ids, int tokens, int top_k, int hidden,
+                             int num_experts, void* y, int y_dtype, void* stream)
+{
+    if (tokens < 0 || top_k < 1 || hidden < 0 || (hidden % 2) || num_experts < 1) return EXL3_ERR_BAD_SHAPE;
+    if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (tokens == 0 || hidden == 0) return EXL3_OK;
+    if (!aligned(yd, 4) || !aligned(topk_weights, 4) || !aligned(topk_ids, 4) || !aligned(y, 4)) return EXL3_ERR_BAD_POINTER;
+    return launch_moe_combine(reinterpret_cast<const __half*>(yd), topk_weights, topk_ids, tokens, top_k, hidden, num_experts, y,
+                              y_dtype == EXL3_BF16, (cudaStream_t)stream);
 }
 
 /* ---- exl3_linear_static: the fused linear for callers that cannot bring a workspace ---------------------------

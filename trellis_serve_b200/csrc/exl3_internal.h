@@ -69,6 +69,18 @@ void gemv_set_mode_override(int mode);      // -1 = default; test / measurement 
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
 int gemv_init_device();
 
+// exl3_moe.cu -------------------------------------------------------------------------------------------
+struct MoeGemmLaunch;
+int moe_init_device();
+int launch_moe_align(const int* topk_ids, int numel, int E, int block, int cap, int* sorted_ids, int* expert_ids, int* num_post,
+                     cudaStream_t st);
+int launch_moe_had_in(const void* x, int x_bf16, const __half* suh, int shards, int hidden, int top_k, int numel, int cap,
+                      const int* sorted_ids, const int* expert_ids, const int* num_post, uint32_t* xf, int mode, cudaStream_t st);
+int launch_moe_glu_had_in(const __half* gu, const __half* suh2, int inter, int numel, int cap, const int* sorted_ids,
+                          const int* expert_ids, const int* num_post, uint32_t* xf, int mode, cudaStream_t st);
+int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, int tokens, int top_k, int hidden, int E, void* y,
+                       int y_bf16, cudaStream_t st);
+
 // Workspace carved up identically by every entry point that takes one.
 struct WorkspaceLayout {
     size_t err_off, counters_off, xf_off, partials_off, total;

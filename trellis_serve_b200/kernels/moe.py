@@ -1,0 +1,190 @@
+"""Routed-expert (MoE) EXL3 layer on B200: the function surface of the reference's grouped backend
+(cuda/src/sglang_exl3/kernels/marlin_moe.py of 0xSero/trellis-serve) over libexl3_b200's C ABI.
+
+All experts of a projection are stacked `[E, ...]` in the resident layout of the dense kernel, gate and up
+concatenated along n.  One layer is the reference's sequence (marlin_moe.py:272-294):
+
+    had_in (gather, per-expert suh, 2 rotations) -> grouped GEMV gate|up (output transform inside the launch)
+    -> glu_had_in (fp32 silu * up -> fp16 -> per-expert suh) -> grouped GEMV down -> fp32 router-weighted combine
+
+Every (token, expert) slot has its own input rotation because every expert has its own suh (marlin_moe.py:11-13).
+Routing is read on the device, so a captured CUDA graph replays with fresh routing.  Moe blocks are 8 rows of one
+expert (`BLOCK_SIZES`); `align` here produces the (sorted_ids, expert_ids, num_post_padded) triple that the engine's
+`moe_align_block_size` would, for that block size.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from .base import BackendStatus
+from .linear import _dtype_code, _ptr, _require_cuda, _stream, prepare_matrix
+
+BLOCK_SIZES = (8,)
+_workspace: dict[int, torch.Tensor] = {}
+
+
+def probe() -> BackendStatus:
+    try:
+        lib = _lib.load()
+    except (ImportError, OSError) as e:
+        return BackendStatus(False, detail=str(e))
+    return BackendStatus(True, version=str(lib.exl3_version()))
+
+
+def moe_block_size(tokens: int, top_k: int, num_experts: int) -> int:
+    """Rows per moe block.  The reference picks from a ladder 8..64 by shape (marlin_moe.py:52-57); the grouped GEMV
+    here always works on 8-row blocks, larger groups simply span several blocks."""
+    return BLOCK_SIZES[0]
+
+
+def sorted_ids_capacity(tokens: int, top_k: int, num_experts: int, block: int = 8) -> int:
+    """Length of sorted_ids for these shapes (same bound as the engine's moe_align_block_size)."""
+    return int(_lib.load().exl3_moe_sorted_capacity(tokens * top_k, num_experts))
+
+
+def stack_repacked(trellis: list[torch.Tensor]) -> torch.Tensor:
+    """E x int16 [k/16, n/16, 16K] -> int32 [E, n/128, k/128, 8, 2, K, 32]: a pure permutation of the stored words."""
+    shapes = {tuple(t.shape) for t in trellis}
+    if len(shapes) != 1:
+        raise ValueError(f"experts must share one shape and bitrate, got {sorted(shapes)}")
+    return torch.stack([prepare_matrix(t if t.is_cuda else t.cuda()) for t in trellis]).contiguous()
+
+
+def bits_of_stack(stack: torch.Tensor) -> int:
+    return stack.shape[-2]
+
+
+@dataclass
+class ExpertPack:
+    w13: torch.Tensor      # int32 [E, 2I/128, H/128, 8, 2, K, 32]   gate | up along n
+    w2: torch.Tensor       # int32 [E, H/128, I/128, 8, 2, K, 32]
+    suh13: torch.Tensor    # fp16 [E, 2, H]
+    svh13: torch.Tensor    # fp16 [E, 2I]
+    suh2: torch.Tensor     # fp16 [E, I]
+    svh2: torch.Tensor     # fp16 [E, H]
+    codebook: int
+    hidden: int
+    inter: int
+    num_experts: int
+    bits: int = 4
+
+    def tensors(self) -> list[torch.Tensor]:
+        return [self.w13, self.w2, self.suh13, self.svh13, self.suh2, self.svh2]
+
+
+def supports(gate: list[torch.Tensor], up: list[torch.Tensor], down: list[torch.Tensor], codebook: int) -> tuple[bool, str]:
+    shapes = {tuple(t.shape) for t in gate} | {tuple(t.shape) for t in up}
+    if len(shapes) != 1 or len({tuple(t.shape) for t in down}) != 1:
+        return False, "experts differ in shape / bitrate"
+    (kt, nt, words), (kt2, nt2, words2) = shapes.pop(), tuple(down[0].shape)
+    if words != words2 or words % 16 or not 2 <= words // 16 <= 8:
+        return False, "one integer K in 2..8 for all projections"
+    if kt % 8 or nt % 8 or kt2 != nt or nt2 != kt:
+        return False, "hidden / intermediate not multiples of 128, or down does not mirror gate/up"
+    if codebook not in (0, 1, 2):
+        return False, "codebook must be 3inst, mcg or mul1"
+    return True, ""
+
+
+def prepare(gate, up, down, codebook: int) -> ExpertPack:
+    """gate / up / down = (trellis list, suh list, svh list) indexed by expert.  Pure re-layout, no value changes."""
+    dev = gate[0][0].device
+    if dev.type != "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.init_device(dev.index)
+    w13 = torch.cat([stack_repacked(gate[0]), stack_repacked(up[0])], dim=1).contiguous()
+    w2 = stack_repacked(down[0])
+    suh13 = torch.stack([torch.stack(gate[1]), torch.stack(up[1])], dim=1).contiguous().to(dev)
+    svh13 = torch.cat([torch.stack(gate[2]), torch.stack(up[2])], dim=1).contiguous().to(dev)
+    suh2, svh2 = torch.stack(down[1]).contiguous().to(dev), torch.stack(down[2]).contiguous().to(dev)
+    hidden, inter = w13.shape[2] * 128, w2.shape[2] * 128
+    return ExpertPack(w13, w2, suh13, svh13, suh2, svh2, codebook, hidden, inter, w13.shape[0], bits_of_stack(w13))
+
+
+def _reserve(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    cur = _workspace.get(idx)
+    if cur is None or cur.numel() < nbytes:
+        cur = _workspace[idx] = torch.zeros(nbytes, dtype=torch.uint8, device=torch.device("cuda", idx))
+    return cur
+
+
+def align(topk_ids: torch.Tensor, num_experts: int, block: int = 8):
+    """-> (sorted_ids int32 [cap], expert_ids int32 [cap / 8], num_post_padded int32 [1]), computed on the device."""
+    _require_cuda(topk_ids, "topk_ids")
+    lib = _lib.load()
+    ids = topk_ids.reshape(-1).to(torch.int32).contiguous()
+    cap = int(lib.exl3_moe_sorted_capacity(ids.numel(), num_experts))
+    sorted_ids = torch.empty((cap,), dtype=torch.int32, device=ids.device)
+    expert_ids = torch.empty((max(cap // 8, 1),), dtype=torch.int32, device=ids.device)
+    num_post = torch.empty((1,), dtype=torch.int32, device=ids.device)
+    with torch.cuda.device(ids.device):
+        _lib.check(lib.exl3_moe_align(_ptr(ids), ids.numel(), num_experts, _ptr(sorted_ids), cap, _ptr(expert_ids), _ptr(num_post),
+                                      _stream(ids.device)), "exl3_moe_align")
+    return sorted_ids, expert_ids, num_post
+
+
+def gemm_rotated(xf, stack, out, sorted_ids, expert_ids, num_post_padded, slots: int, shard_end: int, codebook: int,
+                 svh=None) -> torch.Tensor:
+    """Grouped product (svh=None: rotated basis, no output transform).  xf = activation fragments of the blocks."""
+    lib = _lib.load()
+    e, nb, kg, _, _, K, _ = stack.shape
+    k, n_total, cap = kg * 128, nb * 128, sorted_ids.numel()
+    ws = _reserve(stack.device, int(lib.exl3_moe_workspace_bytes(cap, n_total)))
+    with torch.cuda.device(stack.device):
+        _lib.check(lib.exl3_moe_gemm(_ptr(xf), _ptr(stack), K, codebook, _ptr(svh), _ptr(sorted_ids), _ptr(expert_ids),
+                                     _ptr(num_post_padded), cap, slots, k, n_total, shard_end, _ptr(out), _ptr(ws), ws.numel(),
+                                     _stream(stack.device)), "exl3_moe_gemm")
+    return out
+
+
+def run_tensors(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block: int, w13, w2, suh13, svh13,
+                suh2, svh2, codebook: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x fp16 | bf16 [T, H]; topk_weights float32 [T, top_k]; topk_ids int32 | int64 [T, top_k]; routing triple from
+    `align` (or the engine's moe_align_block_size with block 8).  -> y [T, H] in x's dtype."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
+    tokens, hidden = x.shape
+    top_k, inter = topk_ids.shape[1], suh2.shape[1]
+    slots = tokens * top_k
+    y = out if out is not None else torch.empty_like(x)
+    if tokens == 0:
+        return y
+    if block != 8:
+        raise RuntimeError(f"the grouped GEMV works on 8-row moe blocks, got block = {block}")
+    dev, st = x.device, _stream(x.device)
+    cap = sorted_ids.numel()
+    ids32 = topk_ids.reshape(-1).to(torch.int32).contiguous()
+    wts = topk_weights.reshape(-1).to(torch.float32).contiguous()
+    xf13 = torch.empty(int(lib.exl3_moe_fragment_bytes(cap, hidden, 2, codebook)), dtype=torch.uint8, device=dev)
+    gu = torch.empty((slots, 2 * inter), dtype=torch.float16, device=dev)
+    xf2 = torch.empty(int(lib.exl3_moe_fragment_bytes(cap, inter, 1, codebook)), dtype=torch.uint8, device=dev)
+    yd = torch.empty((slots, hidden), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.exl3_moe_had_in(_ptr(x), _dtype_code(x), _ptr(suh13), 2, hidden, top_k, slots, _ptr(sorted_ids), cap,
+                                       _ptr(expert_ids), _ptr(num_post_padded), codebook, _ptr(xf13), st), "exl3_moe_had_in")
+    gemm_rotated(xf13, w13, gu, sorted_ids, expert_ids, num_post_padded, slots, inter, codebook, svh13)
+    with torch.cuda.device(dev):
+        _lib.check(lib.exl3_moe_glu_had_in(_ptr(gu), _ptr(suh2), inter, slots, _ptr(sorted_ids), cap, _ptr(expert_ids),
+                                           _ptr(num_post_padded), codebook, _ptr(xf2), st), "exl3_moe_glu_had_in")
+    gemm_rotated(xf2, w2, yd, sorted_ids, expert_ids, num_post_padded, slots, 0, codebook, svh2)
+    with torch.cuda.device(dev):
+        _lib.check(lib.exl3_moe_combine(_ptr(yd), _ptr(wts), _ptr(ids32), tokens, top_k, hidden, w13.shape[0], _ptr(y),
+                                        _dtype_code(y), st), "exl3_moe_combine")
+    return y
+
+
+def run(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block: int, pack: ExpertPack,
+        out: torch.Tensor | None = None) -> torch.Tensor:
+    return run_tensors(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block, *pack.tensors(),
+                       pack.codebook, out)
+
+
+def forward(x, topk_weights, topk_ids, pack: ExpertPack, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Whole layer including the routing alignment."""
+    s, e, p = align(topk_ids, pack.num_experts)
+    return run(x, topk_weights, topk_ids, s, e, p, 8, pack, out)
