@@ -1,0 +1,95 @@
+"""The `linear` operator: one opaque op per fused EXL3 group with every row-count branch, dtype cast, pad and trim
+inside, as the reference's cuda/src/sglang_exl3/runtime/ops.py:62-137 (0xSero/trellis-serve) does for its engines.
+
+Same schema as the reference's custom op (ops.py:133):
+
+    linear(Tensor x, Tensor[] trellis, Tensor[] suh, Tensor[] svh, Tensor[] dense, Tensor[] sliced, int sliced_min_rows,
+           Tensor[] marlin_w, int[] marlin_ends, int[] codebooks, int[] out_widths) -> Tensor
+
+registered as `torch.ops.exl3_b200.linear`, with a fake (meta) implementation so tracing compilers see only shapes.
+`marlin_w` carries the output of `kernels.linear.prepare`: [packed, suh_cat, svh_cat]; `marlin_ends` its shard ends.
+`trellis`, `suh`, `svh` (the stored tensors) are optional here: the resident layout alone serves every path.
+`dense` may hold resident decoded fp16 weights per matrix; `sliced` is accepted for schema compatibility and unused.
+
+Dispatch (there is a single backend, so it collapses to two paths, SURVEY of the reference: ops.py:79-95):
+
+  rows <  DENSE_ROWS        fused decode kernel (weights streamed once per 16 rows)
+  rows >= DENSE_ROWS        many-row path of `dense_group`: one batched input rotation, per matrix decode to fp16
+                            (or the resident `dense` weight) + fp16 GEMM + output rotation into the fused output
+
+x may have any leading dims; a last dim narrower than the stored (128-padded) k is zero-padded (ops.py:98-99) and
+stored output columns beyond the true `out_widths` are dropped (ops.py:122-124).  fp16 / bf16 go through as they are;
+any other dtype is computed in fp16 and cast back.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..kernels import linear as lin
+
+_lib = torch.library.Library("exl3_b200", "FRAGMENT")       # must stay alive at module scope
+
+# Rows from which decode-to-fp16 + GEMM beats streaming the packed weights once per 16 rows.
+DENSE_ROWS = int(os.environ.get("EXL3_B200_DENSE_ROWS", "33"))
+
+
+def dense_group(x: torch.Tensor, packed: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int],
+                codebook: int, out: torch.Tensor, weights: list[torch.Tensor] | None = None) -> torch.Tensor:
+    """Many-row (prefill) path of a fused group, the reference's `dense_group` (ops.py:36-59): ONE batched input
+    rotation for all matrices, per matrix the decoded fp16 weight (resident `weights[i]`, or decoded now from the
+    resident layout) times the rotated rows in an fp16 GEMM with fp32 accumulation, and an output rotation written
+    straight into the matrix's column span of `out` in out's dtype."""
+    rows = x.shape[0]
+    xh = lin.had_in_group(x, suh_cat)
+    bounds = [0, *shard_ends, svh_cat.shape[0]]
+    for i, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):
+        w = weights[i] if weights is not None else lin.reconstruct_packed(packed[a // 128:b // 128], codebook)
+        y = torch.mm(xh[i * rows:(i + 1) * rows], w)
+        del w
+        lin.had_out_into(y, svh_cat[a:b], out, a)
+    return out
+
+
+def _linear(x: torch.Tensor, trellis: list[torch.Tensor], suh: list[torch.Tensor], svh: list[torch.Tensor],
+            dense: list[torch.Tensor], sliced: list[torch.Tensor], sliced_min_rows: int, marlin_w: list[torch.Tensor],
+            marlin_ends: list[int], codebooks: list[int], out_widths: list[int]) -> torch.Tensor:
+    if len(marlin_w) != 3:
+        raise RuntimeError("marlin_w must be [packed, suh_cat, svh_cat] from kernels.linear.prepare")
+    if len(set(codebooks)) != 1:
+        raise RuntimeError("one codebook per fused group")
+    packed, suh_cat, svh_cat = marlin_w
+    ends = list(marlin_ends)
+    k, n_total = packed.shape[1] * 128, packed.shape[0] * 128
+    rows = x.reshape(-1, x.shape[-1])
+    h = rows if rows.dtype in (torch.float16, torch.bfloat16) else rows.to(torch.float16)
+    if h.shape[1] > k:
+        raise RuntimeError(f"input width {h.shape[1]} exceeds the stored width {k}")
+    if h.shape[1] < k:                                   # stored input width is padded to 128
+        h = torch.nn.functional.pad(h, (0, k - h.shape[1]))
+    h = h.contiguous()
+    if h.shape[0] < DENSE_ROWS:
+        y = lin.run(h, packed, suh_cat, svh_cat, ends, codebooks[0])
+    else:
+        y = torch.empty((h.shape[0], n_total), dtype=h.dtype, device=h.device)
+        dense_group(h, packed, suh_cat, svh_cat, ends, codebooks[0], y, list(dense) if dense else None)
+    bounds = [0, *ends, n_total]
+    stored = [b - a for a, b in zip(bounds[:-1], bounds[1:])]
+    if any(w > s for w, s in zip(out_widths, stored)):
+        raise RuntimeError(f"out_widths {list(out_widths)} exceed the stored widths {stored}")
+    if list(out_widths) != stored:                       # stored output columns beyond the true width are dropped
+        y = torch.cat([y[:, a:a + w] for a, w in zip(bounds[:-1], out_widths)], dim=1)
+    return y.to(x.dtype).view(*x.shape[:-1], y.shape[1])
+
+
+def _linear_fake(x, trellis, suh, svh, dense, sliced, sliced_min_rows, marlin_w, marlin_ends, codebooks, out_widths):
+    return x.new_empty((*x.shape[:-1], sum(out_widths)))
+
+
+_lib.define("linear(Tensor x, Tensor[] trellis, Tensor[] suh, Tensor[] svh, Tensor[] dense, Tensor[] sliced, int sliced_min_rows, "
+            "Tensor[] marlin_w, int[] marlin_ends, int[] codebooks, int[] out_widths) -> Tensor")
+_lib.impl("linear", _linear, "CUDA")
+torch.library.register_fake("exl3_b200::linear", _linear_fake, lib=_lib)
+
+linear = torch.ops.exl3_b200.linear
