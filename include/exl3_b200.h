@@ -93,6 +93,17 @@ exl3_status exl3_linear(const void *x, int x_dtype, const uint32_t *packed, int 
                         const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
                         int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- fused linear for many rows (prefill) on the tcgen05 tensor cores -----------------------------------
+ * Same contract as exl3_linear (fused group, dtypes, shard ends); built for hundreds to thousands of rows: the
+ * weights are decoded once per 512 rows straight into the shared-memory operand of tcgen05.mma, accumulators live in
+ * tensor memory.  The reference has no fused many-row kernel; this replaces its decode + library GEMM sequence
+ * `dense_group` (cuda/src/sglang_exl3/runtime/ops.py:36-59).  The workspace (exl3_gemm_tc_workspace_bytes) holds the
+ * rotated activations and the rotated-basis product; its first 256 bytes must be zero (error word). */
+size_t exl3_gemm_tc_workspace_bytes(int rows, int k, int n_total, int n_shards);
+exl3_status exl3_linear_tc(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
+                           const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
+                           int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
 /* The same fused linear for callers that can neither allocate device memory nor carry a workspace around: code
  * running inside another framework's captured or memory-pool-managed region, plugin hooks that only receive the
  * tensors of the call, hosts that hand out device memory once at start-up.  Its scratch is a fixed array of

@@ -1,0 +1,52 @@
+"""GPU parity of the many-row fused GEMM on the tcgen05 tensor cores (exl3_linear_tc) against the oracle's fp32
+forward (relative L2 <= 2e-3, max|d|/rms <= 4e-3: the product is rounded to fp16 before the output rotation, as in
+the reference's many-row path, cuda/src/sglang_exl3/runtime/ops.py:36-59) and against the decode kernel."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import seeded_signs, seeded_trellis
+from oracle import exl3_oracle as orc
+from trellis_serve_b200.kernels import linear as lin
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _t(a):
+    return torch.from_numpy(np.ascontiguousarray(a.view(np.int16) if a.dtype == np.uint16 else a)).to(DEV)
+
+
+@pytest.mark.parametrize("K,cb,k,n,rows", [(4, 1, 256, 256, 130), (3, 0, 512, 384, 512), (4, 1, 1024, 640, 700),
+                                           (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025)])
+def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows):
+    tr, suh, svh = seeded_trellis(K * 7 + cb, k // 16, n // 16, K), seeded_signs(1, k), seeded_signs(2, n)
+    x = np.random.default_rng(rows).standard_normal((rows, k)).astype(np.float16)
+    packed = lin.prepare_matrix(_t(tr))
+    y = lin.run_tc(_t(x), packed, _t(suh).reshape(1, -1), _t(svh), [], cb)
+    torch.cuda.synchronize()
+    lin.device_error(torch.device(DEV))
+    ref = orc.c_linear_forward(x, tr, suh, svh, K, cb)
+    got = y.float().cpu().numpy()
+    assert orc.rel_norm(got, ref) <= 2e-3, orc.rel_norm(got, ref)
+    assert orc.max_over_rms(got, ref) <= 4e-3, orc.max_over_rms(got, ref)
+
+
+def test_fused_group_and_bf16_through_the_tensor_core_path():
+    K, cb, k, ns, rows = 4, 1, 512, [256, 128], 300
+    parts = [(seeded_trellis(80 + i, k // 16, n // 16, K), seeded_signs(81 + i, k), seeded_signs(84 + i, n)) for i, n in enumerate(ns)]
+    b, suh_cat, svh_cat, ends = lin.prepare([_t(p[0]) for p in parts], [_t(p[1]) for p in parts], [_t(p[2]) for p in parts])
+    x = np.random.default_rng(3).standard_normal((rows, k)).astype(np.float16)
+    y = lin.run_tc(_t(x).to(torch.bfloat16), b, suh_cat, svh_cat, ends, cb)
+    assert y.dtype == torch.bfloat16
+    xb = _t(x).to(torch.bfloat16).to(torch.float16).cpu().numpy()
+    col = 0
+    for (tr, suh, svh), n in zip(parts, ns):
+        ref = orc.c_linear_forward(xb, tr, suh, svh, K, cb)
+        assert orc.rel_norm(y[:, col:col + n].float().cpu().numpy(), ref) <= 6e-3          # bf16 output
+        col += n
+    y16 = lin.run_tc(_t(x), b, suh_cat, svh_cat, ends, cb)
+    dec = lin.run(_t(x), b, suh_cat, svh_cat, ends, cb)
+    assert orc.rel_norm(y16.float().cpu().numpy(), dec.float().cpu().numpy()) <= 2e-3     # same answer as the decode kernel

@@ -34,6 +34,8 @@ SIGNATURES = {
     "exl3_had_out": (_i, [_vp, _i, _vp, _i, _i, _vp, _i64, _i, _vp]),
     "exl3_linear_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_linear": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "exl3_gemm_tc_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "exl3_linear_tc": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "exl3_linear_static": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp]),
     "exl3_static_workspace_bytes": (_sz, []),
     "exl3_gemm_rotated": (_i, [_vp, _vp, _i, _i, _ip, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),

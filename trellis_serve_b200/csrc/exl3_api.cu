@@ -254,6 +254,40 @@ exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* str
     return EXL3_ERR_DEVICE_WAIT;
 }
 
+/* ---- many-row (prefill) fused GEMM on tcgen05 ------------------------------------------------------------- */
+
+static size_t tc_up(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t exl3_gemm_tc_workspace_bytes(int rows, int k, int n_total, int n_shards)
+{
+    if (rows < 0 || k < 0 || n_total < 0 || n_shards < 1) return 0;
+    return 256 + tc_up(gemm_tc_activation_bytes(rows, k, n_shards)) + tc_up((size_t)rows * n_total * sizeof(__half));
+}
+
+exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat,
+                           const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y,
+                           int y_dtype, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
+    if (rows < 0) return EXL3_ERR_BAD_SHAPE;
+    GemvArgs a;
+    memset(&a, 0, sizeof(a));
+    if (int rc = fill_shards(a, shard_ends, n_shards, n_total)) return rc;
+    if ((x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) || (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16)) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
+    if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
+    if (!aligned(x, 2) || !aligned(packed, 16) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8) || !aligned(y, 8)) return EXL3_ERR_BAD_POINTER;
+    if (!aligned(workspace, 256) || workspace_bytes < exl3_gemm_tc_workspace_bytes(rows, k, n_total, n_shards)) return EXL3_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+    __half* xa = reinterpret_cast<__half*>(ws + 256);
+    __half* rot = reinterpret_cast<__half*>(ws + 256 + tc_up(gemm_tc_activation_bytes(rows, k, n_shards)));
+    if (int rc = launch_gemm_tc(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), packed, K, codebook, a.shard_end_blocks,
+                                n_shards, rows, k, n_total, xa, rot, reinterpret_cast<int*>(ws), st))
+        return rc;
+    return launch_had_out(rot, 0, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y, n_total, y_dtype == EXL3_BF16, st);
+}
+
 /* ---- MoE ------------------------------------------------------------------------------------------------------ */
 
 namespace exl3 {

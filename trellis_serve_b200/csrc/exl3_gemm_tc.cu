@@ -1,0 +1,381 @@
+// Prefill GEMM of the EXL3 linear on the 5th-generation tensor cores (sm_100a): out = Xh @ W_inner for many rows,
+// with the weights decoded from the resident trellis straight into the shared-memory operand of tcgen05.mma.
+//
+// The reference has no fused many-row kernel: it materialises the fp16 weight and calls a library GEMM
+// (cuda/src/sglang_exl3/runtime/ops.py:36-59 of 0xSero/trellis-serve).  Here one persistent CTA per SM owns an output
+// tile of 512 rows x 128 columns at a time and walks the reduction dimension in blocks of 64:
+//
+//   warps 0-7   decode: warp w decodes column tile w of the 64 x 128 weight block from the resident layout (register
+//               level decode of exl3_decode.cuh, weights rounded to fp16 exactly as the reference decoder) and stores
+//               it K-major, in 8x8 core matrices, as the B operand; after the main loop the same warps read the
+//               accumulators back from tensor memory (tcgen05.ld) and store fp16 rows
+//   warp 8      A producer: one 64 KB bulk async copy per stage; the rotated activations are laid out in global
+//               memory by had_in_tc_kernel exactly as the A operand wants them (four 128 x 64 K-major tiles)
+//   warp 9      allocates tensor memory (512 columns = four 128 x 128 fp32 accumulators), issues
+//               tcgen05.mma.cta_group::1.kind::f16 (M 128, N 128, K 16) from one elected lane and commits to the
+//               mbarriers that release the stage / publish the accumulators
+//
+// Each weight block is decoded once per 512 rows and reused by 16 MMAs, so the kernel is bound by the tensor pipe,
+// not by the decode.  Every wait is bounded (exl3_ptx.cuh); on a time-out the error word is set and the control flow
+// continues unchanged to the common exit, where tensor memory is released.
+#include "exl3_internal.h"
+#include "exl3_ptx.cuh"
+
+namespace exl3 {
+
+constexpr int TC_M_TILES = 4;                 // 128-row accumulators per CTA tile
+constexpr int TC_ROWS = 128 * TC_M_TILES;     // 512
+constexpr int TC_KB = 64;                     // reduction block
+constexpr int TC_STAGES = 2;
+constexpr int TC_DECODE_WARPS = 8;
+constexpr int TC_THREADS = (TC_DECODE_WARPS + 2) * 32;
+constexpr uint32_t TC_A_TILE_BYTES = 128 * TC_KB * 2;                 // 16 KB
+constexpr uint32_t TC_A_STAGE_BYTES = TC_A_TILE_BYTES * TC_M_TILES;   // 64 KB
+constexpr uint32_t TC_B_STAGE_BYTES = 128 * TC_KB * 2;                // 16 KB
+constexpr uint32_t TC_STAGE_BYTES = TC_A_STAGE_BYTES + TC_B_STAGE_BYTES;
+constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES;
+
+enum { TC_ERR_WAIT = 3 };
+
+struct GemmTcLaunch {
+    const uint32_t* packed;      // resident weights [NB][KG][8][2][K][32]
+    const __half* xa;            // rotated activations in A-operand layout [MS][k/64][4][8][16][8][8]
+    __half* out;                 // [rows][n_total] fp16, rotated basis
+    int* err;
+    int rows, KG, NB, MS;        // MS = ceil(rows / 512)
+    int n_total;
+    int shard_end_block[GEMV_MAX_SHARDS];
+    int n_shards;
+    long long xa_shard_stride;   // halves between shards
+    uint32_t mul, add;
+    Pow2 pw;
+};
+
+// Operand layout shared by A tiles and the B block: 8 x 8 fp16 core matrices of 128 contiguous bytes, core (c, j) =
+// (k chunk of 8, row group of 8) at (c * 16 + j) * 128 bytes: 2048 bytes between k chunks, 128 between row groups.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_byte_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_byte_addr >> 4) & 0x3FFF);          // start address
+    d |= (uint64_t)(2048 >> 4) << 16;                         // leading byte offset: between the two k chunks of an MMA
+    d |= (uint64_t)(128 >> 4) << 32;                          // stride byte offset: between 8-row groups
+    d |= 1ull << 46;                                          // descriptor version of this architecture
+    return d;                                                 // layout type 0: no swizzle
+}
+
+// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = 128
+constexpr uint32_t TC_IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(TC_IDESC), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ptx::smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int K, int FAM>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
+{
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* a_full = reinterpret_cast<uint64_t*>(smem);            // [stages]
+    uint64_t* b_full = a_full + TC_STAGES;
+    uint64_t* empty = b_full + TC_STAGES;
+    uint64_t* acc_full = empty + TC_STAGES;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    unsigned char* stage0 = smem + 1024;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            ptx::mbar_init(&a_full[s], 1);
+            ptx::mbar_init(&b_full[s], TC_DECODE_WARPS);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, TC_DECODE_WARPS);
+        ptx::mbar_fence_init();
+    }
+    if (warp == TC_DECODE_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_addr(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int KB = p.KG * 2;                           // reduction blocks of 64
+    const long long n_tiles = (long long)p.MS * p.NB;
+    bool failed = false;
+    auto fail = [&]() {
+        if (!failed) {
+            failed = true;
+            atomicExch(p.err, TC_ERR_WAIT);
+        }
+    };
+
+    if (warp < TC_DECODE_WARPS) {
+        // ------------------------------------------------------------------ decode + epilogue
+        const int nt = warp, g = lane >> 2, q = lane & 3;
+        const CodebookConst cbc = {p.mul, p.add};
+        uint32_t it = 0, acc_round = 0;
+        for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+            const int ms = (int)(t % p.MS), nb = (int)(t / p.MS);
+            for (int kb = 0; kb < KB; kb++, it++) {
+                const int s = it % TC_STAGES;
+                const uint32_t round = it / TC_STAGES;
+                const int kg = kb >> 1, kq = kb & 1;
+                uint32_t L[K];
+                const uint32_t* src = p.packed + (((((long long)nb * p.KG + kg) * 8 + nt) * 2 + kq) * K) * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < K; i++) L[i] = __ldg(src + i * 32);
+                if (round > 0 && !failed && !ptx::mbar_wait(&empty[s], (round - 1) & 1)) fail();
+                unsigned char* bst = stage0 + (size_t)s * TC_STAGE_BYTES + TC_A_STAGE_BYTES;
+                auto tile = [&](auto tconst) {
+                    constexpr int T = decltype(tconst)::value;
+                    uint32_t own[2];
+                    own_words<K, T>(L, own);
+                    const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
+                    const LaneRegs<K> R = lane_regs<K>(own, prev0);
+                    uint32_t st[8];
+                    st[0] = window_mul<K, 0>(R, p.pw); st[1] = window_mul<K, 1>(R, p.pw); st[2] = window_mul<K, 2>(R, p.pw);
+                    st[3] = window_mul<K, 3>(R, p.pw); st[4] = window_mul<K, 4>(R, p.pw); st[5] = window_mul<K, 5>(R, p.pw);
+                    st[6] = window_mul<K, 6>(R, p.pw); st[7] = window_mul<K, 7>(R, p.pw);
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        w[j] = FAM == FAM_HASH ? hash_pair_rounded(st[2 * j], st[2 * j + 1], cbc) : mul1_pair(st[2 * j], st[2 * j + 1], cbc);
+                    // pair j: k chunk 2T + (j & 1), column group 2nt + (j >> 1), row g of the core matrix, bytes 4q..4q+3
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int c = 2 * T + (j & 1), jn = 2 * nt + (j >> 1);
+                        *reinterpret_cast<uint32_t*>(bst + (c * 16 + jn) * 128 + g * 16 + q * 4) = w[j];
+                    }
+                };
+                tile(std::integral_constant<int, 0>{});
+                tile(std::integral_constant<int, 1>{});
+                tile(std::integral_constant<int, 2>{});
+                tile(std::integral_constant<int, 3>{});
+                fence_async_smem();                     // generic-proxy stores -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&b_full[s]);
+            }
+            // ---- epilogue of this tile: accumulators -> fp16 rows
+            if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
+            tc_fence_after();
+            const int quarter = warp & 3, half = warp >> 2;
+#pragma unroll 1
+            for (int mt = 0; mt < TC_M_TILES; mt++) {
+                const int row = ms * TC_ROWS + mt * 128 + quarter * 32 + lane;
+#pragma unroll 1
+                for (int cc = 0; cc < 2; cc++) {
+                    const int col = half * 64 + cc * 32;
+                    uint32_t r[32];
+                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * 128 + col), r);
+                    if (row < p.rows) {
+                        __half* dst = p.out + (size_t)row * p.n_total + nb * 128 + col;
+#pragma unroll
+                        for (int v = 0; v < 32; v += 8) {
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(__uint_as_float(r[v]), __uint_as_float(r[v + 1]));
+                            __half2 h1 = __floats2half2_rn(__uint_as_float(r[v + 2]), __uint_as_float(r[v + 3]));
+                            __half2 h2 = __floats2half2_rn(__uint_as_float(r[v + 4]), __uint_as_float(r[v + 5]));
+                            __half2 h3 = __floats2half2_rn(__uint_as_float(r[v + 6]), __uint_as_float(r[v + 7]));
+                            o.x = *reinterpret_cast<uint32_t*>(&h0);
+                            o.y = *reinterpret_cast<uint32_t*>(&h1);
+                            o.z = *reinterpret_cast<uint32_t*>(&h2);
+                            o.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(dst + v) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty);
+            acc_round++;
+        }
+    } else if (warp == TC_DECODE_WARPS) {
+        // ------------------------------------------------------------------ A producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                const int ms = (int)(t % p.MS), nb = (int)(t / p.MS);
+                int shard = 0;
+                while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
+                for (int kb = 0; kb < KB; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t round = it / TC_STAGES;
+                    if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
+                    const __half* src = p.xa + shard * p.xa_shard_stride + ((long long)ms * KB + kb) * (TC_A_STAGE_BYTES / 2);
+                    ptx::mbar_arrive_expect_tx(&a_full[s], TC_A_STAGE_BYTES);
+                    ptx::bulk_g2s(stage0 + (size_t)s * TC_STAGE_BYTES, src, TC_A_STAGE_BYTES, &a_full[s]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            uint32_t it = 0, acc_round = 0;
+            for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                if (acc_round > 0 && !failed && !ptx::mbar_wait(acc_empty, (acc_round - 1) & 1)) fail();
+                tc_fence_after();
+                for (int kb = 0; kb < KB; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t round = it / TC_STAGES;
+                    if (!failed && !ptx::mbar_wait(&a_full[s], round & 1)) fail();
+                    if (!failed && !ptx::mbar_wait(&b_full[s], round & 1)) fail();
+                    tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_addr(stage0 + (size_t)s * TC_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TC_A_STAGE_BYTES;
+#pragma unroll
+                    for (int mt = 0; mt < TC_M_TILES; mt++)
+#pragma unroll
+                        for (int ks = 0; ks < TC_KB / 16; ks++)
+                            tc_mma(tmem_base + (uint32_t)(mt * 128), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096),
+                                   tc_smem_desc(b_addr + ks * 4096), (kb > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(&empty[s]);               // stage reusable once these MMAs have read it
+                }
+                tc_commit(acc_full);                    // accumulators complete
+                acc_round++;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_DECODE_WARPS + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// Rotated activations in the A-operand layout of gemm_tc_kernel.  One warp per (shard, row, 128-block); rows beyond
+// `rows` up to the next multiple of 512 must have been zero-filled by the caller.
+__global__ void had_in_tc_kernel(const void* __restrict__ x, int x_bf16, const __half* __restrict__ suh, int shards, int rows, int k,
+                                 __half* __restrict__ xa, long long shard_stride)
+{
+    const int lane = threadIdx.x & 31;
+    const int kgs = k >> 7;
+    const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)shards * rows * kgs) return;
+    const int kg = (int)(item % kgs);
+    const int row = (int)((item / kgs) % rows);
+    const int s = (int)(item / ((long long)kgs * rows));
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const int col = kg * 128 + 4 * lane + e;
+        float xv = x_bf16 ? __half2float(__float2half_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[(long long)row * k + col])))
+                          : __half2float(reinterpret_cast<const __half*>(x)[(long long)row * k + col]);
+        v[e] = xv * __half2float(suh[(long long)s * k + col]);
+    }
+    fwht128(v[0], v[1], v[2], v[3], lane);
+    __half h[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) h[e] = __float2half_rn(v[e] * HAD_SCALE);
+    const int kk = 4 * lane;                               // column inside the 128 block
+    const int kb = kg * 2 + (kk >> 6), c = (kk & 63) >> 3, e0 = kk & 7;
+    const int ms = row / TC_ROWS, mt = (row % TC_ROWS) >> 7, j = (row & 127) >> 3, rr = row & 7;
+    const long long KB = (long long)kgs * 2;
+    const long long off = ((((((long long)ms * KB + kb) * TC_M_TILES + mt) * 8 + c) * 16 + j) * 8 + rr) * 8 + e0;
+    *reinterpret_cast<uint2*>(xa + s * shard_stride + off) = *reinterpret_cast<uint2*>(h);
+}
+
+template <int K>
+static int launch_tc_k(const GemmTcLaunch& l, int fam, int grid, cudaStream_t st)
+{
+    if (fam == FAM_HASH) {
+        static bool attr_hash = false;
+        if (!attr_hash) {
+            if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_HASH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES))) return rc;
+            attr_hash = true;
+        }
+        gemm_tc_kernel<K, FAM_HASH><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(l);
+    } else {
+        static bool attr_mul1 = false;
+        if (!attr_mul1) {
+            if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_MUL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES))) return rc;
+            attr_mul1 = true;
+        }
+        gemm_tc_kernel<K, FAM_MUL1><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(l);
+    }
+    return cuda_status(cudaGetLastError());
+}
+
+size_t gemm_tc_activation_bytes(int rows, int k, int shards)
+{
+    const size_t ms = (size_t)(rows + TC_ROWS - 1) / TC_ROWS;
+    return (size_t)shards * ms * TC_ROWS * k * sizeof(__half);
+}
+
+// xa: gemm_tc_activation_bytes() of scratch.  out: [rows][n_total] fp16 in the rotated basis.
+int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, int* err, cudaStream_t st)
+{
+    const DeviceInfo* d = current_device_info();
+    if (!d) return EXL3_ERR_NOT_INITIALISED;
+    GemmTcLaunch l;
+    l.packed = packed;
+    l.xa = xa;
+    l.out = out;
+    l.err = err;
+    l.rows = rows;
+    l.KG = k / 128;
+    l.NB = n_total / 128;
+    l.MS = (rows + TC_ROWS - 1) / TC_ROWS;
+    l.n_total = n_total;
+    l.n_shards = n_shards;
+    for (int s = 0; s < GEMV_MAX_SHARDS; s++) l.shard_end_block[s] = shard_end_blocks[s];
+    l.xa_shard_stride = (long long)l.MS * TC_ROWS * k;
+    const CodebookConst c = codebook_const(codebook);
+    l.mul = c.mul;
+    l.add = c.add;
+    for (int i = 0; i <= 16; i++) l.pw.v[i] = 1u << i;
+    if (int rc = cuda_status(cudaMemsetAsync(xa, 0, gemm_tc_activation_bytes(rows, k, n_shards), st))) return rc;
+    const long long items = (long long)n_shards * rows * (k / 128);
+    had_in_tc_kernel<<<(unsigned)((items + 7) / 8), 256, 0, st>>>(x, x_bf16, suh_cat, n_shards, rows, k, xa, l.xa_shard_stride);
+    if (int rc = cuda_status(cudaGetLastError())) return rc;
+    const long long tiles = (long long)l.MS * l.NB;
+    int grid = d->sm_count;
+    if (tiles < grid) grid = (int)tiles;
+    const int fam = codebook_family(codebook);
+    switch (K) {
+        case 2: return launch_tc_k<2>(l, fam, grid, st);
+        case 3: return launch_tc_k<3>(l, fam, grid, st);
+        case 4: return launch_tc_k<4>(l, fam, grid, st);
+        case 5: return launch_tc_k<5>(l, fam, grid, st);
+        case 6: return launch_tc_k<6>(l, fam, grid, st);
+        case 7: return launch_tc_k<7>(l, fam, grid, st);
+        case 8: return launch_tc_k<8>(l, fam, grid, st);
+    }
+    return EXL3_ERR_UNSUPPORTED_K;
+}
+
+}  // namespace exl3

@@ -81,6 +81,11 @@ int launch_moe_glu_had_in(const __half* gu, const __half* suh2, int inter, int n
 int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, int tokens, int top_k, int hidden, int E, void* y,
                        int y_bf16, cudaStream_t st);
 
+// exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
+size_t gemm_tc_activation_bytes(int rows, int k, int shards);
+int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, int* err, cudaStream_t st);
+
 // Workspace carved up identically by every entry point that takes one.
 struct WorkspaceLayout {
     size_t err_off, counters_off, xf_off, partials_off, total;

@@ -45,7 +45,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 }
 
 // Bounded wait: about a second of polling at most, then gives up.
-constexpr uint32_t MBAR_MAX_POLLS = 1u << 20;
+constexpr uint32_t MBAR_MAX_POLLS = 1u << 16;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {

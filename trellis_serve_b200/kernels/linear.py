@@ -24,6 +24,7 @@ from .base import BackendStatus
 
 MAX_ROWS = 64            # rows the per-device workspace is sized for at load time (marlin.py:24-27)
 _workspace: dict[int, torch.Tensor] = {}
+_tc_workspace: dict[int, torch.Tensor] = {}
 
 
 def _dtype_code(t: torch.Tensor, allow_f32: bool = False) -> int:
@@ -167,6 +168,31 @@ def run(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.
         _lib.check(lib.exl3_linear(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
                                    _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(y), _dtype_code(y, True),
                                    _ptr(ws), ws.numel(), _stream(x.device)), "exl3_linear")
+    return y
+
+
+def run_tc(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int],
+           codebook: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Many-row version of `run` on the tcgen05 tensor cores: weights decoded once per 512 rows into the MMA operand."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
+    _lib.init_device(x.device.index if x.device.index is not None else torch.cuda.current_device())
+    rows, kx = x.shape
+    k, n_total, K = _geometry(b)
+    if kx != k:
+        raise RuntimeError(f"x has width {kx}, the packed weights expect {k}")
+    shards = len(shard_ends) + 1
+    y = out if out is not None else torch.empty((rows, n_total), dtype=x.dtype, device=x.device)
+    if rows == 0:
+        return y
+    need = int(lib.exl3_gemm_tc_workspace_bytes(rows, k, n_total, shards))
+    ws = _tc_workspace.get(x.device.index)
+    if ws is None or ws.numel() < need:
+        ws = _tc_workspace[x.device.index] = torch.zeros(need, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.exl3_linear_tc(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
+                                      _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(y), _dtype_code(y), _ptr(ws),
+                                      ws.numel(), _stream(x.device)), "exl3_linear_tc")
     return y
 
 
