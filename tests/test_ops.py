@@ -54,7 +54,10 @@ def test_prefill_path_agrees_with_the_decode_path(monkeypatch):
     monkeypatch.setattr(ops, "DENSE_ROWS", 10 ** 9)
     decode = ops.linear(x, [], [], [], [], [], 0, w, ends, [cb], ns).float()
     monkeypatch.setattr(ops, "DENSE_ROWS", 1)
-    prefill = ops.linear(x, [], [], [], [], [], 0, w, ends, [cb], ns).float()
+    fused = ops.linear(x, [], [], [], [], [], 0, w, ends, [cb], ns).float()           # tcgen05 kernel
+    assert orc.rel_norm(fused.cpu().numpy(), decode.cpu().numpy()) <= 2e-3
+    monkeypatch.setattr(ops, "PREFILL", "library")
+    prefill = ops.linear(x, [], [], [], [], [], 0, w, ends, [cb], ns).float()         # decode + library GEMM
     assert orc.rel_norm(prefill.cpu().numpy(), decode.cpu().numpy()) <= 2e-3
     from trellis_serve_b200.kernels import linear as lin
     resident = [lin.reconstruct_packed(w[0], cb)]

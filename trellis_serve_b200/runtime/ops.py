@@ -14,8 +14,10 @@ registered as `torch.ops.exl3_b200.linear`, with a fake (meta) implementation so
 Dispatch (there is a single backend, so it collapses to two paths, SURVEY of the reference: ops.py:79-95):
 
   rows <  DENSE_ROWS        fused decode kernel (weights streamed once per 16 rows)
-  rows >= DENSE_ROWS        many-row path of `dense_group`: one batched input rotation, per matrix decode to fp16
-                            (or the resident `dense` weight) + fp16 GEMM + output rotation into the fused output
+  rows >= DENSE_ROWS        many-row path: the fused tcgen05 kernel (`kernels.linear.run_tc`: weights decoded once per
+                            512 rows into the tensor-core operand); when resident decoded weights are passed in `dense`,
+                            `dense_group` instead (batched input rotation, library fp16 GEMM on the resident weight,
+                            output rotation), which is the reference's many-row sequence
 
 x may have any leading dims; a last dim narrower than the stored (128-padded) k is zero-padded (ops.py:98-99) and
 stored output columns beyond the true `out_widths` are dropped (ops.py:122-124).  fp16 / bf16 go through as they are;
@@ -33,6 +35,8 @@ _lib = torch.library.Library("exl3_b200", "FRAGMENT")       # must stay alive at
 
 # Rows from which decode-to-fp16 + GEMM beats streaming the packed weights once per 16 rows.
 DENSE_ROWS = int(os.environ.get("EXL3_B200_DENSE_ROWS", "33"))
+# "tc": fused tcgen05 kernel; "library": decode to fp16 + library GEMM (the reference's sequence), for comparisons.
+PREFILL = os.environ.get("EXL3_B200_PREFILL", "tc")
 
 
 def dense_group(x: torch.Tensor, packed: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int],
@@ -71,9 +75,11 @@ def _linear(x: torch.Tensor, trellis: list[torch.Tensor], suh: list[torch.Tensor
     h = h.contiguous()
     if h.shape[0] < DENSE_ROWS:
         y = lin.run(h, packed, suh_cat, svh_cat, ends, codebooks[0])
-    else:
+    elif dense or PREFILL == "library":
         y = torch.empty((h.shape[0], n_total), dtype=h.dtype, device=h.device)
         dense_group(h, packed, suh_cat, svh_cat, ends, codebooks[0], y, list(dense) if dense else None)
+    else:
+        y = lin.run_tc(h, packed, suh_cat, svh_cat, ends, codebooks[0])
     bounds = [0, *ends, n_total]
     stored = [b - a for a, b in zip(bounds[:-1], bounds[1:])]
     if any(w > s for w, s in zip(out_widths, stored)):
