@@ -10,8 +10,19 @@ namespace exl3 {
 template <int K, int MODE, int FAM, int MB>
 static int launch_one(const GemvLaunch& l, size_t smem, cudaStream_t st)
 {
-    gemv_kernel<K, MODE, FAM, MB><<<l.grid, GEMV_THREADS, smem, st>>>(l);
-    return cuda_status(cudaGetLastError());
+    // Launched with programmatic stream serialization: its prologue and weight copies overlap the tail of the kernel
+    // ahead of it; the kernel itself waits (griddepcontrol.wait) before touching anything that kernel wrote.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(l.grid);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&cfg, gemv_kernel<K, MODE, FAM, MB>, l));
 }
 
 template <int K, int MODE, int FAM, int MB>

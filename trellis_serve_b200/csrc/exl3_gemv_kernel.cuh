@@ -100,8 +100,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     }
     __syncthreads();
 
+    ptx::grid_launch_dependents();             // the next kernel in the stream may begin its prologue
     if (warp == GEMV_CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer
+        // Weights are constants: their copies start before the kernel ahead of this one has finished.
         // One bulk copy per stage and stages of several units: the copy engine has a fixed cost of a few hundred
         // nanoseconds per bulk copy, so small copies cap the stream far below HBM speed.  The CTA's units are
         // contiguous in memory, so a stage is simply the next `units_per_stage` units.  One thread issues the
@@ -129,6 +131,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     }
 
     // ---------------------------------------------------------------------- consumers
+    // Everything below reads or writes memory other kernels write (activation fragments, workspace, output).
+    ptx::grid_dependency_wait();
     const int nt = warp & 7, kq = warp >> 3;
     const int g = lane >> 2, q = lane & 3;
     const CodebookConst cbc = {p.mul, p.add};

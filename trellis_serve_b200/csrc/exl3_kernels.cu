@@ -140,6 +140,9 @@ __global__ void reconstruct_packed_kernel(const uint32_t* __restrict__ packed, _
 
 // ------------------------------------------------------------------------------------------------ Hadamard
 
+__device__ __forceinline__ void ptx_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ptx_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float load_as_f16_value(const void* p, long long idx, bool bf16)
 {
     // bf16 inputs are first converted to fp16 (round to nearest even, overflow to +-inf), the value
@@ -161,6 +164,8 @@ template <int MODE>
 __global__ void had_in_kernel(const void* __restrict__ x, int x_bf16, const __half* __restrict__ suh, int shards, int rows, int k,
                               void* __restrict__ out)
 {
+    ptx_grid_launch_dependents();              // the GEMV behind this kernel may start streaming weights already
+    ptx_grid_dependency_wait();                // x may be the output of the kernel ahead
     const int lane = threadIdx.x & 31;
     const int kgs = k >> 7;
     long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -333,11 +338,19 @@ int launch_had_in(const void* x, int x_bf16, const __half* suh, int shards, int 
 {
     long long items = (long long)shards * rows * (k / 128);
     if (items == 0) return EXL3_OK;
-    unsigned grid = blocks_for(items, 8);
-    if (mode == 0) had_in_kernel<0><<<grid, 256, 0, st>>>(x, x_bf16, suh, shards, rows, k, out);
-    else if (mode == 1) had_in_kernel<1><<<grid, 256, 0, st>>>(x, x_bf16, suh, shards, rows, k, out);
-    else had_in_kernel<2><<<grid, 256, 0, st>>>(x, x_bf16, suh, shards, rows, k, out);
-    return cuda_status(cudaGetLastError());
+    // programmatic stream serialization: see the GEMV launcher
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks_for(items, 8));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (mode == 0) return cuda_status(cudaLaunchKernelEx(&cfg, had_in_kernel<0>, x, x_bf16, suh, shards, rows, k, out));
+    if (mode == 1) return cuda_status(cudaLaunchKernelEx(&cfg, had_in_kernel<1>, x, x_bf16, suh, shards, rows, k, out));
+    return cuda_status(cudaLaunchKernelEx(&cfg, had_in_kernel<2>, x, x_bf16, suh, shards, rows, k, out));
 }
 
 int launch_to_fragments(const __half* xh, int shards, int rows, int k, uint32_t* out, int mode, cudaStream_t st)

@@ -74,6 +74,12 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
                  : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start before
+// the kernel ahead of it in the stream has finished.  `grid_dependency_wait` blocks until that kernel has completed
+// and its writes are visible; `grid_launch_dependents` lets the next kernel in the stream start its own prologue.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
