@@ -159,6 +159,8 @@ def main() -> None:
     ap.add_argument("--bits", type=int, default=3)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="exchange step of row-parallel layers at N > 1: the library's one-shot peer-memory kernel, or NCCL")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -182,7 +184,11 @@ def main() -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     K, cb = args.bits, 0
-    ls = DecodeLayerSet(args.layers, K, cb, args.rows, tp_rank=rank, tp_size=world, device=dev)
+    reducer = None
+    if world > 1 and args.allreduce == "peer":
+        from trellis_serve_b200.runtime.allreduce import PeerAllReduce
+        reducer = PeerAllReduce(dev, 16 * 5120)
+    ls = DecodeLayerSet(args.layers, K, cb, args.rows, tp_rank=rank, tp_size=world, device=dev, allreduce=reducer)
     gen = torch.Generator(device=dev)
     gen.manual_seed(7 + rank)
     for buf in (ls.x_hidden, ls.x_attn, ls.x_ffn):
@@ -207,6 +213,8 @@ def main() -> None:
         barrier()
     ms_total = start.elapsed_time(stop)
     lin.device_error(dev)
+    if reducer is not None:
+        reducer.check()
 
     # ---- end to end: pinned host inputs -> device, step, result -> host, every step
     hx = [torch.randn(b.shape).to(b.dtype).pin_memory() for b in (ls.x_hidden, ls.x_attn, ls.x_ffn)]
@@ -245,7 +253,8 @@ def main() -> None:
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
                 "data": "synthetic",
                 "config": {"workload": WORKLOAD, "layers": args.layers, "bits": K, "codebook": "3inst", "rows": args.rows,
-                           "parallelism": f"tp{world}", "l2": "inputs larger than L2, no flush",
+                           "parallelism": f"tp{world}", "allreduce": (args.allreduce if world > 1 else None),
+                           "l2": "inputs larger than L2, no flush",
                            "packed_bytes_per_step": total_bytes},
                 "tok_s": 1e3 / ms_step,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

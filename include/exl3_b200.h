@@ -129,6 +129,21 @@ exl3_status exl3_gemm_rotated(const uint16_t *xh, const uint32_t *packed, int K,
                               int n_shards, int rows, int k, int n_total, uint16_t *out, void *workspace,
                               size_t workspace_bytes, void *stream);
 
+/* ---- tensor-parallel exchange step -------------------------------------------------------------------------
+ * Row-parallel shards (o_proj, down_proj) produce partial sums (core/src/trellis_core/format/geometry.py:62-66); this
+ * adds them over the ranks of one node, in place, with one latency-bound kernel over peer-mapped memory (ordinary peer
+ * loads and stores over NVLink, no multicast).  The reference itself has no collective (tensor parallelism is refused
+ * at cuda/src/sglang_exl3/sglang_glue/linear.py:74-75).
+ *   peer_regions (host array of `world` device pointers): every rank's symmetric region of
+ *     exl3_allreduce_region_bytes(max_elems) bytes, zero-filled once, mapped into this process (peer_regions[rank] is
+ *     this rank's own); state: 2 ints of this rank's device memory, zero-filled once (call counter, error word).
+ *   data: n fp16 / bf16 values (n % 8 == 0, n <= max_elems), summed in fp32 in rank order: every rank gets the same bits.
+ * All ranks must make the same sequence of calls.  A peer that never arrives ends the bounded wait with a non-zero
+ * state[1] instead of a hang. */
+size_t exl3_allreduce_region_bytes(size_t max_elems);
+exl3_status exl3_allreduce(void *data, int dtype, size_t n, void *const *peer_regions, int rank, int world, size_t max_elems,
+                           int *state, void *stream);
+
 /* ---- MoE layer (routed experts) ------------------------------------------------------------------------
  * One layer = align -> had_in (gate, up) -> grouped GEMV gate|up -> glu_had_in -> grouped GEMV down -> combine, the
  * launch structure of cuda/src/sglang_exl3/kernels/marlin_moe.py:272-294.  Slots are (token, k) pairs, slot = t*top_k+j.

@@ -1,0 +1,74 @@
+"""Two-GPU test of the one-shot peer-memory all-reduce (skipped with fewer than two devices): every rank must get
+exactly the fp32 rank-order sum of all ranks' inputs, call after call, also under CUDA-graph replay."""
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from trellis_serve_b200.runtime.allreduce import PeerAllReduce
+    ar = PeerAllReduce(dev, 16 * 5120)
+    gen = torch.Generator(device=dev)
+    for call, (rows, dtype) in enumerate([(1, torch.float16), (3, torch.float16), (16, torch.bfloat16), (1, torch.float16)]):
+        gen.manual_seed(100 * call + rank)
+        x = torch.randn((rows, 5120), device=dev, generator=gen).to(dtype)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        want = sum(p.float() for p in parts).to(dtype)                      # fp32 sum in rank order, one rounding
+        got = ar(x.clone())
+        torch.cuda.synchronize()
+        ar.check()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (rank, call)
+    # CUDA-graph replay: the call counter lives on the device, so a replay is a new call
+    buf = torch.zeros((1, 5120), dtype=torch.float16, device=dev)
+    src = torch.zeros_like(buf)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        buf.copy_(src)
+        ar(buf)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        buf.copy_(src)
+        ar(buf)
+    for it in range(3):
+        src.fill_(float(rank + 1 + it))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.all(buf == float(sum(r + 1 + it for r in range(world)))), (rank, it)
+    ar.check()
+    open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_get_the_same_exact_sum(tmp_path):
+    ctx = mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=False)
+    ctx.join(timeout=150)
+    for p in ctx.processes:
+        if p.is_alive():
+            p.kill()
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

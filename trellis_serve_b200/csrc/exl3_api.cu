@@ -288,6 +288,22 @@ exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, i
     return launch_had_out(rot, 0, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y, n_total, y_dtype == EXL3_BF16, st);
 }
 
+/* ---- tensor-parallel exchange step ------------------------------------------------------------------------ */
+
+size_t exl3_allreduce_region_bytes(size_t max_elems) { return allreduce_region_bytes(max_elems); }
+
+exl3_status exl3_allreduce(void* data, int dtype, size_t n, void* const* peer_regions, int rank, int world, size_t max_elems, int* state,
+                           void* stream)
+{
+    if (world < 1 || world > 16 || rank < 0 || rank >= world || n > max_elems || (n % 8)) return EXL3_ERR_BAD_SHAPE;
+    if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (n == 0 || world == 1) return EXL3_OK;
+    if (!aligned(data, 16) || peer_regions == nullptr || !aligned(state, 8)) return EXL3_ERR_BAD_POINTER;
+    for (int r = 0; r < world; r++)
+        if (!aligned(peer_regions[r], 256)) return EXL3_ERR_BAD_POINTER;
+    return launch_allreduce(data, dtype == EXL3_BF16, n, peer_regions, rank, world, max_elems, state, (cudaStream_t)stream);
+}
+
 /* ---- MoE ------------------------------------------------------------------------------------------------------ */
 
 namespace exl3 {

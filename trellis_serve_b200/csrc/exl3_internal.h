@@ -86,6 +86,11 @@ size_t gemm_tc_activation_bytes(int rows, int k, int shards);
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
                    int n_shards, int rows, int k, int n_total, __half* xa, __half* out, int* err, cudaStream_t st);
 
+// exl3_allreduce.cu -------------------------------------------------------------------------------------
+size_t allreduce_region_bytes(size_t max_elems);
+int launch_allreduce(void* data, int bf16, size_t n, void* const* peer_bases_host, int rank, int world, size_t max_elems, int* state,
+                     cudaStream_t st);
+
 // Workspace carved up identically by every entry point that takes one.
 struct WorkspaceLayout {
     size_t err_off, counters_off, xf_off, partials_off, total;
