@@ -149,6 +149,110 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def run_prefill(args) -> None:
+    """Secondary workload (BASELINE config 3): the four fused groups of one 27B-shape layer at M = 2048 rows, K = 4,
+    MCG codebook, through the fused tcgen05 kernel.  One step = one layer.  Tensor-pipe roofline."""
+    import torch
+    from trellis_serve_b200.kernels import linear as lin
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(200)
+    K, cb, rows = 4, 1, args.rows if args.rows > 1 else 2048
+    shapes = [(5120, [5120, 1024, 1024]), (5120, [5120]), (5120, [17408, 17408]), (17408, [5120])]
+    groups = []
+    for k, ns in shapes:
+        packed = torch.cat([random_packed(k, n, K, gen, dev) for n in ns])
+        ends = [sum(ns[:i + 1]) for i in range(len(ns) - 1)]
+        x = torch.randn((rows, k), device=dev, generator=gen).half()
+        groups.append((x, packed, random_signs(k, gen, dev, len(ns)), random_signs(sum(ns), gen, dev).view(-1), ends,
+                       torch.empty((rows, sum(ns)), dtype=torch.float16, device=dev)))
+    flops = sum(2.0 * rows * k * sum(ns) for k, ns in shapes)
+
+    def step():
+        for x, packed, suh, svh, ends, out in groups:
+            lin.run_tc(x, packed, suh, svh, ends, cb, out=out)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    lin.device_error(dev)
+    peak = 1648.3
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        peak = float(json.load(open(path))["bf16_tflops"])
+    tf = flops / ms / 1e9
+    print(json.dumps({"metric": "exl3_prefill_tflops_27b_layer_m2048_k4_mcg", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": f"one 27B-shape layer (qkv, o, gate_up, down), {rows} rows, K=4 MCG, fused tcgen05 GEMM",
+                                 "rows": rows, "l2": "weights 165 MB per layer, larger than L2"},
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                                   "peak_source": "of measured (burst)", "kernel": "gemm_tc_kernel"},
+                      "gpu_launches": 16 * args.steps, "clocks": clocks.summary()}))
+
+
+def run_moe(args) -> None:
+    """Secondary workload (BASELINE config 4): one MoE layer, hidden 2048, 256 experts, intermediate 512, top-8, K = 3,
+    softmax-of-N(0,1) routing, captured in a CUDA graph.  GB/s on the packed bytes of the distinct routed experts."""
+    import torch
+    from trellis_serve_b200 import _lib
+    from trellis_serve_b200.kernels import moe
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    _lib.init_device(0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(300)
+    E, H, I, top_k, K, cb = 256, 2048, 512, 8, 3, 0
+    T = args.rows
+    w13 = torch.stack([torch.cat([random_packed(H, I, K, gen, dev), random_packed(H, I, K, gen, dev)]) for _ in range(E)])
+    w2 = torch.stack([random_packed(I, H, K, gen, dev) for _ in range(E)])
+    pack = moe.ExpertPack(w13, w2, random_signs(H, gen, dev, E * 2).view(E, 2, H), (random_signs(2 * I, gen, dev, E) / 32).half(),
+                          random_signs(I, gen, dev, E), (random_signs(H, gen, dev, E) / 32).half(), cb, H, I, E, K)
+    wts, ids = torch.topk(torch.softmax(torch.randn((T, E), device=dev, generator=gen), -1), top_k)
+    wts, ids = (wts / wts.sum(-1, keepdim=True)).float(), ids.int()
+    x = torch.randn((T, H), device=dev, generator=gen).half()
+    out = torch.empty_like(x)
+    for _ in range(args.warmup):
+        moe.forward(x, wts, ids, pack, out=out)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        moe.forward(x, wts, ids, pack, out=out)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    distinct = int(torch.unique(ids).numel())
+    nbytes = distinct * (H * 2 * I + I * H) * K // 8
+    peak, kind = measured_peak_hbm()
+    gbs = nbytes / ms / 1e6
+    print(json.dumps({"metric": "exl3_moe_layer_gbs_touched_expert_bytes", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": f"MoE layer hidden 2048, 256 experts, intermediate 512, top-8, K=3 3INST, {T} tokens",
+                                 "tokens": T, "distinct_experts": distinct, "touched_bytes": nbytes,
+                                 "l2": "the layer's working set is L2-resident on replay (302 MB of experts, touched subset smaller)"},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                                   "peak_source": f"of {kind}", "kernel": "moe_gemm_kernel"},
+                      "gpu_launches": 6 * args.steps, "clocks": clocks.summary()}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -161,11 +265,19 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="exchange step of row-parallel layers at N > 1: the library's one-shot peer-memory kernel, or NCCL")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
+                    help="decode = the headline 27B-shape layer set (default); prefill / moe = secondary single-GPU workloads")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "prefill":
+        run_prefill(args)
+        return
+    if args.workload == "moe":
+        run_moe(args)
         return
 
     import torch

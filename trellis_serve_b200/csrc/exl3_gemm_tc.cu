@@ -145,16 +145,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
         const int nt = warp, g = lane >> 2, q = lane & 3;
         const CodebookConst cbc = {p.mul, p.add};
         uint32_t it = 0, acc_round = 0;
+        // The warp's words of the next reduction block are requested one block ahead, so their L2 latency hides
+        // behind the decode of the current block.
+        auto words_ptr = [&](long long tile, int kb) {
+            const int nb_ = (int)(tile / p.MS);
+            return p.packed + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
+        };
+        uint32_t Lnext[K];
+        if ((long long)blockIdx.x < n_tiles) {
+            const uint32_t* src = words_ptr(blockIdx.x, 0);
+#pragma unroll
+            for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
+        }
         for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
             const int ms = (int)(t % p.MS), nb = (int)(t / p.MS);
             for (int kb = 0; kb < KB; kb++, it++) {
                 const int s = it % TC_STAGES;
                 const uint32_t round = it / TC_STAGES;
-                const int kg = kb >> 1, kq = kb & 1;
                 uint32_t L[K];
-                const uint32_t* src = p.packed + (((((long long)nb * p.KG + kg) * 8 + nt) * 2 + kq) * K) * 32 + lane;
 #pragma unroll
-                for (int i = 0; i < K; i++) L[i] = __ldg(src + i * 32);
+                for (int i = 0; i < K; i++) L[i] = Lnext[i];
+                {
+                    const bool last = kb + 1 == KB;
+                    const long long tn = last ? t + gridDim.x : t;
+                    if (tn < n_tiles) {
+                        const uint32_t* src = words_ptr(tn, last ? 0 : kb + 1);
+#pragma unroll
+                        for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
+                    }
+                }
                 if (round > 0 && !failed && !ptx::mbar_wait(&empty[s], (round - 1) & 1)) fail();
                 unsigned char* bst = stage0 + (size_t)s * TC_STAGE_BYTES + TC_A_STAGE_BYTES;
                 auto tile = [&](auto tconst) {
