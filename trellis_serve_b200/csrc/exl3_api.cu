@@ -216,10 +216,17 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
                 if (rc) return rc;
             }
         } else {
+            // Up to two rows: the GEMV rotates its own input (one launch); otherwise the rotation kernel runs ahead of it.
             const unsigned char* xr = reinterpret_cast<const unsigned char*>(x) + (size_t)r0 * k * esz;
-            rc = launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
-                               const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
-            if (rc) return rc;
+            a.x = xr;
+            a.suh = reinterpret_cast<const __half*>(suh_cat);
+            a.x_bf16 = x_dtype == EXL3_BF16;
+            if (!gemv_rotates_input(a)) {
+                a.x = nullptr;
+                rc = launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
+                                   const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
+                if (rc) return rc;
+            }
         }
         rc = launch_gemv(a, st);
         if (rc) return rc;

@@ -16,9 +16,7 @@ void gemv_set_mode_override(int mode) { g_mode_override = mode; }
 
 constexpr size_t GEMV_FIXED_SMEM = 256 + GEMV_MAX_ROWS * 128 * 4;
 constexpr size_t GEMV_RING_TARGET = 96 * 1024;
-constexpr size_t GEMV_STAGE_TARGET = 24 * 1024;
-
-size_t gemv_smem_bytes(const GemvLaunch& l) { return GEMV_FIXED_SMEM + (size_t)l.stages * l.stage_stride; }
+constexpr size_t GEMV_STAGE_TARGET = 32 * 1024;
 
 WorkspaceLayout workspace_layout(int rows, int k, int n_total, int n_shards)
 {
@@ -48,17 +46,14 @@ int gemv_init_device()
     return rc;
 }
 
-int launch_gemv(const GemvArgs& a, cudaStream_t st)
+// Work split and shared-memory plan of one launch.  With `fused` the fragment slots of the in-kernel rotation are
+// budgeted first and the ring takes what is left; an error status when that leaves fewer than three stages.
+static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLaunch& l, size_t& smem)
 {
-    const DeviceInfo* d = current_device_info();
-    if (!d) return EXL3_ERR_NOT_INITIALISED;
-    if (a.rows < 1 || a.rows > GEMV_MAX_ROWS) return EXL3_ERR_UNSUPPORTED_ROWS;
-    GemvLaunch l;
     l.a = a;
     l.KG = a.k / 128;
     l.NB = a.n_total / 128;
     const long long units = (long long)l.KG * l.NB;
-    if (units == 0) return EXL3_OK;
     int grid = d->sm_count * GEMV_CTAS_PER_SM;
     if (grid > GEMV_MAX_GRID) grid = GEMV_MAX_GRID;
     if (units < grid) grid = (int)units;
@@ -66,34 +61,66 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     l.units_q = (int)(units / grid);
     l.units_r = (int)(units % grid);
     const int fw = gemv_frag_words(a.mode);
-    // Stage = as many whole units as make one bulk copy of about 24-32 KB; at least 3 stages in flight.
+    // Stage = as many whole units as make one bulk copy of 32 KB or a little more; two or three stages in flight.
     const uint32_t unit_bytes = 2048u * a.K;
     int ups = (int)((GEMV_STAGE_TARGET + unit_bytes - 1) / unit_bytes);
     if (ups < 1) ups = 1;
     const long long per_cta = units / grid;
-    if (per_cta < 3ll * ups) ups = (int)(per_cta / 3 > 0 ? per_cta / 3 : 1);      // short ranges: keep several copies in flight
+    // Short ranges travel as one copy: the copies of a launch start while the kernel ahead of it is still finishing, so
+    // nothing is gained by cutting a small range into several copies, each of which pays the copy engine's fixed cost.
+    const long long per_cta_max = per_cta + (l.units_r ? 1 : 0);
+    if (per_cta_max < ups) ups = (int)per_cta_max;
+    if (ups < 1) ups = 1;
     l.units_per_stage = ups;
     l.stage_stride = (uint32_t)ups * unit_bytes;
+    size_t xs_bytes = 0;
+    if (fused) xs_bytes = GEMV_XS_ZERO_BYTES + (size_t)(l.units_q + 1) * gemv_xs_slot_bytes(a.mode, a.rows);
+    const size_t budget = (size_t)d->max_smem_optin / GEMV_CTAS_PER_SM - 2048 - GEMV_FIXED_SMEM;
+    if (xs_bytes + 2 * (size_t)l.stage_stride > budget) return EXL3_ERR_UNSUPPORTED_ROWS;
     int stages = (int)(GEMV_RING_TARGET / l.stage_stride);
-    const int cap = (int)((d->max_smem_optin / GEMV_CTAS_PER_SM - 2048 - GEMV_FIXED_SMEM) / l.stage_stride);
+    const int cap = (int)((budget - xs_bytes) / l.stage_stride);
     if (stages > cap) stages = cap;
     if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
     if (stages < 2) return EXL3_ERR_UNSUPPORTED_ROWS;
     l.stages = stages;
+    l.xs_off = (uint32_t)(GEMV_FIXED_SMEM + (size_t)stages * l.stage_stride);
+    smem = l.xs_off + xs_bytes;
     const CodebookConst c = codebook_const(a.codebook);
     l.mul = c.mul;
     l.add = c.add;
     l.xf_shard_stride = (long long)(a.k / 16) * a.rows * 4 * fw;
     for (int c = 0; c <= 16; c++) l.pw.v[c] = 1u << c;
     l.zeros = reinterpret_cast<const unsigned char*>(a.err) + 64;      // the workspace header stays zero past the error word
+    return EXL3_OK;
+}
+
+bool gemv_rotates_input(const GemvArgs& a)
+{
+    const DeviceInfo* d = current_device_info();
+    if (!d || !a.x || !a.suh || a.rotated || a.rows < 1 || a.rows > GEMV_FUSED_ROWS) return false;
+    if (a.k < 128 || a.n_total < 128) return false;
+    GemvLaunch l;
+    size_t smem;
+    return plan_gemv(a, d, true, l, smem) == EXL3_OK;
+}
+
+int launch_gemv(const GemvArgs& a, cudaStream_t st)
+{
+    const DeviceInfo* d = current_device_info();
+    if (!d) return EXL3_ERR_NOT_INITIALISED;
+    if (a.rows < 1 || a.rows > GEMV_MAX_ROWS) return EXL3_ERR_UNSUPPORTED_ROWS;
+    if ((long long)(a.k / 128) * (a.n_total / 128) == 0) return EXL3_OK;
+    GemvLaunch l;
+    size_t smem = 0;
+    if (int rc = plan_gemv(a, d, a.x != nullptr, l, smem)) return rc;
     switch (a.K) {
-        case 2: return launch_gemv_for_k<2>(l, st);
-        case 3: return launch_gemv_for_k<3>(l, st);
-        case 4: return launch_gemv_for_k<4>(l, st);
-        case 5: return launch_gemv_for_k<5>(l, st);
-        case 6: return launch_gemv_for_k<6>(l, st);
-        case 7: return launch_gemv_for_k<7>(l, st);
-        case 8: return launch_gemv_for_k<8>(l, st);
+        case 2: return launch_gemv_for_k<2>(l, smem, st);
+        case 3: return launch_gemv_for_k<3>(l, smem, st);
+        case 4: return launch_gemv_for_k<4>(l, smem, st);
+        case 5: return launch_gemv_for_k<5>(l, smem, st);
+        case 6: return launch_gemv_for_k<6>(l, smem, st);
+        case 7: return launch_gemv_for_k<7>(l, smem, st);
+        case 8: return launch_gemv_for_k<8>(l, smem, st);
     }
     return EXL3_ERR_UNSUPPORTED_K;
 }

@@ -7,7 +7,7 @@
 
 namespace exl3 {
 
-template <int K, int MODE, int FAM, int MB>
+template <int K, int MODE, int FAM, int MB, int XR>
 static int launch_one(const GemvLaunch& l, size_t smem, cudaStream_t st)
 {
     // Launched with programmatic stream serialization: its prologue and weight copies overlap the tail of the kernel
@@ -22,42 +22,53 @@ static int launch_one(const GemvLaunch& l, size_t smem, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cuda_status(cudaLaunchKernelEx(&cfg, gemv_kernel<K, MODE, FAM, MB>, l));
+    return cuda_status(cudaLaunchKernelEx(&cfg, gemv_kernel<K, MODE, FAM, MB, XR>, l));
 }
 
-template <int K, int MODE, int FAM, int MB>
+template <int K, int MODE, int FAM, int MB, int XR>
 static int set_attr(int max_smem)
 {
-    return cuda_status(cudaFuncSetAttribute(gemv_kernel<K, MODE, FAM, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    return cuda_status(cudaFuncSetAttribute(gemv_kernel<K, MODE, FAM, MB, XR>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
 }
 
-size_t gemv_smem_bytes(const GemvLaunch& l);
+template <int K, int MODE, int FAM>
+static int launch_variant(const GemvLaunch& l, size_t smem, cudaStream_t st)
+{
+    if (l.a.x) {                                  // the kernel rotates the input itself
+        if (l.a.rows == 1) return launch_one<K, MODE, FAM, 1, 1>(l, smem, st);
+        if (l.a.rows == 2) return launch_one<K, MODE, FAM, 1, 2>(l, smem, st);
+        return EXL3_ERR_UNSUPPORTED_ROWS;
+    }
+    return l.a.rows > 8 ? launch_one<K, MODE, FAM, 2, 0>(l, smem, st) : launch_one<K, MODE, FAM, 1, 0>(l, smem, st);
+}
+
+template <int K, int MODE, int FAM>
+static int set_attr_variants(int max_smem)
+{
+    int rc = set_attr<K, MODE, FAM, 1, 0>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 2, 0>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 1>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 2>(max_smem);
+    return rc;
+}
 
 template <>
-int launch_gemv_for_k<EXL3_GEMV_K>(const GemvLaunch& l, cudaStream_t st)
+int launch_gemv_for_k<EXL3_GEMV_K>(const GemvLaunch& l, size_t smem, cudaStream_t st)
 {
     constexpr int K = EXL3_GEMV_K;
-    const size_t smem = gemv_smem_bytes(l);
-    const bool two = l.a.rows > 8;
     const int fam = codebook_family(l.a.codebook);
-    if (l.a.mode == GEMV_SPLIT && fam == FAM_HASH)
-        return two ? launch_one<K, GEMV_SPLIT, FAM_HASH, 2>(l, smem, st) : launch_one<K, GEMV_SPLIT, FAM_HASH, 1>(l, smem, st);
-    if (fam == FAM_HASH)
-        return two ? launch_one<K, GEMV_PAIRED, FAM_HASH, 2>(l, smem, st) : launch_one<K, GEMV_PAIRED, FAM_HASH, 1>(l, smem, st);
-    return two ? launch_one<K, GEMV_PAIRED, FAM_MUL1, 2>(l, smem, st) : launch_one<K, GEMV_PAIRED, FAM_MUL1, 1>(l, smem, st);
+    if (l.a.mode == GEMV_SPLIT && fam == FAM_HASH) return launch_variant<K, GEMV_SPLIT, FAM_HASH>(l, smem, st);
+    if (fam == FAM_HASH) return launch_variant<K, GEMV_PAIRED, FAM_HASH>(l, smem, st);
+    return launch_variant<K, GEMV_PAIRED, FAM_MUL1>(l, smem, st);
 }
 
 template <>
 int gemv_set_attributes_for_k<EXL3_GEMV_K>(int max_smem)
 {
     constexpr int K = EXL3_GEMV_K;
-    int rc = EXL3_OK;
-    if (rc == EXL3_OK) rc = set_attr<K, GEMV_SPLIT, FAM_HASH, 1>(max_smem);
-    if (rc == EXL3_OK) rc = set_attr<K, GEMV_SPLIT, FAM_HASH, 2>(max_smem);
-    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_HASH, 1>(max_smem);
-    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_HASH, 2>(max_smem);
-    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_MUL1, 1>(max_smem);
-    if (rc == EXL3_OK) rc = set_attr<K, GEMV_PAIRED, FAM_MUL1, 2>(max_smem);
+    int rc = set_attr_variants<K, GEMV_SPLIT, FAM_HASH>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr_variants<K, GEMV_PAIRED, FAM_HASH>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr_variants<K, GEMV_PAIRED, FAM_MUL1>(max_smem);
     return rc;
 }
 

@@ -41,8 +41,16 @@ struct GemvLaunch {
     const void* zeros;          // at least 16 bytes of zeros in global memory
     uint32_t mul, add;
     long long xf_shard_stride;  // words between shards in xf
+    uint32_t xs_off;            // in-kernel rotation only: byte offset of the fragment slots in shared memory
     Pow2 pw;                    // powers of two for the multiply that cuts a window out (constant bank)
 };
+
+// Largest row count whose input rotation the GEMV does itself (one launch per linear instead of two).
+constexpr int GEMV_FUSED_ROWS = 2;
+// Shared memory of the in-kernel rotation: a block of zeros (read by lanes whose batch row does not exist) followed by
+// one slot of fragments per unit of the CTA.
+constexpr uint32_t GEMV_XS_ZERO_BYTES = 512;
+__host__ __device__ constexpr uint32_t gemv_xs_slot_bytes(int mode, int rows) { return 8u * rows * 4u * gemv_frag_words(mode) * 4u; }
 
 __host__ __device__ inline long long gemv_first_unit(int cta, int q, int r) { return (long long)cta * q + (cta < r ? cta : r); }
 
@@ -70,10 +78,22 @@ __device__ __forceinline__ void decode_tile_regs(const LaneRegs<K>& R, const Pow
     }
 }
 
+__device__ __forceinline__ float gemv_load_x(const void* p, long long idx, bool bf16)
+{
+    // bf16 inputs are first converted to fp16 (round to nearest even), as the stand-alone rotation kernel does.
+    if (bf16) return __half2float(__float2half_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx])));
+    return __half2float(reinterpret_cast<const __half*>(p)[idx]);
+}
+
 // MODE: GEMV_SPLIT / GEMV_PAIRED.  FAM: FAM_HASH / FAM_MUL1 (split implies hash).  MB: 8-row groups (1 or 2).
-template <int K, int MODE, int FAM, int MB>
+// XR: 0 = activation fragments come from the workspace (written by the rotation kernel ahead of this launch);
+//     1, 2 = that many rows, and the kernel rotates the input itself: before the main loop every consumer warp turns
+//     x * suh of a few of the CTA's units into fragments in shared memory (one slot per unit, in unit order), so the
+//     linear is ONE launch and the main loop reads its activations with immediate-offset shared loads.
+template <int K, int MODE, int FAM, int MB, int XR>
 __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(const GemvLaunch p)
 {
+    static_assert(XR == 0 || MB == 1, "in-kernel rotation serves one 8-row group");
     constexpr int FW = gemv_frag_words(MODE);
     constexpr uint32_t W_BYTES = 2048u * K;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -107,13 +127,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         // One bulk copy per stage and stages of several units: the copy engine has a fixed cost of a few hundred
         // nanoseconds per bulk copy, so small copies cap the stream far below HBM speed.  The CTA's units are
         // contiguous in memory, so a stage is simply the next `units_per_stage` units.  One thread issues the
-        // copies in ring order and sleeps between polls while it waits for the oldest stage to be released.
+        // copies in ring order; while it waits for the oldest stage to be released the hardware keeps it suspended
+        // (try_wait with a time hint), so it takes no issue slots from the consumer warps of its scheduler.
         if (lane == 0) {
             int s = 0;
             uint32_t wait_parity = 1;              // parity of the empty-barrier phase awaited in the current lap
             bool first_lap = true;
             for (long long u = u0; u < u1; u += p.units_per_stage) {
-                if (!first_lap && !ptx::mbar_wait_relaxed(&empty[s], wait_parity)) {
+                if (!first_lap && !ptx::mbar_wait(&empty[s], wait_parity)) {
                     atomicExch(p.a.err, GEMV_ERR_EMPTY_WAIT);
                     break;
                 }
@@ -131,8 +152,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     }
 
     // ---------------------------------------------------------------------- consumers
-    // Everything below reads or writes memory other kernels write (activation fragments, workspace, output).
-    ptx::grid_dependency_wait();
+    // Everything below reads or writes memory other kernels write (activations, workspace, output) and so comes after
+    // the wait for the kernel ahead; with the in-kernel rotation the (constant) sign vectors are fetched before it.
+    if constexpr (XR == 0) ptx::grid_dependency_wait();
     const int nt = warp & 7, kq = warp >> 3;
     const int g = lane >> 2, q = lane & 3;
     const CodebookConst cbc = {p.mul, p.add};
@@ -145,59 +167,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     const uint32_t stage0_addr = ptx::smem_addr(stage0);
     const uint32_t w_off = (uint32_t)((nt * 2 + kq) * K) * 128u + lane * 4u;
     int nb = (int)(u0 / p.KG), kg = (int)(u0 % p.KG);
-    bool dirty = false;
 
-    auto flush = [&](int fnb) {
-        // acc -> P (the two k-halves of a column tile add up), then either finish the block here or hand the
-        // partial sums to the workspace and let the last CTA to arrive finish it.
-        ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            if (kq == half) {
-#pragma unroll
-                for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        int m = 8 * mb + 2 * q + (e & 1);
-                        int col = nt * 16 + g + 8 * (e >> 1);
-                        if (m < rows) {
-                            float* dst = &P[m * 128 + col];
-                            *dst = half == 0 ? acc[mb][e] : *dst + acc[mb][e];
-                        }
-                    }
-            }
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
-        }
-        const long long ub = (long long)fnb * p.KG;
-        const int c_first = gemv_cta_of_unit(ub, p.units_q, p.units_r);
-        const int c_last = gemv_cta_of_unit(ub + p.KG - 1, p.units_q, p.units_r);
-        const int tid = threadIdx.x;
-        const int nelem = rows * 128;
-        bool finish = true;
-        if (c_first != c_last) {
-            float* slot = p.a.partials + (size_t)(cta + fnb) * rows * 128;
-            for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) slot[e] = P[e];
-            __threadfence();
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
-            if (tid == 0) {
-                int old = atomicAdd(&p.a.counters[fnb], 1);
-                int last = (old == c_last - c_first);
-                if (last) p.a.counters[fnb] = 0;          // leave the counter ready for the next launch
-                flag[0] = last;
-            }
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
-            finish = flag[0] != 0;
-            if (finish) {
-                __threadfence();
-                for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) {
-                    float sum = 0.f;
-                    for (int c = c_first; c <= c_last; c++) sum += __ldcg(p.a.partials + (size_t)(c + fnb) * rows * 128 + e);
-                    P[e] = sum;
-                }
-            }
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
-        }
-        if (finish && warp < rows) {
+    // P -> out for column block fnb: one warp per batch row applies Had128 * svh (or stores the rotated-basis product).
+    auto epilogue = [&](int fnb) {
+        if (warp < rows) {
             const int m = warp;
             float v[4];
 #pragma unroll
@@ -233,27 +206,159 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 }
             }
         }
+    };
+
+    auto flush = [&](int fnb) {
+        // acc -> P (the two k-halves of a column tile add up), then either finish the block here or hand the
+        // partial sums to the workspace and let the last CTA to arrive finish it.
+        ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            if (kq == half) {
+#pragma unroll
+                for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        int m = 8 * mb + 2 * q + (e & 1);
+                        int col = nt * 16 + g + 8 * (e >> 1);
+                        if (m < rows) {
+                            float* dst = &P[m * 128 + col];
+                            *dst = half == 0 ? acc[mb][e] : *dst + acc[mb][e];
+                        }
+                    }
+            }
+            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+        }
+        const long long ub = (long long)fnb * p.KG;
+        const int c_first = gemv_cta_of_unit(ub, p.units_q, p.units_r);
+        const int c_last = gemv_cta_of_unit(ub + p.KG - 1, p.units_q, p.units_r);
+        bool finish = true;
+        if (c_first != c_last) {
+            const int tid = threadIdx.x;
+            const int nelem = rows * 128;
+            float* slot = p.a.partials + (size_t)(cta + fnb) * rows * 128;
+            for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) slot[e] = P[e];
+            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            if (tid == 0) {
+                // The barrier orders every thread's stores before this thread; its fence then publishes them all
+                // (fences are cumulative) ahead of the counter update.
+                __threadfence();
+                int old = atomicAdd(&p.a.counters[fnb], 1);
+                int last = (old == c_last - c_first);
+                if (last) p.a.counters[fnb] = 0;          // leave the counter ready for the next launch
+                flag[0] = last;
+            }
+            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            finish = flag[0] != 0;
+            if (finish) {                                 // the last CTA to arrive adds up in a fixed order
+                __threadfence();
+                for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) {
+                    float sum = 0.f;
+                    for (int c = c_first; c <= c_last; c++) sum += __ldcg(p.a.partials + (size_t)(c + fnb) * rows * 128 + e);
+                    P[e] = sum;
+                }
+            }
+            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+        }
+        if (finish) epilogue(fnb);
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
 #pragma unroll
             for (int e = 0; e < 4; e++) acc[mb][e] = 0.f;
     };
 
-    // Activation fragments come straight from global memory (they are tiny and stay in L1/L2).  Lanes whose batch
-    // row does not exist read a block of zeros instead, so no select is needed per tile.
-    // Fragment elements are FW words: element index = (k-tile * rows + row) * 4 + q.
+    // Activation fragments.  Fragment elements are FW words: element index = (k-tile * rows + row) * 4 + q.  Lanes whose
+    // batch row does not exist read a block of zeros instead, so no select is needed per tile.
+    //   XR == 0: straight from global memory (they are tiny and stay in L1/L2), written by the kernel ahead;
+    //   XR  > 0: from the shared-memory slots filled below, slot i = unit u0 + i.
     using Frag = typename std::conditional<FW == 4, uint4, uint2>::type;
     const Frag* x_base[MB];
     uint32_t x_lane[MB], x_tile[MB], x_unit[MB];      // element offsets: lane, per 16-row tile, per unit (8 tiles)
-#pragma unroll
-    for (int mb = 0; mb < MB; mb++) {
-        const bool ok = (g + 8 * mb) < rows;
-        x_base[mb] = reinterpret_cast<const Frag*>(ok ? static_cast<const void*>(p.a.xf) : p.zeros);
-        x_lane[mb] = ok ? (uint32_t)((g + 8 * mb) * 4 + q + kq * 4 * rows * 4) : 0u;
-        x_tile[mb] = ok ? (uint32_t)(rows * 4) : 0u;
-        x_unit[mb] = ok ? (uint32_t)(8 * rows * 4) : 0u;
-    }
     const uint32_t x_shard_elems = (uint32_t)(p.xf_shard_stride / FW);
+    uint32_t xaddr = 0, xstep = 0;                    // XR > 0: shared address of the lane's fragments, bytes per unit
+    constexpr uint32_t XS_TILE = (uint32_t)(XR > 0 ? XR : 1) * 4u * FW * 4u;      // bytes per 16-row tile in a slot
+    constexpr uint32_t XS_SLOT = 8u * XS_TILE;
+    if constexpr (XR == 0) {
+#pragma unroll
+        for (int mb = 0; mb < MB; mb++) {
+            const bool ok = (g + 8 * mb) < rows;
+            x_base[mb] = reinterpret_cast<const Frag*>(ok ? static_cast<const void*>(p.a.xf) : p.zeros);
+            x_lane[mb] = ok ? (uint32_t)((g + 8 * mb) * 4 + q + kq * 4 * rows * 4) : 0u;
+            x_tile[mb] = ok ? (uint32_t)(rows * 4) : 0u;
+            x_unit[mb] = ok ? (uint32_t)(8 * rows * 4) : 0u;
+        }
+    } else {
+        unsigned char* xs = smem + p.xs_off;
+        uint32_t* slots = reinterpret_cast<uint32_t*>(xs + GEMV_XS_ZERO_BYTES);
+        if (threadIdx.x < GEMV_XS_ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xs)[threadIdx.x] = 0u;
+        const int items = (int)(u1 - u0) * XR;
+        const bool bf16 = p.a.x_bf16 != 0;
+        constexpr int BATCH = 3;                      // rotations in flight per warp: their loads overlap
+        bool waited = false;
+        for (int it0 = warp; it0 < items; it0 += GEMV_CONSUMER_WARPS * BATCH) {
+            float v[BATCH][4];
+            long long xi[BATCH];
+#pragma unroll
+            for (int b = 0; b < BATCH; b++) {
+                const int it = it0 + GEMV_CONSUMER_WARPS * b;
+                xi[b] = 0;
+                if (it < items) {
+                    const int i = it / XR, row = it % XR;
+                    const long long u = u0 + i;
+                    const int unb = (int)(u / p.KG), ukg = (int)(u - (long long)unb * p.KG);
+                    int s = 0;
+                    while (s < p.a.n_shards - 1 && unb >= p.a.shard_end_blocks[s]) s++;
+                    const long long col = (long long)ukg * 128 + 4 * lane;
+                    xi[b] = (long long)row * p.a.k + col;
+#pragma unroll
+                    for (int e = 0; e < 4; e++) v[b][e] = __half2float(p.a.suh[(long long)s * p.a.k + col + e]);
+                }
+            }
+            if (!waited) {
+                ptx::grid_dependency_wait();
+                waited = true;
+            }
+#pragma unroll
+            for (int b = 0; b < BATCH; b++) {
+                if (it0 + GEMV_CONSUMER_WARPS * b < items) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) v[b][e] *= gemv_load_x(p.a.x, xi[b] + e, bf16);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BATCH; b++) {
+                const int it = it0 + GEMV_CONSUMER_WARPS * b;
+                if (it < items) {                     // warp-uniform: every lane takes part in the shuffles
+                    const int i = it / XR, row = it % XR;
+                    fwht128(v[b][0], v[b][1], v[b][2], v[b][3], lane);
+                    // the lane holds tile-local rows r = 4*(lane&3) + e of 16-row tile lane/4 of the unit
+                    uint32_t* o = slots + (size_t)i * (XS_SLOT / 4) + (size_t)((lane >> 2) * XR + row) * 4 * FW;
+                    const int rbase = 4 * (lane & 3);
+                    uint32_t hv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) hv[e] = __half_as_ushort(__float2half_rn(v[b][e] * HAD_SCALE));
+                    if constexpr (MODE == GEMV_SPLIT) {
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int r = rbase + e;
+                            o[((r & 7) >> 1) * 4 + (r & 1) + 2 * (r >> 3)] = hv[e] | (hv[e] << 16);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; e += 2) {
+                            const int r = rbase + e;
+                            o[((r & 7) >> 1) * 2 + (r >> 3)] = hv[e] | (hv[e + 1] << 16);
+                        }
+                    }
+                }
+            }
+        }
+        if (!waited) ptx::grid_dependency_wait();
+        ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+        const bool ok = g < XR;
+        xaddr = ptx::smem_addr(xs) + (ok ? GEMV_XS_ZERO_BYTES + (uint32_t)(kq * 4 * XR + g) * 4u * FW * 4u + (uint32_t)q * FW * 4u : 0u);
+        xstep = ok ? XS_SLOT : 0u;
+    }
     bool aborted = false;
     const int ups = p.units_per_stage;
 
@@ -267,62 +372,85 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 
     int shard = 0;
     while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
-    // Everything that changes from unit to unit is kept as a running value (no division, no 64-bit arithmetic
-    // in the steady state): shared-memory address of the warp's words, fragment offsets, unit-in-stage counter.
-    int slot = 0, in_stage = 0;
+    // The main loop is cut into runs of units that end where something has to happen (stage used up, column block
+    // finished, range finished); inside a run only two addresses advance: no division, no 64-bit arithmetic, no
+    // bookkeeping per unit.
+    int slot = 0, stage_left = ups;
     uint32_t phase = 0;
     uint32_t waddr = stage0_addr + w_off;
     uint32_t xu[MB];
+    if constexpr (XR == 0) {
 #pragma unroll
-    for (int mb = 0; mb < MB; mb++)
-        xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems + (uint32_t)kg * x_unit[mb] : 0u);
+        for (int mb = 0; mb < MB; mb++)
+            xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems + (uint32_t)kg * x_unit[mb] : 0u);
+    }
     int remaining = (int)(u1 - u0);
     if (remaining > 0) wait_stage(0, 0);
 
     while (remaining > 0) {
-        uint32_t L[K];
+        int run = p.KG - kg;
+        if (run > stage_left) run = stage_left;
+        if (run > remaining) run = remaining;
+        remaining -= run;
+        stage_left -= run;
+        kg += run;
+#pragma unroll 1
+        for (; run > 0; run--) {
+            uint32_t L[K];
 #pragma unroll
-        for (int i = 0; i < K; i++) L[i] = ptx::lds32(waddr + i * 128u);
-        // All activation fragments of the unit are requested up front so that their latency hides behind the decode.
-        Frag bfrag[MB][4];
+            for (int i = 0; i < K; i++) L[i] = ptx::lds32(waddr + i * 128u);
+            // All activation fragments of the unit are requested up front so that their latency hides behind the decode.
+            Frag bfrag[MB][4];
+            if constexpr (XR == 0) {
 #pragma unroll
-        for (int mb = 0; mb < MB; mb++)
+                for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-            for (int T = 0; T < 4; T++) bfrag[mb][T] = __ldg(x_base[mb] + (xu[mb] + T * x_tile[mb]));
-
-        auto tile = [&](auto tconst) {
-            constexpr int T = decltype(tconst)::value;
-            uint32_t own[2];
-            own_words<K, T>(L, own);
-            const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
-            const LaneRegs<K> R = lane_regs<K>(own, prev0);
-            uint32_t w[8];
-            decode_tile_regs<K, MODE, FAM>(R, p.pw, cbc, w);
+                    for (int T = 0; T < 4; T++) bfrag[mb][T] = __ldg(x_base[mb] + (xu[mb] + T * x_tile[mb]));
+            } else {
 #pragma unroll
-            for (int mb = 0; mb < MB; mb++) {
-                if constexpr (MODE == GEMV_SPLIT) {
-                    const uint4 b = bfrag[mb][T];
-                    ptx::mma_m16n8k16(acc[mb], w[0], w[4], w[1], w[5], b.x, b.y);
-                    ptx::mma_m16n8k16(acc[mb], w[2], w[6], w[3], w[7], b.z, b.w);
-                } else {
-                    const uint2 b = bfrag[mb][T];
-                    ptx::mma_m16n8k16(acc[mb], w[0], w[2], w[1], w[3], b.x, b.y);
+                for (int T = 0; T < 4; T++) {
+                    if constexpr (FW == 4) bfrag[0][T] = ptx::lds128(xaddr + T * XS_TILE);
+                    else bfrag[0][T] = ptx::lds64(xaddr + T * XS_TILE);
                 }
             }
-        };
-        tile(std::integral_constant<int, 0>{});
-        tile(std::integral_constant<int, 1>{});
-        tile(std::integral_constant<int, 2>{});
-        tile(std::integral_constant<int, 3>{});
 
-        remaining--;
-        waddr += W_BYTES;
+            auto tile = [&](auto tconst) {
+                constexpr int T = decltype(tconst)::value;
+                uint32_t own[2];
+                own_words<K, T>(L, own);
+                const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
+                const LaneRegs<K> R = lane_regs<K>(own, prev0);
+                uint32_t w[8];
+                decode_tile_regs<K, MODE, FAM>(R, p.pw, cbc, w);
 #pragma unroll
-        for (int mb = 0; mb < MB; mb++) xu[mb] += x_unit[mb];
-        if (++in_stage == ups || remaining == 0) {          // stage finished: hand it back, move to the next one
+                for (int mb = 0; mb < MB; mb++) {
+                    if constexpr (MODE == GEMV_SPLIT) {
+                        const uint4 b = bfrag[mb][T];
+                        ptx::mma_m16n8k16(acc[mb], w[0], w[4], w[1], w[5], b.x, b.y);
+                        ptx::mma_m16n8k16(acc[mb], w[2], w[6], w[3], w[7], b.z, b.w);
+                    } else {
+                        const uint2 b = bfrag[mb][T];
+                        ptx::mma_m16n8k16(acc[mb], w[0], w[2], w[1], w[3], b.x, b.y);
+                    }
+                }
+            };
+            tile(std::integral_constant<int, 0>{});
+            tile(std::integral_constant<int, 1>{});
+            tile(std::integral_constant<int, 2>{});
+            tile(std::integral_constant<int, 3>{});
+
+            waddr += W_BYTES;
+            if constexpr (XR == 0) {
+#pragma unroll
+                for (int mb = 0; mb < MB; mb++) xu[mb] += x_unit[mb];
+            } else {
+                xaddr += xstep;
+            }
+        }
+        if (stage_left == 0 || remaining == 0) {            // stage finished: hand it back, move to the next one
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty[slot]);
-            in_stage = 0;
+            stage_left = ups;
             if (++slot == p.stages) {
                 slot = 0;
                 phase ^= 1;
@@ -330,22 +458,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             waddr = stage0_addr + (uint32_t)slot * p.stage_stride + w_off;
             if (remaining > 0) wait_stage(slot, phase);
         }
-        dirty = true;
-        if (++kg == p.KG) {                                  // column block finished
+        if (kg == p.KG) {                                    // column block finished
             flush(nb);
-            dirty = false;
             kg = 0;
             nb++;
-            while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
+            if constexpr (XR == 0) {
+                while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
 #pragma unroll
-            for (int mb = 0; mb < MB; mb++) xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems : 0u);
+                for (int mb = 0; mb < MB; mb++) xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems : 0u);
+            }
         }
     }
-    if (dirty) flush(nb);
+    if (kg != 0 && u1 > u0) flush(nb);
 }
 
 template <int K>
-int launch_gemv_for_k(const GemvLaunch& l, cudaStream_t st);
+int launch_gemv_for_k(const GemvLaunch& l, size_t smem, cudaStream_t st);
 template <int K>
 int gemv_set_attributes_for_k(int max_smem);
 

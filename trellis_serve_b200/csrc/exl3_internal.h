@@ -50,6 +50,9 @@ __host__ __device__ constexpr int gemv_frag_words(int mode) { return mode == GEM
 struct GemvArgs {
     const uint32_t* packed;     // resident weights, n-blocks of all shards concatenated
     const uint32_t* xf;         // activation fragments [shard][k/16][rows][4][frag_words]
+    const void* x;              // in-kernel rotation (rows <= 2): raw activations [rows, k], else nullptr
+    const __half* suh;          //   and the input sign vectors [n_shards][k]
+    int x_bf16;
     const __half* svh;          // [n_total]; unused when rotated
     void* out;                  // [rows, n_total]
     float* partials;            // [(grid + NB)][rows][128]
@@ -66,6 +69,9 @@ struct GemvArgs {
 // Preferred mode for a codebook (split for the hash codebooks, paired for MUL1).
 int gemv_default_mode(int codebook);
 void gemv_set_mode_override(int mode);      // -1 = default; test / measurement knob
+// With a.x set the GEMV rotates the input itself (no rotation launch ahead of it); gemv_rotates_input() tells whether
+// that variant can serve the problem (row count, shared-memory budget) and launch_gemv() then requires it to.
+bool gemv_rotates_input(const GemvArgs& a);
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
 int gemv_init_device();
 

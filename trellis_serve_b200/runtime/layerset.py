@@ -95,7 +95,8 @@ class DecodeLayerSet:
         self.y_gu = torch.empty((rows, 2 * f), dtype=dtype, device=self.device)
         self.y_down = torch.empty((rows, h), dtype=dtype, device=self.device)
         self.graph: torch.cuda.CUDAGraph | None = None
-        self.launches_per_step = layers * 4 * 2          # activation rotation + GEMV per group
+        # up to two rows the GEMV rotates its own input: one launch per group; otherwise rotation + GEMV
+        self.launches_per_step = layers * 4 * (1 if rows <= 2 else 2)
 
     @property
     def packed_bytes(self) -> int:
