@@ -109,7 +109,9 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     const DeviceInfo* d = current_device_info();
     if (!d) return EXL3_ERR_NOT_INITIALISED;
     if (a.rows < 1 || a.rows > GEMV_MAX_ROWS) return EXL3_ERR_UNSUPPORTED_ROWS;
-    if ((long long)(a.k / 128) * (a.n_total / 128) == 0) return EXL3_OK;
+    const long long units = (long long)(a.k / 128) * (a.n_total / 128);
+    if (units == 0) return EXL3_OK;
+    if (units >= (1ll << 31)) return EXL3_ERR_BAD_SHAPE;
     GemvLaunch l;
     size_t smem = 0;
     if (int rc = plan_gemv(a, d, a.x != nullptr, l, smem)) return rc;

@@ -52,12 +52,13 @@ constexpr int GEMV_FUSED_ROWS = 2;
 constexpr uint32_t GEMV_XS_ZERO_BYTES = 512;
 __host__ __device__ constexpr uint32_t gemv_xs_slot_bytes(int mode, int rows) { return 8u * rows * 4u * gemv_frag_words(mode) * 4u; }
 
-__host__ __device__ inline long long gemv_first_unit(int cta, int q, int r) { return (long long)cta * q + (cta < r ? cta : r); }
+// Unit indices fit 32 bits (the host refuses matrices with 2^31 or more units).
+__host__ __device__ inline int gemv_first_unit(int cta, int q, int r) { return cta * q + (cta < r ? cta : r); }
 
-__device__ __forceinline__ int gemv_cta_of_unit(long long u, int q, int r)
+__device__ __forceinline__ int gemv_cta_of_unit(int u, int q, int r)
 {
-    long long boundary = (long long)r * (q + 1);
-    return u < boundary ? (int)(u / (q + 1)) : r + (int)((u - boundary) / q);
+    const unsigned boundary = (unsigned)r * (unsigned)(q + 1);
+    return (unsigned)u < boundary ? (int)((unsigned)u / (unsigned)(q + 1)) : r + (int)(((unsigned)u - boundary) / (unsigned)q);
 }
 
 template <int K, int MODE, int FAM>
@@ -105,8 +106,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x;
-    const long long u0 = gemv_first_unit(cta, p.units_q, p.units_r);
-    const long long u1 = gemv_first_unit(cta + 1, p.units_q, p.units_r);
+    const int u0 = gemv_first_unit(cta, p.units_q, p.units_r);
+    const int u1 = gemv_first_unit(cta + 1, p.units_q, p.units_r);
     const int rows = p.a.rows;
 
     if (threadIdx.x == 0) {
@@ -133,15 +134,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             int s = 0;
             uint32_t wait_parity = 1;              // parity of the empty-barrier phase awaited in the current lap
             bool first_lap = true;
-            for (long long u = u0; u < u1; u += p.units_per_stage) {
+            for (int u = u0; u < u1; u += p.units_per_stage) {
                 if (!first_lap && !ptx::mbar_wait(&empty[s], wait_parity)) {
                     atomicExch(p.a.err, GEMV_ERR_EMPTY_WAIT);
                     break;
                 }
-                const long long left = u1 - u;
+                const int left = u1 - u;
                 const uint32_t bytes = (uint32_t)(left < p.units_per_stage ? left : p.units_per_stage) * W_BYTES;
                 ptx::mbar_arrive_expect_tx(&full[s], bytes);
-                ptx::bulk_g2s(stage0 + (size_t)s * p.stage_stride, p.a.packed + u * (512ll * K), bytes, &full[s]);
+                ptx::bulk_g2s(stage0 + (size_t)s * p.stage_stride, p.a.packed + (long long)u * (512 * K), bytes, &full[s]);
                 if (++s == p.stages) {
                     s = 0;
                     if (first_lap) { first_lap = false; wait_parity = 0; } else wait_parity ^= 1;
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 
     const uint32_t stage0_addr = ptx::smem_addr(stage0);
     const uint32_t w_off = (uint32_t)((nt * 2 + kq) * K) * 128u + lane * 4u;
-    int nb = (int)(u0 / p.KG), kg = (int)(u0 % p.KG);
+    int nb = (int)((unsigned)u0 / (unsigned)p.KG), kg = u0 - nb * p.KG;
 
     // P -> out for column block fnb: one warp per batch row applies Had128 * svh (or stores the rotated-basis product).
     auto epilogue = [&](int fnb) {
@@ -229,7 +230,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             }
             ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
         }
-        const long long ub = (long long)fnb * p.KG;
+        const int ub = fnb * p.KG;
         const int c_first = gemv_cta_of_unit(ub, p.units_q, p.units_r);
         const int c_last = gemv_cta_of_unit(ub + p.KG - 1, p.units_q, p.units_r);
         bool finish = true;
@@ -291,7 +292,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         unsigned char* xs = smem + p.xs_off;
         uint32_t* slots = reinterpret_cast<uint32_t*>(xs + GEMV_XS_ZERO_BYTES);
         if (threadIdx.x < GEMV_XS_ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xs)[threadIdx.x] = 0u;
-        const int items = (int)(u1 - u0) * XR;
+        const int items = (u1 - u0) * XR;
         const bool bf16 = p.a.x_bf16 != 0;
         constexpr int BATCH = 3;                      // rotations in flight per warp: their loads overlap
         bool waited = false;
@@ -304,8 +305,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 xi[b] = 0;
                 if (it < items) {
                     const int i = it / XR, row = it % XR;
-                    const long long u = u0 + i;
-                    const int unb = (int)(u / p.KG), ukg = (int)(u - (long long)unb * p.KG);
+                    const unsigned u = (unsigned)(u0 + i);
+                    const int unb = (int)(u / (unsigned)p.KG), ukg = (int)(u - (unsigned)unb * (unsigned)p.KG);
                     int s = 0;
                     while (s < p.a.n_shards - 1 && unb >= p.a.shard_end_blocks[s]) s++;
                     const long long col = (long long)ukg * 128 + 4 * lane;
@@ -384,7 +385,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         for (int mb = 0; mb < MB; mb++)
             xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems + (uint32_t)kg * x_unit[mb] : 0u);
     }
-    int remaining = (int)(u1 - u0);
+    int remaining = u1 - u0;
     if (remaining > 0) wait_stage(0, 0);
 
     while (remaining > 0) {

@@ -97,6 +97,25 @@ size_t allreduce_region_bytes(size_t max_elems);
 int launch_allreduce(void* data, int bf16, size_t n, void* const* peer_bases_host, int rank, int world, size_t max_elems, int* state,
                      cudaStream_t st);
 
+// Launch with programmatic stream serialization: the kernel may become resident while the kernel ahead of it in the stream
+// is still finishing.  Every kernel launched this way executes griddepcontrol.wait before it touches global memory that
+// is not constant, and does so in every thread (also those that leave early), so completion stays ordered along the stream.
+template <typename... KArgs, typename... Args>
+inline int launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
 // Workspace carved up identically by every entry point that takes one.
 struct WorkspaceLayout {
     size_t err_off, counters_off, xf_off, partials_off, total;

@@ -15,6 +15,8 @@ namespace exl3 {
 __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int numel, int E, int block, int cap, int* __restrict__ sorted_ids,
                                  int* __restrict__ expert_ids, int* __restrict__ num_post)
 {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     extern __shared__ int sh[];
     int* count = sh;              // [E]
     int* offset = sh + E;         // [E + 1]
@@ -29,14 +31,43 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int numel, in
         if (e >= 0 && e < E) atomicAdd(&count[e], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int at = 0;
-        for (int e = 0; e < E; e++) {
-            offset[e] = at;
-            at += (count[e] + block - 1) / block * block;
+    // Exclusive prefix sum of the padded counts: warp scans by shuffle, warp totals through shared memory; experts are
+    // taken in chunks of blockDim.x with a running carry.
+    __shared__ int warp_total[32];
+    __shared__ int carry_sh;
+    if (threadIdx.x == 0) carry_sh = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e0 = 0; e0 < E; e0 += blockDim.x) {
+        const int e = e0 + threadIdx.x;
+        const int padded = e < E ? (count[e] + block - 1) / block * block : 0;
+        int incl = padded;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += up;
         }
-        offset[E] = at;
-        *num_post = at;
+        if (lane == 31) warp_total[wid] = incl;
+        __syncthreads();
+        if (wid == 0) {
+            int t = lane < nwarps ? warp_total[lane] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xFFFFFFFFu, t, d);
+                if (lane >= d) t += up;
+            }
+            warp_total[lane] = t;                      // inclusive totals of the warps
+        }
+        __syncthreads();
+        const int base = carry_sh + (wid > 0 ? warp_total[wid - 1] : 0);
+        if (e < E) offset[e] = base + incl - padded;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry_sh = base + incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        offset[E] = carry_sh;
+        *num_post = carry_sh;
     }
     __syncthreads();
     const int total = offset[E];
@@ -82,6 +113,8 @@ __global__ void moe_had_in_kernel(const void* __restrict__ x, int x_bf16, const 
                                   int numel, int cap, const int* __restrict__ sorted_ids, const int* __restrict__ expert_ids,
                                   const int* __restrict__ num_post, uint32_t* __restrict__ xf)
 {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const int kgs = hidden >> 7, KT = hidden >> 4;
     const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -121,6 +154,8 @@ __global__ void moe_glu_had_in_kernel(const __half* __restrict__ gu, const __hal
                                       const int* __restrict__ sorted_ids, const int* __restrict__ expert_ids,
                                       const int* __restrict__ num_post, uint32_t* __restrict__ xf)
 {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const int kgs = inter >> 7, KT = inter >> 4;
     const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -158,6 +193,8 @@ __global__ void moe_glu_had_in_kernel(const __half* __restrict__ gu, const __hal
 __global__ void moe_combine_kernel(const __half* __restrict__ yd, const float* __restrict__ w, const int* __restrict__ topk_ids, int tokens,
                                    int top_k, int hidden, int E, void* __restrict__ y, int y_bf16)
 {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;       // one thread per (token, 2 columns)
     const int half_h = hidden >> 1;
     if (idx >= (long long)tokens * half_h) return;
@@ -205,8 +242,8 @@ static inline unsigned blocks_for(long long items, int per_block) { return (unsi
 int launch_moe_align(const int* topk_ids, int numel, int E, int block, int cap, int* sorted_ids, int* expert_ids, int* num_post,
                      cudaStream_t st)
 {
-    moe_align_kernel<<<1, 1024, (3 * E + 1) * sizeof(int), st>>>(topk_ids, numel, E, block, cap, sorted_ids, expert_ids, num_post);
-    return cuda_status(cudaGetLastError());
+    return launch_chained(moe_align_kernel, dim3(1), dim3(1024), (3 * E + 1) * sizeof(int), st, topk_ids, numel, E, block, cap, sorted_ids, expert_ids,
+                          num_post);
 }
 
 int launch_moe_had_in(const void* x, int x_bf16, const __half* suh, int shards, int hidden, int top_k, int numel, int cap,
@@ -214,13 +251,9 @@ int launch_moe_had_in(const void* x, int x_bf16, const __half* suh, int shards, 
 {
     const long long items = (long long)shards * cap * (hidden / 128);
     if (items == 0) return EXL3_OK;
-    if (mode == GEMV_SPLIT)
-        moe_had_in_kernel<GEMV_SPLIT><<<blocks_for(items, 8), 256, 0, st>>>(x, x_bf16, suh, shards, hidden, top_k, numel, cap, sorted_ids,
-                                                                           expert_ids, num_post, xf);
-    else
-        moe_had_in_kernel<GEMV_PAIRED><<<blocks_for(items, 8), 256, 0, st>>>(x, x_bf16, suh, shards, hidden, top_k, numel, cap, sorted_ids,
-                                                                            expert_ids, num_post, xf);
-    return cuda_status(cudaGetLastError());
+    auto kernel = mode == GEMV_SPLIT ? moe_had_in_kernel<GEMV_SPLIT> : moe_had_in_kernel<GEMV_PAIRED>;
+    return launch_chained(kernel, dim3(blocks_for(items, 8)), dim3(256), 0, st, x, x_bf16, suh, shards, hidden, top_k, numel, cap, sorted_ids,
+                          expert_ids, num_post, xf);
 }
 
 int launch_moe_glu_had_in(const __half* gu, const __half* suh2, int inter, int numel, int cap, const int* sorted_ids,
@@ -228,11 +261,8 @@ int launch_moe_glu_had_in(const __half* gu, const __half* suh2, int inter, int n
 {
     const long long items = (long long)cap * (inter / 128);
     if (items == 0) return EXL3_OK;
-    if (mode == GEMV_SPLIT)
-        moe_glu_had_in_kernel<GEMV_SPLIT><<<blocks_for(items, 8), 256, 0, st>>>(gu, suh2, inter, numel, cap, sorted_ids, expert_ids, num_post, xf);
-    else
-        moe_glu_had_in_kernel<GEMV_PAIRED><<<blocks_for(items, 8), 256, 0, st>>>(gu, suh2, inter, numel, cap, sorted_ids, expert_ids, num_post, xf);
-    return cuda_status(cudaGetLastError());
+    auto kernel = mode == GEMV_SPLIT ? moe_glu_had_in_kernel<GEMV_SPLIT> : moe_glu_had_in_kernel<GEMV_PAIRED>;
+    return launch_chained(kernel, dim3(blocks_for(items, 8)), dim3(256), 0, st, gu, suh2, inter, numel, cap, sorted_ids, expert_ids, num_post, xf);
 }
 
 int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, int tokens, int top_k, int hidden, int E, void* y,
@@ -240,8 +270,7 @@ int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, in
 {
     const long long items = (long long)tokens * (hidden / 2);
     if (items == 0) return EXL3_OK;
-    moe_combine_kernel<<<blocks_for(items, 256), 256, 0, st>>>(yd, w, topk_ids, tokens, top_k, hidden, E, y, y_bf16);
-    return cuda_status(cudaGetLastError());
+    return launch_chained(moe_combine_kernel, dim3(blocks_for(items, 256)), dim3(256), 0, st, yd, w, topk_ids, tokens, top_k, hidden, E, y, y_bf16);
 }
 
 int launch_moe_gemm(MoeGemmLaunch l, int K, int codebook, int mode, cudaStream_t st)

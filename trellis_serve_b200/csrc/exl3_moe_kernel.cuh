@@ -56,13 +56,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kerne
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x;
-    const int UB = p.NB * p.KG;                                  // units per moe block
-    const int nblocks = *p.num_post / MOE_BLOCK_ROWS;
-    const long long total = (long long)nblocks * UB;
-    const int units_q = (int)(total / gridDim.x), units_r = (int)(total % gridDim.x);
-    const long long u0 = gemv_first_unit(cta, units_q, units_r);
-    const long long u1 = gemv_first_unit(cta + 1, units_q, units_r);
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             ptx::mbar_init(&full[s], 1);
@@ -72,6 +65,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kerne
         ptx::mbar_fence_init();
     }
     __syncthreads();
+    // The routing lists come from kernels ahead of this one in the stream: nothing is read before they have finished.
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const int UB = p.NB * p.KG;                                  // units per moe block
+    const int nblocks = *p.num_post / MOE_BLOCK_ROWS;
+    const long long total = (long long)nblocks * UB;
+    const int units_q = (int)(total / gridDim.x), units_r = (int)(total % gridDim.x);
+    const long long u0 = gemv_first_unit(cta, units_q, units_r);
+    const long long u1 = gemv_first_unit(cta + 1, units_q, units_r);
     if (u0 >= u1) return;
 
     // position of the first unit: moe block, unit inside the block
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kerne
                 int n = p.units_per_stage;
                 if (n > UB - in_blk) n = UB - in_blk;          // a stage never crosses into the next expert's matrix
                 if (n > left) n = (int)left;
-                if (!first_lap && !ptx::mbar_wait_relaxed(&empty[s], wait_parity)) {
+                if (!first_lap && !ptx::mbar_wait(&empty[s], wait_parity)) {
                     atomicExch(p.err, GEMV_ERR_EMPTY_WAIT);
                     break;
                 }
@@ -154,9 +156,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kerne
         if (c_first != c_last) {
             float* slot = p.partials + (size_t)(cta + gb) * nelem;
             for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) slot[e] = P[e];
-            __threadfence();
             ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
             if (tid == 0) {
+                __threadfence();          // publishes every thread's stores (ordered before it by the barrier) ahead of the counter
                 const int old = atomicAdd(&p.counters[gb], 1);
                 const int last = (old == c_last - c_first);
                 if (last) p.counters[gb] = 0;
@@ -202,58 +204,68 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kerne
 
     int slot = 0, in_stage = 0;
     uint32_t phase = 0;
-    long long left = u1 - u0;
+    int left = (int)(u1 - u0);
     int stage_units = p.units_per_stage;
     if (stage_units > UB - in_blk) stage_units = UB - in_blk;
-    if (stage_units > left) stage_units = (int)left;
+    if (stage_units > left) stage_units = left;
     uint32_t waddr = stage0_addr + w_off;
     const Frag* xbase = reinterpret_cast<const Frag*>(p.xf);
     const uint32_t lane_elem = (uint32_t)(g * 4 + q) + (uint32_t)(kq * 4) * 32u;
     bool dirty = false;
     wait_stage(0, 0);
 
+    // Runs of units that end where something has to happen (stage used up, column block finished, range finished);
+    // inside a run only the two read addresses advance.
     while (left > 0) {
-        uint32_t L[K];
-#pragma unroll
-        for (int i = 0; i < K; i++) L[i] = ptx::lds32(waddr + i * 128u);
+        int run = p.KG - kg;
+        if (run > stage_units - in_stage) run = stage_units - in_stage;
+        if (run > left) run = left;
         const uint32_t shard = nb >= p.shard_end_block ? 1u : 0u;
         const Frag* xp = xbase + (shard * p.xf_shard_stride + ((long long)b * KT + kg * 8) * 32 + lane_elem);
-        Frag bfrag[4];
-#pragma unroll
-        for (int T = 0; T < 4; T++) bfrag[T] = __ldg(xp + T * 32);
-
-        auto tile = [&](auto tconst) {
-            constexpr int T = decltype(tconst)::value;
-            uint32_t own[2];
-            own_words<K, T>(L, own);
-            const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
-            const LaneRegs<K> R = lane_regs<K>(own, prev0);
-            uint32_t w[8];
-            decode_tile_regs<K, MODE, FAM>(R, p.pw, cbc, w);
-            if constexpr (MODE == GEMV_SPLIT) {
-                const uint4 bb = bfrag[T];
-                ptx::mma_m16n8k16(acc, w[0], w[4], w[1], w[5], bb.x, bb.y);
-                ptx::mma_m16n8k16(acc, w[2], w[6], w[3], w[7], bb.z, bb.w);
-            } else {
-                const uint2 bb = bfrag[T];
-                ptx::mma_m16n8k16(acc, w[0], w[2], w[1], w[3], bb.x, bb.y);
-            }
-        };
-        tile(std::integral_constant<int, 0>{});
-        tile(std::integral_constant<int, 1>{});
-        tile(std::integral_constant<int, 2>{});
-        tile(std::integral_constant<int, 3>{});
-
-        left--;
-        in_blk++;
-        waddr += W_BYTES;
+        left -= run;
+        in_blk += run;
+        in_stage += run;
+        kg += run;
         dirty = true;
-        const bool stage_done = (++in_stage == stage_units);
+#pragma unroll 1
+        for (; run > 0; run--) {
+            uint32_t L[K];
+#pragma unroll
+            for (int i = 0; i < K; i++) L[i] = ptx::lds32(waddr + i * 128u);
+            Frag bfrag[4];
+#pragma unroll
+            for (int T = 0; T < 4; T++) bfrag[T] = __ldg(xp + T * 32);
+
+            auto tile = [&](auto tconst) {
+                constexpr int T = decltype(tconst)::value;
+                uint32_t own[2];
+                own_words<K, T>(L, own);
+                const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
+                const LaneRegs<K> R = lane_regs<K>(own, prev0);
+                uint32_t w[8];
+                decode_tile_regs<K, MODE, FAM>(R, p.pw, cbc, w);
+                if constexpr (MODE == GEMV_SPLIT) {
+                    const uint4 bb = bfrag[T];
+                    ptx::mma_m16n8k16(acc, w[0], w[4], w[1], w[5], bb.x, bb.y);
+                    ptx::mma_m16n8k16(acc, w[2], w[6], w[3], w[7], bb.z, bb.w);
+                } else {
+                    const uint2 bb = bfrag[T];
+                    ptx::mma_m16n8k16(acc, w[0], w[2], w[1], w[3], bb.x, bb.y);
+                }
+            };
+            tile(std::integral_constant<int, 0>{});
+            tile(std::integral_constant<int, 1>{});
+            tile(std::integral_constant<int, 2>{});
+            tile(std::integral_constant<int, 3>{});
+            waddr += W_BYTES;
+            xp += 8 * 32;
+        }
+        const bool stage_done = in_stage == stage_units;
         if (stage_done) {
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty[slot]);
         }
-        if (++kg == p.KG) {                                      // column block of this moe block finished
+        if (kg == p.KG) {                                        // column block of this moe block finished
             flush();
             dirty = false;
             kg = 0;
@@ -271,7 +283,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kerne
             }
             stage_units = p.units_per_stage;
             if (stage_units > UB - in_blk) stage_units = UB - in_blk;
-            if (stage_units > left) stage_units = (int)left;
+            if (stage_units > left) stage_units = left;
             waddr = stage0_addr + (uint32_t)slot * p.stage_stride + w_off;
             wait_stage(slot, phase);
         }
