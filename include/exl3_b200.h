@@ -168,6 +168,12 @@ int exl3_moe_block_rows(void);
 size_t exl3_moe_sorted_capacity(int slots, int num_experts);
 exl3_status exl3_moe_align(const int32_t *topk_ids, int slots, int num_experts, int32_t *sorted_ids, int cap, int32_t *expert_ids,
                            int32_t *num_post, void *stream);
+/* Alignment for one bitrate class of a mixed-K expert set (moe_align_decode with its expert_map list,
+ * cuda/src/sglang_exl3/kernels/marlin_moe.py:195-213): expert_map is int32 [num_experts], global id -> id in
+ * [0, num_local) or -1; slots of other classes are dropped, expert_ids come out local.  cap >=
+ * exl3_moe_sorted_capacity(slots, num_local). */
+exl3_status exl3_moe_align_mapped(const int32_t *topk_ids, int slots, int num_experts, const int32_t *expert_map, int num_local,
+                                  int32_t *sorted_ids, int cap, int32_t *expert_ids, int32_t *num_post, void *stream);
 size_t exl3_moe_fragment_bytes(int cap, int k, int shards, int codebook);
 exl3_status exl3_moe_had_in(const void *x, int x_dtype, const uint16_t *suh, int shards, int hidden, int top_k, int slots,
                             const int32_t *sorted_ids, int cap, const int32_t *expert_ids, const int32_t *num_post, int codebook,

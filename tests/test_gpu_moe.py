@@ -141,3 +141,45 @@ def test_no_tokens_and_unsupported_packs():
     assert moe.supports(g[0], u[0], d[0], 0) == (True, "")
     ok, why = moe.supports(g[0], u[0], d[0][:1] + [torch.zeros((8, 16, 48), dtype=torch.int16, device=DEV)], 0)
     assert not ok and "differ" in why
+
+
+def _mixed_experts(seed, Ks, hidden, inter):
+    """Experts whose bitrate differs (Ks[e] per expert): the three projections of an expert share its K."""
+    gate, up, down = ([], [], []), ([], [], []), ([], [], [])
+    for e, K in enumerate(Ks):
+        g, u, d = _experts(seed + 31 * e, 1, hidden, inter, K)
+        for dst, src in ((gate, g), (up, u), (down, d)):
+            for j in range(3):
+                dst[j].append(src[j][0])
+    return gate, up, down
+
+
+@pytest.mark.parametrize("tokens,zipf", [(1, False), (9, False), (24, True)])
+def test_mixed_bitrate_layer_matches_the_float64_reference(tokens, zipf):
+    """Mixed-K expert set (the reference's MixedPack): per-class alignment with an expert map, shared slabs, one combine."""
+    Ks = [3, 4, 3, 3, 4, 3, 4, 3, 3, 3, 4, 3]
+    E, hidden, inter, top_k, cb = len(Ks), 256, 128, 3, 0
+    gate, up, down = _mixed_experts(7000, Ks, hidden, inter)
+    pack = moe.prepare_mixed(_to_dev(gate), _to_dev(up), _to_dev(down), cb)
+    assert pack.bits == [3, 4] and [p.num_experts for p in pack.packs] == [8, 4] and pack.num_experts == E
+    assert [m.tolist() for m in pack.expert_ids] == [[e for e in range(E) if Ks[e] == 3], [e for e in range(E) if Ks[e] == 4]]
+    ids, w = _routing(tokens, top_k, E, 90 + tokens, zipf)
+    x = np.random.default_rng(tokens).standard_normal((tokens, hidden)).astype(np.float16)
+    xt, wt, it = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV), torch.from_numpy(ids).to(DEV)
+    routings = moe.align_decode(it, pack, tokens, top_k)
+    torch.cuda.synchronize()
+    flat = ids.reshape(-1)
+    for (s, e, n, block), emap in zip(routings, pack.expert_maps):          # each class sees exactly its own slots
+        n_post, s_np, m = int(n.item()), s.cpu().numpy(), emap.cpu().numpy()
+        valid = s_np[:n_post][s_np[:n_post] < flat.size]
+        assert block == 8 and np.array_equal(np.sort(valid), np.nonzero(m[flat] >= 0)[0])
+        for i, slot in enumerate(s_np[:n_post]):
+            if slot < flat.size:
+                assert m[flat[slot]] == e.cpu().numpy()[i // 8]
+    y = moe.run_mixed(xt, wt, it, routings, pack)
+    torch.cuda.synchronize()
+    ref = orc.np_moe_layer(x, ids, w, gate, up, down, Ks, cb)
+    got = y.float().cpu().numpy()
+    assert orc.rel_norm(got, ref) <= 3e-3, orc.rel_norm(got, ref)
+    assert orc.max_over_rms(got, ref) <= 8e-3, orc.max_over_rms(got, ref)
+    assert torch.equal(moe.forward_mixed(xt, wt, it, pack), y)              # deterministic, alignment included

@@ -44,6 +44,7 @@ SIGNATURES = {
     "exl3_moe_block_rows": (_i, []),
     "exl3_moe_sorted_capacity": (_sz, [_i, _i]),
     "exl3_moe_align": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp]),
+    "exl3_moe_align_mapped": (_i, [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp]),
     "exl3_moe_fragment_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_moe_had_in": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp]),
     "exl3_moe_glu_had_in": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp]),

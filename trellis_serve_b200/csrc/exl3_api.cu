@@ -347,7 +347,20 @@ exl3_status exl3_moe_align(const int32_t* topk_ids, int slots, int num_experts, 
     if ((size_t)cap < exl3_moe_sorted_capacity(slots, num_experts)) return EXL3_ERR_BAD_SHAPE;
     if (!aligned(num_post, 4) || (slots > 0 && !aligned(topk_ids, 4)) || (cap > 0 && (!aligned(sorted_ids, 4) || !aligned(expert_ids, 4))))
         return EXL3_ERR_BAD_POINTER;
-    return launch_moe_align(topk_ids, slots, num_experts, MOE_BLOCK_ROWS, cap, sorted_ids, expert_ids, num_post, (cudaStream_t)stream);
+    return launch_moe_align(topk_ids, slots, num_experts, MOE_BLOCK_ROWS, cap, sorted_ids, expert_ids, num_post, nullptr, 0,
+                            (cudaStream_t)stream);
+}
+
+exl3_status exl3_moe_align_mapped(const int32_t* topk_ids, int slots, int num_experts, const int32_t* expert_map, int num_local,
+                                  int32_t* sorted_ids, int cap, int32_t* expert_ids, int32_t* num_post, void* stream)
+{
+    if (slots < 0 || num_experts < 1 || num_local < 1 || num_local > 4096 || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
+    if ((size_t)cap < exl3_moe_sorted_capacity(slots, num_local)) return EXL3_ERR_BAD_SHAPE;
+    if (!expert_map || !aligned(expert_map, 4) || !aligned(num_post, 4) || (slots > 0 && !aligned(topk_ids, 4)) ||
+        (cap > 0 && (!aligned(sorted_ids, 4) || !aligned(expert_ids, 4))))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_moe_align(topk_ids, slots, num_local, MOE_BLOCK_ROWS, cap, sorted_ids, expert_ids, num_post, expert_map, num_experts,
+                            (cudaStream_t)stream);
 }
 
 size_t exl3_moe_fragment_bytes(int cap, int k, int shards, int codebook)

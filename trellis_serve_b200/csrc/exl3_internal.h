@@ -79,7 +79,7 @@ int gemv_init_device();
 struct MoeGemmLaunch;
 int moe_init_device();
 int launch_moe_align(const int* topk_ids, int numel, int E, int block, int cap, int* sorted_ids, int* expert_ids, int* num_post,
-                     cudaStream_t st);
+                     const int* expert_map, int E_global, cudaStream_t st);
 int launch_moe_had_in(const void* x, int x_bf16, const __half* suh, int shards, int hidden, int top_k, int numel, int cap,
                       const int* sorted_ids, const int* expert_ids, const int* num_post, uint32_t* xf, int mode, cudaStream_t st);
 int launch_moe_glu_had_in(const __half* gu, const __half* suh2, int inter, int numel, int cap, const int* sorted_ids,

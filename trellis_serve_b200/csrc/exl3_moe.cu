@@ -12,8 +12,18 @@ namespace exl3 {
 // One CTA.  Slots (token, k) are grouped by expert into blocks of `block` rows: sorted_ids holds the slot of every
 // row (numel = padding), expert_ids the expert of every block, num_post the padded row count.  Ids outside
 // [0, E) are dropped.  The order of slots inside an expert is not specified (rows are independent).
+// With expert_map (int [E_global]: global id -> id in [0, E), or -1) the ids are translated first, so one class of a
+// mixed-bitrate expert set gets the blocks of its own slots only, with local expert ids.
+__device__ __forceinline__ int moe_mapped_id(const int* topk_ids, int i, const int* expert_map, int E_global)
+{
+    const int e = topk_ids[i];
+    if (!expert_map) return e;
+    return (e >= 0 && e < E_global) ? expert_map[e] : -1;
+}
+
 __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int numel, int E, int block, int cap, int* __restrict__ sorted_ids,
-                                 int* __restrict__ expert_ids, int* __restrict__ num_post)
+                                 int* __restrict__ expert_ids, int* __restrict__ num_post, const int* __restrict__ expert_map,
+                                 int E_global)
 {
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
@@ -27,7 +37,7 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int numel, in
     }
     __syncthreads();
     for (int i = threadIdx.x; i < numel; i += blockDim.x) {
-        const int e = topk_ids[i];
+        const int e = moe_mapped_id(topk_ids, i, expert_map, E_global);
         if (e >= 0 && e < E) atomicAdd(&count[e], 1);
     }
     __syncthreads();
@@ -77,7 +87,7 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int numel, in
     for (int i = total / block + threadIdx.x; i < cap / block; i += blockDim.x) expert_ids[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < numel; i += blockDim.x) {
-        const int e = topk_ids[i];
+        const int e = moe_mapped_id(topk_ids, i, expert_map, E_global);
         if (e >= 0 && e < E) sorted_ids[offset[e] + atomicAdd(&fill[e], 1)] = i;
     }
 }
@@ -240,10 +250,10 @@ int moe_init_device()
 static inline unsigned blocks_for(long long items, int per_block) { return (unsigned)((items + per_block - 1) / per_block); }
 
 int launch_moe_align(const int* topk_ids, int numel, int E, int block, int cap, int* sorted_ids, int* expert_ids, int* num_post,
-                     cudaStream_t st)
+                     const int* expert_map, int E_global, cudaStream_t st)
 {
     return launch_chained(moe_align_kernel, dim3(1), dim3(1024), (3 * E + 1) * sizeof(int), st, topk_ids, numel, E, block, cap, sorted_ids, expert_ids,
-                          num_post);
+                          num_post, expert_map, E_global);
 }
 
 int launch_moe_had_in(const void* x, int x_bf16, const __half* suh, int shards, int hidden, int top_k, int numel, int cap,

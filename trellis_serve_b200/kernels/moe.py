@@ -15,7 +15,7 @@ expert (`BLOCK_SIZES`); `align` here produces the (sorted_ids, expert_ids, num_p
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -105,6 +105,72 @@ def prepare(gate, up, down, codebook: int) -> ExpertPack:
     return ExpertPack(w13, w2, suh13, svh13, suh2, svh2, codebook, hidden, inter, w13.shape[0], bits_of_stack(w13))
 
 
+@dataclass
+class MixedPack:
+    """Experts of mixed K (e.g. 192 experts at K = 3 and 64 at K = 4 in one layer), the reference's `MixedPack`
+    (marlin_moe.py:135-161): one ExpertPack per bitrate class in LOCAL expert order and, per class, the map global id ->
+    local id (-1 elsewhere).  Every slot belongs to exactly one class, so the classes' grouped GEMVs together fill the
+    shared gate|up and down slabs; one router-weighted combine closes the layer."""
+    packs: list[ExpertPack]
+    expert_maps: list[torch.Tensor]     # int32 [E] per class: global id -> local id, -1 elsewhere
+    num_experts: int
+    hidden: int
+    inter: int
+    codebook: int
+    expert_ids: list[torch.Tensor] = field(default_factory=list)    # int32 [E_c] per class: local id -> global id
+
+    def __post_init__(self):
+        if not self.expert_ids:
+            self.expert_ids = [(m >= 0).nonzero().flatten().to(torch.int32).contiguous() for m in self.expert_maps]
+
+    @property
+    def bits(self) -> list[int]:
+        return [p.bits for p in self.packs]
+
+    def block_sizes(self, tokens: int, top_k: int) -> list[int]:
+        return [moe_block_size(tokens, top_k, p.num_experts) for p in self.packs]
+
+
+def prepare_mixed(gate, up, down, codebook: int) -> MixedPack:
+    """Like `prepare`, for experts of mixed K (marlin_moe.py:164-181): experts are grouped by their bitrate."""
+    words = [w.shape[2] for w in gate[0]]
+    classes = sorted(set(words))
+    e = len(words)
+    packs, maps = [], []
+    for wd in classes:
+        ids = [i for i in range(e) if words[i] == wd]
+        sub = lambda t: tuple([t[j][i] for i in ids] for j in range(3))
+        packs.append(prepare(sub(gate), sub(up), sub(down), codebook))
+        m = torch.full((e,), -1, dtype=torch.int32)
+        m[ids] = torch.arange(len(ids), dtype=torch.int32)
+        maps.append(m.to(packs[-1].w13.device))
+    return MixedPack(packs, maps, e, packs[0].hidden, packs[0].inter, codebook)
+
+
+def align_capacity(slots: int, num_experts_class: int, block: int = 8) -> int:
+    """Length of sorted_ids for one class (marlin_moe.py:186-192 gives the engine's bound; this is the library's)."""
+    return int(_lib.load().exl3_moe_sorted_capacity(slots, num_experts_class))
+
+
+def align_decode(topk_ids: torch.Tensor, pack: MixedPack, tokens: int, top_k: int) -> list[tuple]:
+    """Routings for run_mixed (marlin_moe.py:195-213): per class (sorted_ids, expert_ids, num_post, block) over that
+    class's slots only, expert ids local to the class."""
+    _require_cuda(topk_ids, "topk_ids")
+    lib = _lib.load()
+    ids = topk_ids.reshape(-1).to(torch.int32).contiguous()
+    out = []
+    with torch.cuda.device(ids.device):
+        for pk, emap in zip(pack.packs, pack.expert_maps):
+            cap = align_capacity(ids.numel(), pk.num_experts)
+            sorted_ids = torch.empty((cap,), dtype=torch.int32, device=ids.device)
+            expert_ids = torch.empty((max(cap // 8, 1),), dtype=torch.int32, device=ids.device)
+            num_post = torch.empty((1,), dtype=torch.int32, device=ids.device)
+            _lib.check(lib.exl3_moe_align_mapped(_ptr(ids), ids.numel(), pack.num_experts, _ptr(emap), pk.num_experts, _ptr(sorted_ids),
+                                                 cap, _ptr(expert_ids), _ptr(num_post), _stream(ids.device)), "exl3_moe_align_mapped")
+            out.append((sorted_ids, expert_ids, num_post, 8))
+    return out
+
+
 def _reserve(device: torch.device, nbytes: int) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     cur = _workspace.get(idx)
@@ -176,6 +242,48 @@ def run_tensors(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padd
         _lib.check(lib.exl3_moe_combine(_ptr(yd), _ptr(wts), _ptr(ids32), tokens, top_k, hidden, w13.shape[0], _ptr(y),
                                         _dtype_code(y), st), "exl3_moe_combine")
     return y
+
+
+def run_mixed(x, topk_weights, topk_ids, routings, pack: MixedPack, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One MoE layer over experts of mixed K (marlin_moe.py:247-269).  routings = `align_decode(...)`.  Per class the
+    input rotation uses the class's own sign vectors and routing, the grouped GEMVs write that class's slots of the
+    shared gate|up and down slabs, and one combine over all slots closes the layer."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
+    tokens, hidden = x.shape
+    top_k, inter = topk_ids.shape[1], pack.inter
+    slots = tokens * top_k
+    y = out if out is not None else torch.empty_like(x)
+    if tokens == 0:
+        return y
+    dev, st = x.device, _stream(x.device)
+    ids32 = topk_ids.reshape(-1).to(torch.int32).contiguous()
+    wts = topk_weights.reshape(-1).to(torch.float32).contiguous()
+    gu = torch.empty((slots, 2 * inter), dtype=torch.float16, device=dev)
+    yd = torch.empty((slots, hidden), dtype=torch.float16, device=dev)
+    for pk, (sorted_ids, expert_ids, num_post, block) in zip(pack.packs, routings):
+        if block != 8:
+            raise RuntimeError(f"the grouped GEMV works on 8-row moe blocks, got block = {block}")
+        cap = sorted_ids.numel()
+        xf13 = torch.empty(int(lib.exl3_moe_fragment_bytes(cap, hidden, 2, pk.codebook)), dtype=torch.uint8, device=dev)
+        xf2 = torch.empty(int(lib.exl3_moe_fragment_bytes(cap, inter, 1, pk.codebook)), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.exl3_moe_had_in(_ptr(x), _dtype_code(x), _ptr(pk.suh13), 2, hidden, top_k, slots, _ptr(sorted_ids), cap,
+                                           _ptr(expert_ids), _ptr(num_post), pk.codebook, _ptr(xf13), st), "exl3_moe_had_in")
+        gemm_rotated(xf13, pk.w13, gu, sorted_ids, expert_ids, num_post, slots, inter, pk.codebook, pk.svh13)
+        with torch.cuda.device(dev):
+            _lib.check(lib.exl3_moe_glu_had_in(_ptr(gu), _ptr(pk.suh2), inter, slots, _ptr(sorted_ids), cap, _ptr(expert_ids),
+                                               _ptr(num_post), pk.codebook, _ptr(xf2), st), "exl3_moe_glu_had_in")
+        gemm_rotated(xf2, pk.w2, yd, sorted_ids, expert_ids, num_post, slots, 0, pk.codebook, pk.svh2)
+    with torch.cuda.device(dev):
+        _lib.check(lib.exl3_moe_combine(_ptr(yd), _ptr(wts), _ptr(ids32), tokens, top_k, hidden, pack.num_experts, _ptr(y),
+                                        _dtype_code(y), st), "exl3_moe_combine")
+    return y
+
+
+def forward_mixed(x, topk_weights, topk_ids, pack: MixedPack, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Whole mixed-K layer including the per-class routing alignment."""
+    return run_mixed(x, topk_weights, topk_ids, align_decode(topk_ids, pack, x.shape[0], topk_ids.shape[1]), pack, out)
 
 
 def run(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block: int, pack: ExpertPack,
