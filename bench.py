@@ -263,7 +263,7 @@ def main() -> None:
     ap.add_argument("--bits", type=int, default=3)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "peer", "nccl"],
                     help="exchange step of row-parallel layers at N > 1: the library's one-shot peer-memory kernel, or NCCL")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
                     help="decode = the headline 27B-shape layer set (default); prefill / moe = secondary single-GPU workloads")
@@ -297,10 +297,11 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
     K, cb = args.bits, 0
     reducer = None
-    if world > 1 and args.allreduce == "peer":
+    if world > 1 and args.allreduce in ("peer", "fused"):
         from trellis_serve_b200.runtime.allreduce import PeerAllReduce
         reducer = PeerAllReduce(dev, 16 * 5120)
-    ls = DecodeLayerSet(args.layers, K, cb, args.rows, tp_rank=rank, tp_size=world, device=dev, allreduce=reducer)
+    ls = DecodeLayerSet(args.layers, K, cb, args.rows, tp_rank=rank, tp_size=world, device=dev, allreduce=reducer,
+                        fused_exchange=args.allreduce == "fused")
     gen = torch.Generator(device=dev)
     gen.manual_seed(7 + rank)
     for buf in (ls.x_hidden, ls.x_attn, ls.x_ffn):

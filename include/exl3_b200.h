@@ -132,15 +132,25 @@ exl3_status exl3_gemm_rotated(const uint16_t *xh, const uint32_t *packed, int K,
 /* ---- tensor-parallel exchange step -------------------------------------------------------------------------
  * Row-parallel shards (o_proj, down_proj) produce partial sums (core/src/trellis_core/format/geometry.py:62-66); this
  * adds them over the ranks of one node, in place, with one latency-bound kernel over peer-mapped memory (ordinary peer
- * loads and stores over NVLink, no multicast).  The reference itself has no collective (tensor parallelism is refused
+ * stores over NVLink of words tagged with the call number, polled for at the receiver; no multicast).  The reference itself has no collective (tensor parallelism is refused
  * at cuda/src/sglang_exl3/sglang_glue/linear.py:74-75).
  *   peer_regions (host array of `world` device pointers): every rank's symmetric region of
  *     exl3_allreduce_region_bytes(max_elems) bytes, zero-filled once, mapped into this process (peer_regions[rank] is
- *     this rank's own); state: 2 ints of this rank's device memory, zero-filled once (call counter, error word).
+ *     this rank's own); state: 4 ints of this rank's device memory, zero-filled once (call counter, error word, ...).
  *   data: n fp16 / bf16 values (n % 8 == 0, n <= max_elems), summed in fp32 in rank order: every rank gets the same bits.
  * All ranks must make the same sequence of calls.  A peer that never arrives ends the bounded wait with a non-zero
  * state[1] instead of a hang. */
 size_t exl3_allreduce_region_bytes(size_t max_elems);
+/* exl3_linear with the exchange step inside the kernel, for row-parallel shards: the CTA that finishes a block of 128
+ * output columns sends the rounded partial results straight to every peer and adds the peers' contributions as they
+ * arrive, so no separate all-reduce launch follows the linear.  Same result bits as exl3_linear followed by
+ * exl3_allreduce.  peer_regions / rank / world / max_elems as for exl3_allreduce (the two may share regions and state);
+ * state: 4 ints, zero-filled once; y_dtype fp16 or bf16; min(rows, 16) * n_total <= max_elems.  A peer that never
+ * arrives ends the bounded wait and exl3_device_error(workspace) reports it.  No counterpart in the reference. */
+exl3_status exl3_linear_allreduce(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
+                                  const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total,
+                                  void *y, int y_dtype, void *workspace, size_t workspace_bytes, void *const *peer_regions, int rank,
+                                  int world, size_t max_elems, int *state, void *stream);
 exl3_status exl3_allreduce(void *data, int dtype, size_t n, void *const *peer_regions, int rank, int world, size_t max_elems,
                            int *state, void *stream);
 

@@ -37,6 +37,24 @@ def _worker(rank, world, port, out_dir):
         torch.cuda.synchronize()
         ar.check()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (rank, call)
+    # The exchange fused into the row-parallel linear gives the bits of linear followed by the all-reduce; the two kinds
+    # of call share regions and the call counter, so they are interleaved here.  Shapes: several column blocks per CTA
+    # range and ranges that share blocks; 1, 2 (in-kernel rotation), 5 and 16 rows; fp16 and bf16.
+    from trellis_serve_b200.kernels import linear as lin
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    for call, (rows, k, n, K, dtype) in enumerate([(1, 1024, 5120, 3, torch.float16), (2, 512, 5120, 4, torch.bfloat16),
+                                                   (5, 2176, 5120, 3, torch.float16), (16, 640, 5120, 2, torch.float16),
+                                                   (1, 2176, 5120, 3, torch.float16)]):
+        gen.manual_seed(7000 + 10 * call + rank)
+        w = random_packed(k, n, K, gen, dev)
+        suh, svh = random_signs(k, gen, dev, 1), (random_signs(n, gen, dev).view(-1) / 16).half()
+        x = torch.randn((rows, k), device=dev, generator=gen).to(dtype)
+        want = ar(lin.run(x, w, suh, svh, [], 0))
+        got = lin.run(x, w, suh, svh, [], 0, exchange=ar)
+        torch.cuda.synchronize()
+        ar.check()
+        lin.device_error(dev)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (rank, "fused", call)
     # CUDA-graph replay: the call counter lives on the device, so a replay is a new call
     buf = torch.zeros((1, 5120), dtype=torch.float16, device=dev)
     src = torch.zeros_like(buf)

@@ -41,6 +41,7 @@ SIGNATURES = {
     "exl3_gemm_rotated": (_i, [_vp, _vp, _i, _i, _ip, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "exl3_allreduce_region_bytes": (_sz, [_sz]),
     "exl3_allreduce": (_i, [_vp, _i, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),
+    "exl3_linear_allreduce": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),
     "exl3_moe_block_rows": (_i, []),
     "exl3_moe_sorted_capacity": (_sz, [_i, _i]),
     "exl3_moe_align": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp]),

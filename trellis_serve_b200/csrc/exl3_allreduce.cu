@@ -3,109 +3,106 @@
 // all (tensor parallelism is refused at cuda/src/sglang_exl3/sglang_glue/linear.py:74-75); the exchange step follows
 // from its slicing rules (core/src/trellis_core/format/geometry.py:62-66): row slices produce partial sums.
 //
-// Messages this small are latency-bound, so one kernel does everything: every rank copies its vector into its own
-// peer-visible slot, raises a flag in every peer's memory, waits (bounded) until all peers have raised theirs, then
-// reads all slots with ordinary peer loads and adds them in rank order in fp32 (deterministic, identical on all
-// ranks).  Slots are double-buffered by call parity: a rank can be at most one call ahead of a peer, because it
-// cannot pass the flag wait of call e+1 before that peer has finished call e.
+// Messages this small are latency-bound, so one kernel does everything, nothing is ever loaded across NVLink and
+// there is no separate flag round: every rank PUSHES its vector into its own slot of every peer's region as 8-byte
+// words {two values, call number} written with single 64-bit stores; a receiver polls (bounded) each word of its own
+// region until it carries the current call number, which proves that its two values have arrived, and adds the slots
+// in rank order in fp32 (deterministic, identical on all ranks).  One NVLink store flight is the whole exchange: no
+// fence, no flag store behind the data.  Slot sets are double-buffered by call parity: a rank can be at most one call
+// ahead of a peer, because it cannot finish call e before it has received that peer's words of call e, which the peer
+// sends only after it has finished reading call e-1.  The kernel is launched with programmatic stream serialization,
+// so its launch overlaps the tail of the linear ahead of it.
 //
-// Per-rank symmetric region: [world flags, 128 bytes apart][slot 0][slot 1].  No multicast, no multimem.
+// Per-rank symmetric region: [256-byte header][parity 0: world slots][parity 1: world slots], slot = 4 bytes per element.
+// No multicast, no multimem.
 #include "exl3_internal.h"
+#include "exl3_ptx.cuh"
 
 namespace exl3 {
 
-constexpr int AR_FLAG_STRIDE = 32;            // uint32 units: one 128-byte line per peer flag
-constexpr int AR_MAX_WORLD = 16;
-constexpr uint32_t AR_MAX_POLLS = 1u << 21;   // bounded wait: about a second, then give up
+constexpr int AR_HEADER_BYTES = TP_HEADER_BYTES;
+constexpr int AR_MAX_WORLD = TP_MAX_WORLD;
+constexpr uint32_t AR_MAX_POLLS = 1u << 20;   // bounded wait per word: about a second, then give up
 enum { AR_ERR_WAIT = 4 };
 
 struct ArPeers {
     unsigned char* base[AR_MAX_WORLD];
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 // state[0] = number of calls completed (epoch), state[1] = error word.  One CTA.
 template <bool BF16>
 __global__ void __launch_bounds__(1024, 1) allreduce_oneshot_kernel(uint16_t* __restrict__ data, size_t n, ArPeers peers, int rank, int world,
                                                                     size_t slot_bytes, int* __restrict__ state)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // data is the output of the kernel ahead; the call counter was written by the previous call, which is certain to be
+    // complete only once the kernels between it and this one are (each of them waits for the one ahead of it).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t epoch = (uint32_t)state[0] + 1u;
-    const size_t slot_off = (size_t)AR_MAX_WORLD * AR_FLAG_STRIDE * 4 + (size_t)(epoch & 1u) * slot_bytes;
-    const size_t n16 = n / 8;                                   // 16-byte chunks (n is a multiple of 8)
-    uint4* mine = reinterpret_cast<uint4*>(peers.base[rank] + slot_off);
-    const uint4* src = reinterpret_cast<const uint4*>(data);
-    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) mine[i] = src[i];
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world) {
-        // tell peer p that this rank's slot for this call is complete ...
-        st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x]) + rank * AR_FLAG_STRIDE, epoch);
-        // ... and wait until peer p has told us the same
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(peers.base[rank]) + threadIdx.x * AR_FLAG_STRIDE;
-        uint32_t polls = 0;
-        while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
-            if (++polls > AR_MAX_POLLS) {
-                atomicExch(&state[1], AR_ERR_WAIT);
-                break;
-            }
-        }
+    const size_t set_off = (size_t)AR_HEADER_BYTES + (size_t)(epoch & 1u) * world * slot_bytes;
+    const size_t nw = n / 2;                                    // 32-bit words of two values (n is a multiple of 8)
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(data);
+    // push: this rank's words, tagged with the call number, into slot `rank` of every region (its own included)
+    for (size_t i = threadIdx.x; i < nw; i += blockDim.x) {
+        const unsigned long long tagged = (unsigned long long)src[i] | ((unsigned long long)epoch << 32);
+        for (int r = 0; r < world; r++)
+            ptx::st_relaxed_sys_u64(reinterpret_cast<unsigned long long*>(peers.base[r] + set_off + (size_t)rank * slot_bytes) + i, tagged);
     }
-    __syncthreads();
-    uint4* dst = reinterpret_cast<uint4*>(data);
-    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint32_t* dst = reinterpret_cast<uint32_t*>(data);
+    const unsigned char* own = peers.base[rank] + set_off;
+    bool gave_up = false;
+    for (size_t i = threadIdx.x; i < nw; i += blockDim.x) {
+        float a0 = 0.f, a1 = 0.f;
         for (int r = 0; r < world; r++) {
-            uint4 v;                              // plain peer load, not cached in L1 across calls
-            asm volatile("ld.global.cv.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(peers.base[r] + slot_off + i * 16) : "memory");
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                if (BF16) {
-                    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-                    acc[2 * e] += __low2float(b);
-                    acc[2 * e + 1] += __high2float(b);
-                } else {
-                    const __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
-                    acc[2 * e] += __low2float(h);
-                    acc[2 * e + 1] += __high2float(h);
+            const unsigned long long* w = reinterpret_cast<const unsigned long long*>(own + (size_t)r * slot_bytes) + i;
+            unsigned long long v = ptx::ld_relaxed_sys_u64(w);
+            uint32_t polls = 0;
+            while ((uint32_t)(v >> 32) != epoch && !gave_up) {
+                if (++polls > AR_MAX_POLLS) {
+                    gave_up = true;
+                    atomicExch(&state[1], AR_ERR_WAIT);
+                    break;
                 }
+                v = ptx::ld_relaxed_sys_u64(w);
             }
-        }
-        uint32_t o[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
+            const uint32_t lo = (uint32_t)v;
             if (BF16) {
-                const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-                o[e] = *reinterpret_cast<const uint32_t*>(&b);
+                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+                a0 += __low2float(b);
+                a1 += __high2float(b);
             } else {
-                const __half2 h = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
-                o[e] = *reinterpret_cast<const uint32_t*>(&h);
+                const __half2 h = *reinterpret_cast<const __half2*>(&lo);
+                a0 += __low2float(h);
+                a1 += __high2float(h);
             }
         }
-        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        uint32_t o;
+        if (BF16) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(a0, a1);
+            o = *reinterpret_cast<const uint32_t*>(&b);
+        } else {
+            const __half2 h = __floats2half2_rn(a0, a1);
+            o = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        dst[i] = o;
     }
     __syncthreads();
     if (threadIdx.x == 0) state[0] = (int)epoch;
 }
 
-size_t allreduce_region_bytes(size_t max_elems) { return (size_t)AR_MAX_WORLD * AR_FLAG_STRIDE * 4 + 2 * ((max_elems * 2 + 255) & ~(size_t)255); }
+size_t allreduce_region_bytes(size_t max_elems)
+{
+    return (size_t)AR_HEADER_BYTES + 2 * (size_t)AR_MAX_WORLD * ((max_elems * 4 + 255) & ~(size_t)255);
+}
 
 int launch_allreduce(void* data, int bf16, size_t n, void* const* peer_bases_host, int rank, int world, size_t max_elems, int* state,
                      cudaStream_t st)
 {
     ArPeers peers;
     for (int r = 0; r < AR_MAX_WORLD; r++) peers.base[r] = r < world ? reinterpret_cast<unsigned char*>(peer_bases_host[r]) : nullptr;
-    const size_t slot_bytes = (max_elems * 2 + 255) & ~(size_t)255;
-    if (bf16) allreduce_oneshot_kernel<true><<<1, 1024, 0, st>>>(reinterpret_cast<uint16_t*>(data), n, peers, rank, world, slot_bytes, state);
-    else allreduce_oneshot_kernel<false><<<1, 1024, 0, st>>>(reinterpret_cast<uint16_t*>(data), n, peers, rank, world, slot_bytes, state);
-    return cuda_status(cudaGetLastError());
+    const size_t slot_bytes = (max_elems * 4 + 255) & ~(size_t)255;
+    auto kernel = bf16 ? allreduce_oneshot_kernel<true> : allreduce_oneshot_kernel<false>;
+    return launch_chained(kernel, dim3(1), dim3(1024), 0, st, reinterpret_cast<uint16_t*>(data), n, peers, rank, world, slot_bytes, state);
 }
 
 }  // namespace exl3

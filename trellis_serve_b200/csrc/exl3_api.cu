@@ -170,7 +170,8 @@ size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards)
 
 static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor, const uint32_t* packed, int K, int codebook,
                          const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k,
-                         int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated)
+                         int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated,
+                         const TpExchange* tp = nullptr)
 {
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (rows < 0) return EXL3_ERR_BAD_SHAPE;
@@ -201,6 +202,7 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
     a.n_total = n_total;
     a.out_dtype = y_dtype;
     a.rotated = rotated ? 1 : 0;
+    if (tp) a.tp = *tp;
     const size_t esz = 2, osz = y_dtype == EXL3_F32 ? 4 : 2;
     for (int r0 = 0; r0 < rows; r0 += GEMV_MAX_ROWS) {
         const int r = rows - r0 < GEMV_MAX_ROWS ? rows - r0 : GEMV_MAX_ROWS;
@@ -240,6 +242,34 @@ exl3_status exl3_linear(const void* x, int x_dtype, const uint32_t* packed, int 
 {
     return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
                          y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false);
+}
+
+exl3_status exl3_linear_allreduce(const void* x, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat,
+                                  const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y,
+                                  int y_dtype, void* workspace, size_t workspace_bytes, void* const* peer_regions, int rank, int world,
+                                  size_t max_elems, int* state, void* stream)
+{
+    if (world < 1 || world > TP_MAX_WORLD || rank < 0 || rank >= world) return EXL3_ERR_BAD_SHAPE;
+    if (world == 1)
+        return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
+                             y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false);
+    if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    const size_t chunk_rows = rows < GEMV_MAX_ROWS ? (rows < 0 ? 0 : rows) : GEMV_MAX_ROWS;
+    const size_t slot_bytes = (max_elems * 4 + 255) & ~(size_t)255;
+    if (chunk_rows * (size_t)(n_total < 0 ? 0 : n_total) > max_elems || slot_bytes > 0xFFFFFFFFu) return EXL3_ERR_BAD_SHAPE;
+    if (!peer_regions || !state || !aligned(state, 4)) return EXL3_ERR_BAD_POINTER;
+    TpExchange tp;
+    memset(&tp, 0, sizeof(tp));
+    for (int r = 0; r < world; r++) {
+        if (!aligned(peer_regions[r], 256)) return EXL3_ERR_BAD_POINTER;
+        tp.base[r] = reinterpret_cast<unsigned char*>(peer_regions[r]);
+    }
+    tp.rank = rank;
+    tp.world = world;
+    tp.slot_bytes = (unsigned int)slot_bytes;
+    tp.state = state;
+    return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
+                         workspace, workspace_bytes, (cudaStream_t)stream, false, &tp);
 }
 
 exl3_status exl3_gemm_rotated(const uint16_t* xh, const uint32_t* packed, int K, int codebook, const int* shard_ends, int n_shards,

@@ -29,7 +29,8 @@ constexpr int GEMV_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;
 constexpr int GEMV_MAX_STAGES = 12;
 constexpr int GEMV_CTAS_PER_SM = 2;         // two resident CTAs per SM: twice the warps to hide instruction latency
 
-enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2 };
+enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2, GEMV_ERR_PEER_WAIT = 3 };
+constexpr uint32_t GEMV_PEER_MAX_POLLS = 1u << 20;       // bounded wait for a peer's words: about a second
 
 struct GemvLaunch {
     GemvArgs a;
@@ -169,6 +170,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     const uint32_t w_off = (uint32_t)((nt * 2 + kq) * K) * 128u + lane * 4u;
     int nb = (int)((unsigned)u0 / (unsigned)p.KG), kg = u0 - nb * p.KG;
 
+    uint32_t tp_epoch = 0;                      // call number of the fused exchange; read once the kernel ahead has finished
     // P -> out for column block fnb: one warp per batch row applies Had128 * svh (or stores the rotated-basis product).
     auto epilogue = [&](int fnb) {
         if (warp < rows) {
@@ -192,6 +194,70 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 v[3] *= HAD_SCALE * __high2float(s23);
                 if (p.a.out_dtype == EXL3_F32) {
                     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.a.out) + o) = make_float4(v[0], v[1], v[2], v[3]);
+                } else if (p.a.tp.world > 1) {
+                    // Row-parallel shard: this rank's 128 columns of row m are a partial sum.  They go, rounded to the
+                    // output type and tagged with the call number, into this rank's slot at every peer (single 64-bit
+                    // peer stores); then the same words of all ranks are awaited here (bounded), added in rank order in
+                    // fp32 and rounded once: the bits a separate all-reduce of the rounded outputs gives.
+                    const bool bf = p.a.out_dtype == EXL3_BF16;
+                    uint32_t w2[2];
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const __half2 hh = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                        if (bf) {
+                            const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(hh), __high2float(hh));
+                            w2[e] = *reinterpret_cast<const uint32_t*>(&bb);
+                        } else {
+                            w2[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                        }
+                    }
+                    const size_t set_off = (size_t)TP_HEADER_BYTES + (size_t)(tp_epoch & 1u) * p.a.tp.world * p.a.tp.slot_bytes;
+                    const size_t word = (size_t)(o >> 1);                    // 32-bit word of two values inside a slot
+                    const unsigned long long tag = (unsigned long long)tp_epoch << 32;
+                    for (int r = 0; r < p.a.tp.world; r++) {
+                        unsigned long long* dst =
+                            reinterpret_cast<unsigned long long*>(p.a.tp.base[r] + set_off + (size_t)p.a.tp.rank * p.a.tp.slot_bytes) + word;
+                        ptx::st_relaxed_sys_u64(dst, tag | w2[0]);
+                        ptx::st_relaxed_sys_u64(dst + 1, tag | w2[1]);
+                    }
+                    float a[4] = {0.f, 0.f, 0.f, 0.f};
+                    const unsigned char* own = p.a.tp.base[p.a.tp.rank] + set_off;
+                    bool gave_up = false;
+                    for (int r = 0; r < p.a.tp.world; r++) {
+                        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * p.a.tp.slot_bytes) + word;
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            unsigned long long got = ptx::ld_relaxed_sys_u64(src + e);
+                            uint32_t polls = 0;
+                            while ((uint32_t)(got >> 32) != tp_epoch && !gave_up) {
+                                if (++polls > GEMV_PEER_MAX_POLLS) {
+                                    gave_up = true;
+                                    atomicExch(p.a.err, GEMV_ERR_PEER_WAIT);
+                                    break;
+                                }
+                                got = ptx::ld_relaxed_sys_u64(src + e);
+                            }
+                            const uint32_t lo = (uint32_t)got;
+                            if (bf) {
+                                const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+                                a[2 * e] += __low2float(bb);
+                                a[2 * e + 1] += __high2float(bb);
+                            } else {
+                                const __half2 hh = *reinterpret_cast<const __half2*>(&lo);
+                                a[2 * e] += __low2float(hh);
+                                a[2 * e + 1] += __high2float(hh);
+                            }
+                        }
+                    }
+                    uint2 res;
+                    if (bf) {
+                        const __nv_bfloat162 b0 = __floats2bfloat162_rn(a[0], a[1]), b1 = __floats2bfloat162_rn(a[2], a[3]);
+                        res = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+                    } else {
+                        const __half2 h0 = __floats2half2_rn(a[0], a[1]), h1 = __floats2half2_rn(a[2], a[3]);
+                        res = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+                    }
+                    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.a.out) + o) = res;
                 } else {
                     __half h[4];
 #pragma unroll
@@ -360,6 +426,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         xaddr = ptx::smem_addr(xs) + (ok ? GEMV_XS_ZERO_BYTES + (uint32_t)(kq * 4 * XR + g) * 4u * FW * 4u + (uint32_t)q * FW * 4u : 0u);
         xstep = ok ? XS_SLOT : 0u;
     }
+    if (p.a.tp.world > 1) tp_epoch = (uint32_t)*reinterpret_cast<volatile int*>(p.a.tp.state) + 1u;
     bool aborted = false;
     const int ups = p.units_per_stage;
 
@@ -471,6 +538,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         }
     }
     if (kg != 0 && u1 > u0) flush(nb);
+    if (p.a.tp.world > 1) {
+        // The call number moves on once every CTA of this launch has read it: the last CTA to get here bumps it.
+        ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(&p.a.tp.state[2], 1) == (int)gridDim.x - 1) {
+                p.a.tp.state[2] = 0;
+                p.a.tp.state[0] = (int)tp_epoch;
+            }
+        }
+    }
 }
 
 template <int K>

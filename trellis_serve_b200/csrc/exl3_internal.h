@@ -47,6 +47,17 @@ constexpr int GEMV_MAX_SHARDS = 4;
 // Words per lane of one activation fragment (four k values of a 16-row tile) in each mode.
 __host__ __device__ constexpr int gemv_frag_words(int mode) { return mode == GEMV_SPLIT ? 4 : 2; }
 
+// Tensor-parallel exchange fused into the GEMV (row-parallel linears): peer regions laid out as for the one-shot
+// all-reduce (256-byte header, then per call parity `world` slots of slot_bytes, 4 bytes per output element).
+constexpr int TP_MAX_WORLD = 16;
+constexpr int TP_HEADER_BYTES = 256;
+struct TpExchange {
+    unsigned char* base[TP_MAX_WORLD];   // every rank's region, mapped into this process
+    int rank, world;                      // world <= 1: no exchange
+    unsigned int slot_bytes;
+    int* state;                           // [0] calls completed, [1] error word, [2] CTAs arrived in the running call
+};
+
 struct GemvArgs {
     const uint32_t* packed;     // resident weights, n-blocks of all shards concatenated
     const uint32_t* xf;         // activation fragments [shard][k/16][rows][4][frag_words]
@@ -64,6 +75,7 @@ struct GemvArgs {
     int shard_end_blocks[GEMV_MAX_SHARDS];   // n-block index where shard s ends (last = NB)
     int out_dtype;              // EXL3_F16 / EXL3_BF16 / EXL3_F32 (fp32 only with the output Hadamard)
     int rotated;                // 1: store the rotated-basis product as fp16, no output Hadamard
+    TpExchange tp;              // world > 1: the output is summed over the ranks inside the kernel
 };
 
 // Preferred mode for a codebook (split for the hash codebooks, paired for MUL1).

@@ -149,9 +149,11 @@ def _geometry(packed: torch.Tensor) -> tuple[int, int, int]:
 
 
 def run(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int],
-        codebook: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        codebook: int, out: torch.Tensor | None = None, exchange=None) -> torch.Tensor:
     """x fp16 | bf16 [rows, k] contiguous -> y (same dtype) [rows, n_total].  Only y is allocated (unless `out`).
-    An fp32 `out` receives the unrounded accumulators (accuracy measurements)."""
+    An fp32 `out` receives the unrounded accumulators (accuracy measurements).  `exchange` (a
+    `runtime.allreduce.PeerAllReduce`): the matrix is a row-parallel shard and y is summed over the ranks inside the
+    kernel, the same bits as `exchange(run(...))`."""
     _require_cuda(x, "x")
     lib = _lib.load()
     _lib.init_device(x.device.index if x.device.index is not None else torch.cuda.current_device())
@@ -165,9 +167,16 @@ def run(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.
         return y
     ws = reserve_workspace(x.device, workspace_bytes(rows, k, n_total, shards))
     with torch.cuda.device(x.device):
-        _lib.check(lib.exl3_linear(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
-                                   _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(y), _dtype_code(y, True),
-                                   _ptr(ws), ws.numel(), _stream(x.device)), "exl3_linear")
+        if exchange is not None and exchange.world > 1:
+            _lib.check(lib.exl3_linear_allreduce(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
+                                                 _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(y), _dtype_code(y),
+                                                 _ptr(ws), ws.numel(), exchange.peer_regions, exchange.rank, exchange.world,
+                                                 exchange.max_elems, _ptr(exchange.state), _stream(x.device)),
+                       "exl3_linear_allreduce")
+        else:
+            _lib.check(lib.exl3_linear(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
+                                       _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(y), _dtype_code(y, True),
+                                       _ptr(ws), ws.numel(), _stream(x.device)), "exl3_linear")
     return y
 
 

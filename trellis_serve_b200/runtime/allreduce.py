@@ -39,7 +39,7 @@ class PeerAllReduce:
         if len(ptrs) != self.world:
             raise RuntimeError(f"symmetric-memory rendezvous returned {len(ptrs)} peers for a group of {self.world}")
         self.peer_regions = (ctypes.c_void_p * self.world)(*ptrs)
-        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.state = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)                 # every region is zero before anyone raises a flag
 

@@ -58,12 +58,14 @@ class DecodeLayerSet:
 
     def __init__(self, layers: int, K: int, codebook: int, rows: int, shape: LayerShape = LayerShape(), tp_rank: int = 0,
                  tp_size: int = 1, seed: int = 100, device: str | torch.device = "cuda:0", group=None,
-                 allreduce=None, dtype: torch.dtype = torch.float16):
+                 allreduce=None, dtype: torch.dtype = torch.float16, fused_exchange: bool = False):
         self.layers, self.K, self.codebook, self.rows = layers, K, codebook, rows
         self.shape, self.tp_rank, self.tp_size = shape, tp_rank, tp_size
         self.device = torch.device(device)
         self.group = group
         self.allreduce = allreduce
+        # fused_exchange (needs a PeerAllReduce in `allreduce`): row-parallel linears sum over the ranks inside their kernel
+        self.fused_exchange = bool(fused_exchange and allreduce is not None and tp_size > 1)
         self.dtype = dtype
         for width in (shape.q_out, shape.kv_out, shape.ffn, shape.hidden):
             if width % tp_size or (width // tp_size) % 128:
@@ -115,11 +117,17 @@ class DecodeLayerSet:
         """All linears of the stack once, in layer order, on the current stream."""
         for qkv, o, gu, down in self.groups:
             lin.run(self.x_hidden, qkv.packed, qkv.suh, qkv.svh, qkv.ends, self.codebook, out=self.y_qkv)
-            lin.run(self.x_attn, o.packed, o.suh, o.svh, o.ends, self.codebook, out=self.y_o)
-            self._reduce(self.y_o)
+            if self.fused_exchange:
+                lin.run(self.x_attn, o.packed, o.suh, o.svh, o.ends, self.codebook, out=self.y_o, exchange=self.allreduce)
+            else:
+                lin.run(self.x_attn, o.packed, o.suh, o.svh, o.ends, self.codebook, out=self.y_o)
+                self._reduce(self.y_o)
             lin.run(self.x_hidden, gu.packed, gu.suh, gu.svh, gu.ends, self.codebook, out=self.y_gu)
-            lin.run(self.x_ffn, down.packed, down.suh, down.svh, down.ends, self.codebook, out=self.y_down)
-            self._reduce(self.y_down)
+            if self.fused_exchange:
+                lin.run(self.x_ffn, down.packed, down.suh, down.svh, down.ends, self.codebook, out=self.y_down, exchange=self.allreduce)
+            else:
+                lin.run(self.x_ffn, down.packed, down.suh, down.svh, down.ends, self.codebook, out=self.y_down)
+                self._reduce(self.y_down)
         return self.y_down
 
     def capture(self, warmup: int = 2) -> None:
