@@ -8,8 +8,9 @@
 //
 //   * persistent grid, one CTA per SM; the (column block, row block) units of the matrix are split evenly and
 //     contiguously over the CTAs ("stream-K"), so every CTA streams ONE contiguous byte range of the weights;
-//   * a producer warp feeds a ring of shared-memory stages with 1-D bulk async copies (TMA engine, mbarrier
-//     byte counting, no multicast): one stage = one unit = 2048*K bytes of weights + its activation fragments;
+//   * a ring of shared-memory stages is fed with 1-D bulk async copies (TMA engine, mbarrier byte counting, no
+//     multicast), one copy of several units per stage; there is no copy warp: the warp that is last to finish a stage
+//     (a shared-memory counter tells it) issues the copy that refills it;
 //   * 16 consumer warps; warp (nt, kq) owns column tile nt of the block and four of the unit's eight row tiles.
 //     A lane reads K words, gets 16-K bits from its neighbour by one shuffle per tile, extracts its eight
 //     16-bit states in registers and hashes them.  The resulting registers ARE the A operand of
@@ -25,11 +26,12 @@
 namespace exl3 {
 
 constexpr int GEMV_CONSUMER_WARPS = 16;
-constexpr int GEMV_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;
+constexpr int GEMV_THREADS = GEMV_CONSUMER_WARPS * 32;             // no copy warp: 512 threads leave 64 registers each
+constexpr int MOE_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;        // the grouped MoE kernel keeps a copy warp
 constexpr int GEMV_MAX_STAGES = 12;
 constexpr int GEMV_CTAS_PER_SM = 2;         // two resident CTAs per SM: twice the warps to hide instruction latency
 
-enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2, GEMV_ERR_PEER_WAIT = 3 };
+enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2, GEMV_ERR_PEER_WAIT = 3 };    // 2: the grouped MoE kernel's copy warp
 constexpr uint32_t GEMV_PEER_MAX_POLLS = 1u << 20;       // bounded wait for a peer's words: about a second
 
 struct GemvLaunch {
@@ -54,12 +56,12 @@ constexpr uint32_t GEMV_XS_ZERO_BYTES = 512;
 __host__ __device__ constexpr uint32_t gemv_xs_slot_bytes(int mode, int rows) { return 8u * rows * 4u * gemv_frag_words(mode) * 4u; }
 
 // Unit indices fit 32 bits (the host refuses matrices with 2^31 or more units).
-__host__ __device__ inline int gemv_first_unit(int cta, int q, int r) { return cta * q + (cta < r ? cta : r); }
+__host__ __device__ inline long long gemv_first_unit(int cta, int q, int r) { return (long long)cta * q + (cta < r ? cta : r); }
 
-__device__ __forceinline__ int gemv_cta_of_unit(int u, int q, int r)
+__device__ __forceinline__ int gemv_cta_of_unit(long long u, int q, int r)
 {
-    const unsigned boundary = (unsigned)r * (unsigned)(q + 1);
-    return (unsigned)u < boundary ? (int)((unsigned)u / (unsigned)(q + 1)) : r + (int)(((unsigned)u - boundary) / (unsigned)q);
+    long long boundary = (long long)r * (q + 1);
+    return u < boundary ? (int)(u / (q + 1)) : r + (int)((u - boundary) / q);
 }
 
 template <int K, int MODE, int FAM>
@@ -87,71 +89,123 @@ __device__ __forceinline__ float gemv_load_x(const void* p, long long idx, bool 
     return __half2float(reinterpret_cast<const __half*>(p)[idx]);
 }
 
+// Row-parallel shard: 4 consecutive columns (index o) of one output row are a partial sum.  They go, rounded to the
+// output type and tagged with the call number, into this rank's slot at every peer (single 64-bit peer stores); then
+// the same words of all ranks are awaited here (bounded), added in rank order in fp32 and rounded once: the bits a
+// separate all-reduce of the rounded outputs gives.  Kept out of line: it runs once per 128 outputs and must not
+// weigh on the register allocation of the decode loop.
+static __device__ __noinline__ void gemv_exchange_store(const TpExchange& tp, uint32_t tp_epoch, bool bf, const float (&v)[4], long long o,
+                                                 uint16_t* out, int* err)
+{
+    uint32_t w2[2];
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const __half2 hh = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+        if (bf) {
+            const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(hh), __high2float(hh));
+            w2[e] = *reinterpret_cast<const uint32_t*>(&bb);
+        } else {
+            w2[e] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+    }
+    const size_t set_off = (size_t)TP_HEADER_BYTES + (size_t)(tp_epoch & 1u) * tp.world * tp.slot_bytes;
+    const size_t word = (size_t)(o >> 1);                    // 32-bit word of two values inside a slot
+    const unsigned long long tag = (unsigned long long)tp_epoch << 32;
+    for (int r = 0; r < tp.world; r++) {
+        unsigned long long* dst = reinterpret_cast<unsigned long long*>(tp.base[r] + set_off + (size_t)tp.rank * tp.slot_bytes) + word;
+        ptx::st_relaxed_sys_u64(dst, tag | w2[0]);
+        ptx::st_relaxed_sys_u64(dst + 1, tag | w2[1]);
+    }
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    const unsigned char* own = tp.base[tp.rank] + set_off;
+    bool gave_up = false;
+    for (int r = 0; r < tp.world; r++) {
+        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * tp.slot_bytes) + word;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            unsigned long long got = ptx::ld_relaxed_sys_u64(src + e);
+            uint32_t polls = 0;
+            while ((uint32_t)(got >> 32) != tp_epoch && !gave_up) {
+                if (++polls > GEMV_PEER_MAX_POLLS) {
+                    gave_up = true;
+                    atomicExch(err, GEMV_ERR_PEER_WAIT);
+                    break;
+                }
+                got = ptx::ld_relaxed_sys_u64(src + e);
+            }
+            const uint32_t lo = (uint32_t)got;
+            if (bf) {
+                const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+                a[2 * e] += __low2float(bb);
+                a[2 * e + 1] += __high2float(bb);
+            } else {
+                const __half2 hh = *reinterpret_cast<const __half2*>(&lo);
+                a[2 * e] += __low2float(hh);
+                a[2 * e + 1] += __high2float(hh);
+            }
+        }
+    }
+    uint2 res;
+    if (bf) {
+        const __nv_bfloat162 b0 = __floats2bfloat162_rn(a[0], a[1]), b1 = __floats2bfloat162_rn(a[2], a[3]);
+        res = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+    } else {
+        const __half2 h0 = __floats2half2_rn(a[0], a[1]), h1 = __floats2half2_rn(a[2], a[3]);
+        res = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+    }
+    *reinterpret_cast<uint2*>(out + o) = res;
+}
+
 // MODE: GEMV_SPLIT / GEMV_PAIRED.  FAM: FAM_HASH / FAM_MUL1 (split implies hash).  MB: 8-row groups (1 or 2).
 // XR: 0 = activation fragments come from the workspace (written by the rotation kernel ahead of this launch);
 //     1, 2 = that many rows, and the kernel rotates the input itself: before the main loop every consumer warp turns
 //     x * suh of a few of the CTA's units into fragments in shared memory (one slot per unit, in unit order), so the
 //     linear is ONE launch and the main loop reads its activations with immediate-offset shared loads.
 template <int K, int MODE, int FAM, int MB, int XR>
-__global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(const GemvLaunch p)
+__global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(const __grid_constant__ GemvLaunch p)
 {
     static_assert(XR == 0 || MB == 1, "in-kernel rotation serves one 8-row group");
     constexpr int FW = gemv_frag_words(MODE);
     constexpr uint32_t W_BYTES = 2048u * K;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-    uint64_t* empty = full + GEMV_MAX_STAGES;
+    int* released = reinterpret_cast<int*>(smem + GEMV_MAX_STAGES * 8);           // per stage: warps that are done with it
     int* flag = reinterpret_cast<int*>(smem + 2 * GEMV_MAX_STAGES * 8);          // [0] last-arriver flag, [1] abort
     float* P = reinterpret_cast<float*>(smem + 256);                              // [16][128]
     unsigned char* stage0 = smem + 256 + GEMV_MAX_ROWS * 128 * 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x;
-    const int u0 = gemv_first_unit(cta, p.units_q, p.units_r);
-    const int u1 = gemv_first_unit(cta + 1, p.units_q, p.units_r);
+    const long long u0 = gemv_first_unit(cta, p.units_q, p.units_r);
+    const long long u1 = gemv_first_unit(cta + 1, p.units_q, p.units_r);
     const int rows = p.a.rows;
 
+    // One bulk copy per stage and stages of several units: the copy engine has a fixed cost of a few hundred nanoseconds
+    // per bulk copy, so small copies cap the stream far below HBM speed.  The CTA's units are contiguous in memory, so
+    // stage number j is simply units [u0 + j * ups, +ups) and lives in slot j % stages.
+    const int ups = p.units_per_stage;
+    const int n_fills = (int)((u1 - u0 + ups - 1) / ups);
+    auto issue_fill = [&](int j, int slot) {       // one thread: start the copy of stage number j into `slot`
+        const long long u = u0 + (long long)j * ups;
+        const long long left = u1 - u;
+        const uint32_t bytes = (uint32_t)(left < ups ? left : ups) * W_BYTES;
+        ptx::mbar_arrive_expect_tx(&full[slot], bytes);
+        ptx::bulk_g2s(stage0 + (size_t)slot * p.stage_stride, p.a.packed + (long long)u * (512 * K), bytes, &full[slot]);
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
+            released[s] = 0;
         }
         flag[0] = 0;
         flag[1] = 0;
         ptx::mbar_fence_init();
+        // Weights are constants: the first lap of copies starts before the kernel ahead of this one has finished.
+        for (int j = 0; j < p.stages && j < n_fills; j++) issue_fill(j, j);
     }
     __syncthreads();
 
     ptx::grid_launch_dependents();             // the next kernel in the stream may begin its prologue
-    if (warp == GEMV_CONSUMER_WARPS) {
-        // ------------------------------------------------------------------ producer
-        // Weights are constants: their copies start before the kernel ahead of this one has finished.
-        // One bulk copy per stage and stages of several units: the copy engine has a fixed cost of a few hundred
-        // nanoseconds per bulk copy, so small copies cap the stream far below HBM speed.  The CTA's units are
-        // contiguous in memory, so a stage is simply the next `units_per_stage` units.  One thread issues the
-        // copies in ring order; while it waits for the oldest stage to be released the hardware keeps it suspended
-        // (try_wait with a time hint), so it takes no issue slots from the consumer warps of its scheduler.
-        if (lane == 0) {
-            int s = 0;
-            uint32_t wait_parity = 1;              // parity of the empty-barrier phase awaited in the current lap
-            bool first_lap = true;
-            for (int u = u0; u < u1; u += p.units_per_stage) {
-                if (!first_lap && !ptx::mbar_wait(&empty[s], wait_parity)) {
-                    atomicExch(p.a.err, GEMV_ERR_EMPTY_WAIT);
-                    break;
-                }
-                const int left = u1 - u;
-                const uint32_t bytes = (uint32_t)(left < p.units_per_stage ? left : p.units_per_stage) * W_BYTES;
-                ptx::mbar_arrive_expect_tx(&full[s], bytes);
-                ptx::bulk_g2s(stage0 + (size_t)s * p.stage_stride, p.a.packed + (long long)u * (512 * K), bytes, &full[s]);
-                if (++s == p.stages) {
-                    s = 0;
-                    if (first_lap) { first_lap = false; wait_parity = 0; } else wait_parity ^= 1;
-                }
-            }
-        }
-        return;
-    }
 
     // ---------------------------------------------------------------------- consumers
     // Everything below reads or writes memory other kernels write (activations, workspace, output) and so comes after
@@ -168,7 +222,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 
     const uint32_t stage0_addr = ptx::smem_addr(stage0);
     const uint32_t w_off = (uint32_t)((nt * 2 + kq) * K) * 128u + lane * 4u;
-    int nb = (int)((unsigned)u0 / (unsigned)p.KG), kg = u0 - nb * p.KG;
+    int nb = (int)(u0 / p.KG), kg = (int)(u0 % p.KG);
 
     uint32_t tp_epoch = 0;                      // call number of the fused exchange; read once the kernel ahead has finished
     // P -> out for column block fnb: one warp per batch row applies Had128 * svh (or stores the rotated-basis product).
@@ -195,69 +249,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 if (p.a.out_dtype == EXL3_F32) {
                     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.a.out) + o) = make_float4(v[0], v[1], v[2], v[3]);
                 } else if (p.a.tp.world > 1) {
-                    // Row-parallel shard: this rank's 128 columns of row m are a partial sum.  They go, rounded to the
-                    // output type and tagged with the call number, into this rank's slot at every peer (single 64-bit
-                    // peer stores); then the same words of all ranks are awaited here (bounded), added in rank order in
-                    // fp32 and rounded once: the bits a separate all-reduce of the rounded outputs gives.
-                    const bool bf = p.a.out_dtype == EXL3_BF16;
-                    uint32_t w2[2];
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const __half2 hh = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-                        if (bf) {
-                            const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(hh), __high2float(hh));
-                            w2[e] = *reinterpret_cast<const uint32_t*>(&bb);
-                        } else {
-                            w2[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                        }
-                    }
-                    const size_t set_off = (size_t)TP_HEADER_BYTES + (size_t)(tp_epoch & 1u) * p.a.tp.world * p.a.tp.slot_bytes;
-                    const size_t word = (size_t)(o >> 1);                    // 32-bit word of two values inside a slot
-                    const unsigned long long tag = (unsigned long long)tp_epoch << 32;
-                    for (int r = 0; r < p.a.tp.world; r++) {
-                        unsigned long long* dst =
-                            reinterpret_cast<unsigned long long*>(p.a.tp.base[r] + set_off + (size_t)p.a.tp.rank * p.a.tp.slot_bytes) + word;
-                        ptx::st_relaxed_sys_u64(dst, tag | w2[0]);
-                        ptx::st_relaxed_sys_u64(dst + 1, tag | w2[1]);
-                    }
-                    float a[4] = {0.f, 0.f, 0.f, 0.f};
-                    const unsigned char* own = p.a.tp.base[p.a.tp.rank] + set_off;
-                    bool gave_up = false;
-                    for (int r = 0; r < p.a.tp.world; r++) {
-                        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * p.a.tp.slot_bytes) + word;
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            unsigned long long got = ptx::ld_relaxed_sys_u64(src + e);
-                            uint32_t polls = 0;
-                            while ((uint32_t)(got >> 32) != tp_epoch && !gave_up) {
-                                if (++polls > GEMV_PEER_MAX_POLLS) {
-                                    gave_up = true;
-                                    atomicExch(p.a.err, GEMV_ERR_PEER_WAIT);
-                                    break;
-                                }
-                                got = ptx::ld_relaxed_sys_u64(src + e);
-                            }
-                            const uint32_t lo = (uint32_t)got;
-                            if (bf) {
-                                const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&lo);
-                                a[2 * e] += __low2float(bb);
-                                a[2 * e + 1] += __high2float(bb);
-                            } else {
-                                const __half2 hh = *reinterpret_cast<const __half2*>(&lo);
-                                a[2 * e] += __low2float(hh);
-                                a[2 * e + 1] += __high2float(hh);
-                            }
-                        }
-                    }
-                    uint2 res;
-                    if (bf) {
-                        const __nv_bfloat162 b0 = __floats2bfloat162_rn(a[0], a[1]), b1 = __floats2bfloat162_rn(a[2], a[3]);
-                        res = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
-                    } else {
-                        const __half2 h0 = __floats2half2_rn(a[0], a[1]), h1 = __floats2half2_rn(a[2], a[3]);
-                        res = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-                    }
-                    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.a.out) + o) = res;
+                    gemv_exchange_store(p.a.tp, tp_epoch, p.a.out_dtype == EXL3_BF16, v, o, reinterpret_cast<uint16_t*>(p.a.out), p.a.err);
                 } else {
                     __half h[4];
 #pragma unroll
@@ -296,7 +288,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             }
             ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
         }
-        const int ub = fnb * p.KG;
+        const long long ub = (long long)fnb * p.KG;
         const int c_first = gemv_cta_of_unit(ub, p.units_q, p.units_r);
         const int c_last = gemv_cta_of_unit(ub + p.KG - 1, p.units_q, p.units_r);
         bool finish = true;
@@ -358,7 +350,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         unsigned char* xs = smem + p.xs_off;
         uint32_t* slots = reinterpret_cast<uint32_t*>(xs + GEMV_XS_ZERO_BYTES);
         if (threadIdx.x < GEMV_XS_ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xs)[threadIdx.x] = 0u;
-        const int items = (u1 - u0) * XR;
+        const int items = (int)(u1 - u0) * XR;
         const bool bf16 = p.a.x_bf16 != 0;
         constexpr int BATCH = 3;                      // rotations in flight per warp: their loads overlap
         bool waited = false;
@@ -371,8 +363,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 xi[b] = 0;
                 if (it < items) {
                     const int i = it / XR, row = it % XR;
-                    const unsigned u = (unsigned)(u0 + i);
-                    const int unb = (int)(u / (unsigned)p.KG), ukg = (int)(u - (unsigned)unb * (unsigned)p.KG);
+                    const long long u = u0 + i;
+                    const int unb = (int)(u / p.KG), ukg = (int)(u - (long long)unb * p.KG);
                     int s = 0;
                     while (s < p.a.n_shards - 1 && unb >= p.a.shard_end_blocks[s]) s++;
                     const long long col = (long long)ukg * 128 + 4 * lane;
@@ -428,7 +420,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     }
     if (p.a.tp.world > 1) tp_epoch = (uint32_t)*reinterpret_cast<volatile int*>(p.a.tp.state) + 1u;
     bool aborted = false;
-    const int ups = p.units_per_stage;
 
     auto wait_stage = [&](int slot, uint32_t phase) {
         if (!aborted && !ptx::mbar_wait(&full[slot], phase)) {
@@ -443,7 +434,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     // The main loop is cut into runs of units that end where something has to happen (stage used up, column block
     // finished, range finished); inside a run only two addresses advance: no division, no 64-bit arithmetic, no
     // bookkeeping per unit.
-    int slot = 0, stage_left = ups;
+    int slot = 0, stage_left = ups, stage_no = 0;
     uint32_t phase = 0;
     uint32_t waddr = stage0_addr + w_off;
     uint32_t xu[MB];
@@ -452,7 +443,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         for (int mb = 0; mb < MB; mb++)
             xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems + (uint32_t)kg * x_unit[mb] : 0u);
     }
-    int remaining = u1 - u0;
+    int remaining = (int)(u1 - u0);
     if (remaining > 0) wait_stage(0, 0);
 
     while (remaining > 0) {
@@ -517,7 +508,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         }
         if (stage_left == 0 || remaining == 0) {            // stage finished: hand it back, move to the next one
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+            // The warp that is last to finish with the stage refills it (its reads and those of the warps counted before
+            // it are ordered ahead of the copy by the acquire-release counter update).
+            if (lane == 0 && ptx::atom_add_acq_rel_cta_shared(&released[slot], 1) == GEMV_CONSUMER_WARPS - 1) {
+                released[slot] = 0;
+                if (stage_no + p.stages < n_fills) issue_fill(stage_no + p.stages, slot);
+            }
+            stage_no++;
             stage_left = ups;
             if (++slot == p.stages) {
                 slot = 0;

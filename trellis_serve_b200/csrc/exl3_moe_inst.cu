@@ -16,9 +16,9 @@ template <>
 int launch_moe_gemm_for_k<EXL3_MOE_K>(const MoeGemmLaunch& l, int mode, int family, int grid, size_t smem, cudaStream_t st)
 {
     constexpr int K = EXL3_MOE_K;
-    if (family == FAM_MUL1) return launch_chained(moe_gemm_kernel<K, GEMV_PAIRED, FAM_MUL1>, dim3(grid), dim3(GEMV_THREADS), smem, st, l);
-    if (mode == GEMV_SPLIT) return launch_chained(moe_gemm_kernel<K, GEMV_SPLIT, FAM_HASH>, dim3(grid), dim3(GEMV_THREADS), smem, st, l);
-    return launch_chained(moe_gemm_kernel<K, GEMV_PAIRED, FAM_HASH>, dim3(grid), dim3(GEMV_THREADS), smem, st, l);
+    if (family == FAM_MUL1) return launch_chained(moe_gemm_kernel<K, GEMV_PAIRED, FAM_MUL1>, dim3(grid), dim3(MOE_THREADS), smem, st, l);
+    if (mode == GEMV_SPLIT) return launch_chained(moe_gemm_kernel<K, GEMV_SPLIT, FAM_HASH>, dim3(grid), dim3(MOE_THREADS), smem, st, l);
+    return launch_chained(moe_gemm_kernel<K, GEMV_PAIRED, FAM_HASH>, dim3(grid), dim3(MOE_THREADS), smem, st, l);
 }
 
 template <>

@@ -42,7 +42,7 @@ struct MoeGemmLaunch {
 int launch_moe_gemm(MoeGemmLaunch l, int K, int codebook, int mode, cudaStream_t st);
 
 template <int K, int MODE, int FAM>
-__global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel(const MoeGemmLaunch p)
+__global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel(const MoeGemmLaunch p)
 {
     constexpr int FW = gemv_frag_words(MODE);
     constexpr uint32_t W_BYTES = 2048u * K;

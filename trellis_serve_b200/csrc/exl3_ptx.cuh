@@ -65,6 +65,14 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Shared-memory counter update with acquire-release semantics inside the CTA.
+__device__ __forceinline__ int atom_add_acq_rel_cta_shared(int* addr, int v)
+{
+    int old;
+    asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_addr(addr)), "r"(v) : "memory");
+    return old;
+}
+
 // Single 64-bit accesses at system scope: the unit of the tagged-word exchange between GPUs (value + call number
 // arrive together, so the receiver needs no fence and no separate flag).
 __device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v)
