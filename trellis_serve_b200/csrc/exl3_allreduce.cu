@@ -51,29 +51,40 @@ __global__ void __launch_bounds__(1024, 1) allreduce_oneshot_kernel(uint16_t* __
     uint32_t* dst = reinterpret_cast<uint32_t*>(data);
     const unsigned char* own = peers.base[rank] + set_off;
     bool gave_up = false;
+    constexpr int BATCH = 8;                      // ranks whose words are requested together: their latencies overlap
     for (size_t i = threadIdx.x; i < nw; i += blockDim.x) {
         float a0 = 0.f, a1 = 0.f;
-        for (int r = 0; r < world; r++) {
-            const unsigned long long* w = reinterpret_cast<const unsigned long long*>(own + (size_t)r * slot_bytes) + i;
-            unsigned long long v = ptx::ld_relaxed_sys_u64(w);
-            uint32_t polls = 0;
-            while ((uint32_t)(v >> 32) != epoch && !gave_up) {
-                if (++polls > AR_MAX_POLLS) {
-                    gave_up = true;
-                    atomicExch(&state[1], AR_ERR_WAIT);
-                    break;
-                }
-                v = ptx::ld_relaxed_sys_u64(w);
+        for (int r0 = 0; r0 < world; r0 += BATCH) {
+            unsigned long long v[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; j++) {
+                const int r = r0 + j < world ? r0 + j : world - 1;
+                v[j] = ptx::ld_relaxed_sys_u64(reinterpret_cast<const unsigned long long*>(own + (size_t)r * slot_bytes) + i);
             }
-            const uint32_t lo = (uint32_t)v;
-            if (BF16) {
-                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&lo);
-                a0 += __low2float(b);
-                a1 += __high2float(b);
-            } else {
-                const __half2 h = *reinterpret_cast<const __half2*>(&lo);
-                a0 += __low2float(h);
-                a1 += __high2float(h);
+#pragma unroll
+            for (int j = 0; j < BATCH; j++) {
+                if (r0 + j < world) {
+                    const unsigned long long* w = reinterpret_cast<const unsigned long long*>(own + (size_t)(r0 + j) * slot_bytes) + i;
+                    uint32_t polls = 0;
+                    while ((uint32_t)(v[j] >> 32) != epoch && !gave_up) {
+                        if (++polls > AR_MAX_POLLS) {
+                            gave_up = true;
+                            atomicExch(&state[1], AR_ERR_WAIT);
+                            break;
+                        }
+                        v[j] = ptx::ld_relaxed_sys_u64(w);
+                    }
+                    const uint32_t lo = (uint32_t)v[j];
+                    if (BF16) {
+                        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+                        a0 += __low2float(b);
+                        a1 += __high2float(b);
+                    } else {
+                        const __half2 h = *reinterpret_cast<const __half2*>(&lo);
+                        a0 += __low2float(h);
+                        a1 += __high2float(h);
+                    }
+                }
             }
         }
         uint32_t o;

@@ -119,29 +119,42 @@ static __device__ __noinline__ void gemv_exchange_store(const TpExchange& tp, ui
     float a[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned char* own = tp.base[tp.rank] + set_off;
     bool gave_up = false;
-    for (int r = 0; r < tp.world; r++) {
-        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * tp.slot_bytes) + word;
+    constexpr int BATCH = 4;                      // ranks whose words are requested together: their latencies overlap
+    for (int r0 = 0; r0 < tp.world; r0 += BATCH) {
+        unsigned long long got[BATCH][2];
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            unsigned long long got = ptx::ld_relaxed_sys_u64(src + e);
-            uint32_t polls = 0;
-            while ((uint32_t)(got >> 32) != tp_epoch && !gave_up) {
-                if (++polls > GEMV_PEER_MAX_POLLS) {
-                    gave_up = true;
-                    atomicExch(err, GEMV_ERR_PEER_WAIT);
-                    break;
+        for (int j = 0; j < BATCH; j++) {
+            const int r = r0 + j < tp.world ? r0 + j : tp.world - 1;
+            const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * tp.slot_bytes) + word;
+            got[j][0] = ptx::ld_relaxed_sys_u64(src);
+            got[j][1] = ptx::ld_relaxed_sys_u64(src + 1);
+        }
+#pragma unroll
+        for (int j = 0; j < BATCH; j++) {
+            if (r0 + j < tp.world) {
+                const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)(r0 + j) * tp.slot_bytes) + word;
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    uint32_t polls = 0;
+                    while ((uint32_t)(got[j][e] >> 32) != tp_epoch && !gave_up) {
+                        if (++polls > GEMV_PEER_MAX_POLLS) {
+                            gave_up = true;
+                            atomicExch(err, GEMV_ERR_PEER_WAIT);
+                            break;
+                        }
+                        got[j][e] = ptx::ld_relaxed_sys_u64(src + e);
+                    }
+                    const uint32_t lo = (uint32_t)got[j][e];
+                    if (bf) {
+                        const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+                        a[2 * e] += __low2float(bb);
+                        a[2 * e + 1] += __high2float(bb);
+                    } else {
+                        const __half2 hh = *reinterpret_cast<const __half2*>(&lo);
+                        a[2 * e] += __low2float(hh);
+                        a[2 * e + 1] += __high2float(hh);
+                    }
                 }
-                got = ptx::ld_relaxed_sys_u64(src + e);
-            }
-            const uint32_t lo = (uint32_t)got;
-            if (bf) {
-                const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&lo);
-                a[2 * e] += __low2float(bb);
-                a[2 * e + 1] += __high2float(bb);
-            } else {
-                const __half2 hh = *reinterpret_cast<const __half2*>(&lo);
-                a[2 * e] += __low2float(hh);
-                a[2 * e + 1] += __high2float(hh);
             }
         }
     }
