@@ -113,8 +113,7 @@ static __device__ __noinline__ void gemv_exchange_store(const TpExchange& tp, ui
     const unsigned long long tag = (unsigned long long)tp_epoch << 32;
     for (int r = 0; r < tp.world; r++) {
         unsigned long long* dst = reinterpret_cast<unsigned long long*>(tp.base[r] + set_off + (size_t)tp.rank * tp.slot_bytes) + word;
-        ptx::st_relaxed_sys_u64(dst, tag | w2[0]);
-        ptx::st_relaxed_sys_u64(dst + 1, tag | w2[1]);
+        ptx::st_relaxed_sys_v2u64(dst, tag | w2[0], tag | w2[1]);          // word is even: 16-byte aligned
     }
     float a[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned char* own = tp.base[tp.rank] + set_off;
@@ -126,8 +125,7 @@ static __device__ __noinline__ void gemv_exchange_store(const TpExchange& tp, ui
         for (int j = 0; j < BATCH; j++) {
             const int r = r0 + j < tp.world ? r0 + j : tp.world - 1;
             const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * tp.slot_bytes) + word;
-            got[j][0] = ptx::ld_relaxed_sys_u64(src);
-            got[j][1] = ptx::ld_relaxed_sys_u64(src + 1);
+            ptx::ld_relaxed_sys_v2u64(src, got[j][0], got[j][1]);
         }
 #pragma unroll
         for (int j = 0; j < BATCH; j++) {

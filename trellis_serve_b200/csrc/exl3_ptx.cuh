@@ -86,6 +86,17 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
     return v;
 }
 
+// Two adjacent tagged words in one 16-byte access (each 8-byte half is what has to arrive whole): a warp then writes
+// full 128-byte lines over NVLink instead of half-filled ones.
+__device__ __forceinline__ void st_relaxed_sys_v2u64(unsigned long long* p, unsigned long long a, unsigned long long b)
+{
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_sys_v2u64(const unsigned long long* p, unsigned long long& a, unsigned long long& b)
+{
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
 // global -> shared bulk copy through the TMA engine; completion is counted in bytes on `bar`.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar)
