@@ -64,6 +64,20 @@ def test_argument_errors_are_statuses_not_launches():
     assert lib.exl3_linear(p, 0, p, 3, 0, p, p, ends, 2, 1, 128, 256, p, 0, p, 4096, nul) == 1    # shard end not 128-aligned
     assert lib.exl3_linear(p, 0, p, 3, 0, p, p, None, 1, 0, 128, 256, p, 0, p, 4096, nul) == 0    # rows == 0
     assert lib.exl3_device_error(nul, 0, nul) == 5
+    # the exchange entry points: geometry of the rank set and of the regions is checked before anything runs
+    regions = (ctypes.c_void_p * 2)(p, p)
+    assert lib.exl3_allreduce(p, 0, 8, regions, 2, 2, 64, p, nul) == 1                             # rank outside the world
+    assert lib.exl3_allreduce(p, 0, 12, regions, 0, 2, 64, p, nul) == 1                            # n not a multiple of 8
+    assert lib.exl3_allreduce(p, 2, 8, regions, 0, 2, 64, p, nul) == 10                            # fp32 is not exchanged
+    assert lib.exl3_allreduce(p, 0, 8, regions, 0, 1, 64, p, nul) == 0                             # a world of one: no-op
+    assert lib.exl3_linear_allreduce(p, 0, p, 3, 0, p, p, None, 1, 1, 128, 256, p, 0, p, 4096, regions, 0, 17, 64, p, nul) == 1
+    assert lib.exl3_linear_allreduce(p, 0, p, 3, 0, p, p, None, 1, 1, 128, 256, p, 2, p, 4096, regions, 0, 2, 4096, p, nul) == 10
+    assert lib.exl3_linear_allreduce(p, 0, p, 3, 0, p, p, None, 1, 1, 128, 256, p, 0, p, 4096, regions, 0, 2, 64, p, nul) == 1   # slot too small
+    assert lib.exl3_linear_allreduce(p, 0, p, 3, 0, p, p, None, 1, 0, 128, 256, p, 0, p, 4096, regions, 0, 2, 4096, p, nul) == 0  # rows == 0
+    # routing alignment of one bitrate class
+    assert lib.exl3_moe_align_mapped(p, 8, 16, p, 0, p, 64, p, p, nul) == 1                        # empty class
+    assert lib.exl3_moe_align_mapped(p, 8, 16, nul, 4, p, 64, p, p, nul) == 4                      # no expert map
+    assert lib.exl3_moe_align_mapped(p, 8, 16, p, 4, p, 8, p, p, nul) == 1                         # sorted_ids too short
 
 
 def test_missing_library_is_a_loud_error(monkeypatch):

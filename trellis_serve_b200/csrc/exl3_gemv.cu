@@ -61,26 +61,29 @@ static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLau
     l.units_q = (int)(units / grid);
     l.units_r = (int)(units % grid);
     const int fw = gemv_frag_words(a.mode);
-    // Stage = as many whole units as make one bulk copy of 32 KB or a little more; two or three stages in flight.
+    // Stage = as many whole units as make one bulk copy of 32 KB or a little more; two or three stages in flight.  When the
+    // fragment slots of the in-kernel rotation leave no room for two such stages, smaller stages are tried.
     const uint32_t unit_bytes = 2048u * a.K;
-    int ups = (int)((GEMV_STAGE_TARGET + unit_bytes - 1) / unit_bytes);
-    if (ups < 1) ups = 1;
     const long long per_cta = units / grid;
-    // Short ranges travel as one copy: the copies of a launch start while the kernel ahead of it is still finishing, so
-    // nothing is gained by cutting a small range into several copies, each of which pays the copy engine's fixed cost.
     const long long per_cta_max = per_cta + (l.units_r ? 1 : 0);
-    if (per_cta_max < ups) ups = (int)per_cta_max;
-    if (ups < 1) ups = 1;
-    l.units_per_stage = ups;
-    l.stage_stride = (uint32_t)ups * unit_bytes;
     size_t xs_bytes = 0;
     if (fused) xs_bytes = GEMV_XS_ZERO_BYTES + (size_t)(l.units_q + 1) * gemv_xs_slot_bytes(a.mode, a.rows);
     const size_t budget = (size_t)d->max_smem_optin / GEMV_CTAS_PER_SM - 2048 - GEMV_FIXED_SMEM;
-    if (xs_bytes + 2 * (size_t)l.stage_stride > budget) return EXL3_ERR_UNSUPPORTED_ROWS;
-    int stages = (int)(GEMV_RING_TARGET / l.stage_stride);
-    const int cap = (int)((budget - xs_bytes) / l.stage_stride);
-    if (stages > cap) stages = cap;
-    if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
+    int stages = 0;
+    for (size_t target = GEMV_STAGE_TARGET; target >= 8 * 1024 && stages < 2; target -= 8 * 1024) {
+        int ups = (int)((target + unit_bytes - 1) / unit_bytes);
+        // Short ranges travel as one copy: the copies of a launch start while the kernel ahead of it is still finishing,
+        // so nothing is gained by cutting a small range into several copies, each of which pays the copy engine's fixed cost.
+        if (per_cta_max < ups) ups = (int)per_cta_max;
+        if (ups < 1) ups = 1;
+        l.units_per_stage = ups;
+        l.stage_stride = (uint32_t)ups * unit_bytes;
+        if (xs_bytes + 2 * (size_t)l.stage_stride > budget) continue;
+        stages = (int)(GEMV_RING_TARGET / l.stage_stride);
+        const int cap = (int)((budget - xs_bytes) / l.stage_stride);
+        if (stages > cap) stages = cap;
+        if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
+    }
     if (stages < 2) return EXL3_ERR_UNSUPPORTED_ROWS;
     l.stages = stages;
     l.xs_off = (uint32_t)(GEMV_FIXED_SMEM + (size_t)stages * l.stage_stride);
