@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(1024, 1) allreduce_oneshot_kernel(uint16_t* __
     }
     uint32_t* dst = reinterpret_cast<uint32_t*>(data);
     const unsigned char* own = peers.base[rank] + set_off;
-    bool gave_up = false;
+    bool gave_up = false;                         // once a wait has run out the thread stops waiting for the other words too
     constexpr int BATCH = 8;                      // ranks whose words are requested together: their latencies overlap
     for (size_t i = threadIdx.x; i < nw; i += blockDim.x) {
         float a0 = 0.f, a1 = 0.f;
