@@ -49,8 +49,8 @@ def test_argument_errors_are_statuses_not_launches():
     """None of these reach a kernel launch, so they run on a machine without a GPU."""
     lib = _lib.load()
     nul = ctypes.c_void_p(0)
-    buf = ctypes.create_string_buffer(4096)
-    p = ctypes.c_void_p(ctypes.addressof(buf))
+    buf = ctypes.create_string_buffer(8192)
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 255) & ~255)           # 256-byte aligned, as device buffers are
     assert lib.exl3_repack(p, 100, 128, 4, p, nul) == 1                # k not a multiple of 128
     assert lib.exl3_repack(p, 128, 128, 9, p, nul) == 2                # K out of range
     assert lib.exl3_repack(nul, 128, 128, 4, p, nul) == 4              # null pointer

@@ -19,12 +19,21 @@ def _t(a):
     return torch.from_numpy(np.ascontiguousarray(a.view(np.int16) if a.dtype == np.uint16 else a)).to(DEV)
 
 
+@pytest.fixture(autouse=True)
+def _default_tiling():
+    yield
+    lin.set_tc_tiling(-1)
+
+
+@pytest.mark.parametrize("tiling", [0, 1])          # 512 x 128 tiles; 256 x 256 tiles (n = 384, 640 and 128 have an odd block: narrow)
 @pytest.mark.parametrize("K,cb,k,n,rows", [(4, 1, 256, 256, 130), (3, 0, 512, 384, 512), (4, 1, 1024, 640, 700),
-                                           (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025)])
-def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows):
+                                           (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025),
+                                           (3, 0, 384, 768, 300), (6, 1, 256, 512, 257)])
+def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows, tiling):
     tr, suh, svh = seeded_trellis(K * 7 + cb, k // 16, n // 16, K), seeded_signs(1, k), seeded_signs(2, n)
     x = np.random.default_rng(rows).standard_normal((rows, k)).astype(np.float16)
     packed = lin.prepare_matrix(_t(tr))
+    lin.set_tc_tiling(tiling)
     y = lin.run_tc(_t(x), packed, _t(suh).reshape(1, -1), _t(svh), [], cb)
     torch.cuda.synchronize()
     lin.device_error(torch.device(DEV))
@@ -34,8 +43,9 @@ def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows):
     assert orc.max_over_rms(got, ref) <= 4e-3, orc.max_over_rms(got, ref)
 
 
-def test_fused_group_and_bf16_through_the_tensor_core_path():
-    K, cb, k, ns, rows = 4, 1, 512, [256, 128], 300
+@pytest.mark.parametrize("ns", [[256, 128], [256, 512]])       # an odd shard boundary forces narrow tiles; even ones pair up
+def test_fused_group_and_bf16_through_the_tensor_core_path(ns):
+    K, cb, k, rows = 4, 1, 512, 300
     parts = [(seeded_trellis(80 + i, k // 16, n // 16, K), seeded_signs(81 + i, k), seeded_signs(84 + i, n)) for i, n in enumerate(ns)]
     b, suh_cat, svh_cat, ends = lin.prepare([_t(p[0]) for p in parts], [_t(p[1]) for p in parts], [_t(p[2]) for p in parts])
     x = np.random.default_rng(3).standard_normal((rows, k)).astype(np.float16)

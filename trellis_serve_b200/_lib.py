@@ -54,6 +54,7 @@ SIGNATURES = {
     "exl3_moe_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "exl3_device_error": (_i, [_vp, _sz, _vp]),
     "exl3_set_gemv_mode": (None, [_i]),
+    "exl3_set_tc_tiling": (None, [_i]),
 }
 
 

@@ -23,17 +23,30 @@
 
 namespace exl3 {
 
-constexpr int TC_M_TILES = 4;                 // 128-row accumulators per CTA tile
-constexpr int TC_ROWS = 128 * TC_M_TILES;     // 512
+constexpr int TC_ROWS = 512;                  // rows of one super tile of the A-operand layout in global memory
 constexpr int TC_KB = 64;                     // reduction block
-constexpr int TC_STAGES = 2;
-constexpr int TC_DECODE_WARPS = 8;
-constexpr int TC_THREADS = (TC_DECODE_WARPS + 2) * 32;
-constexpr uint32_t TC_A_TILE_BYTES = 128 * TC_KB * 2;                 // 16 KB
-constexpr uint32_t TC_A_STAGE_BYTES = TC_A_TILE_BYTES * TC_M_TILES;   // 64 KB
-constexpr uint32_t TC_B_STAGE_BYTES = 128 * TC_KB * 2;                // 16 KB
-constexpr uint32_t TC_STAGE_BYTES = TC_A_STAGE_BYTES + TC_B_STAGE_BYTES;
-constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES;
+constexpr uint32_t TC_A_TILE_BYTES = 128 * TC_KB * 2;                 // 16 KB: one 128-row A tile of a reduction block
+
+// Two tilings of the output.  Narrow: 512 rows x 128 columns (four accumulators), 8 decode warps, 2 stages.  Wide: 256
+// rows x 256 columns (two accumulators of 256 columns), 16 decode warps, 3 stages: an MMA of N = 256 reads 12 KB of
+// operands for twice the MACs of an N = 128 one (8 KB), which is what the shared-memory port of the SM can sustain.
+template <bool WIDE>
+struct TcTile {
+    static constexpr int M_TILES = WIDE ? 2 : 4;
+    static constexpr int NCOLS = WIDE ? 256 : 128;
+    static constexpr int NBLK = NCOLS / 128;                                  // column blocks of 128 per tile
+    static constexpr int ROWS = 128 * M_TILES;
+    static constexpr int STAGES = WIDE ? 3 : 2;
+    static constexpr int DECODE_WARPS = 8 * NBLK;
+    static constexpr int THREADS = (DECODE_WARPS + 2) * 32;
+    static constexpr uint32_t A_STAGE_BYTES = TC_A_TILE_BYTES * M_TILES;
+    static constexpr uint32_t B_STAGE_BYTES = NCOLS * TC_KB * 2;
+    static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES;
+    static constexpr uint32_t B_LBO = (NCOLS / 8) * 128;                      // bytes between k chunks of the B block
+    // kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = NCOLS
+    static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NCOLS >> 3) << 17) | ((128u >> 4) << 24);
+};
 
 enum { TC_ERR_WAIT = 3 };
 
@@ -42,7 +55,7 @@ struct GemmTcLaunch {
     const __half* xa;            // rotated activations in A-operand layout [MS][k/64][4][8][16][8][8]
     __half* out;                 // [rows][n_total] fp16, rotated basis
     int* err;
-    int rows, KG, NB, MS;        // MS = ceil(rows / 512)
+    int rows, KG, NB, MS;        // MS = ceil(rows / 512): super tiles of the A layout
     int n_total;
     int shard_end_block[GEMV_MAX_SHARDS];
     int n_shards;
@@ -52,26 +65,24 @@ struct GemmTcLaunch {
 };
 
 // Operand layout shared by A tiles and the B block: 8 x 8 fp16 core matrices of 128 contiguous bytes, core (c, j) =
-// (k chunk of 8, row group of 8) at (c * 16 + j) * 128 bytes: 2048 bytes between k chunks, 128 between row groups.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_byte_addr)
+// (k chunk of 8, row group of 8) at (c * groups + j) * 128 bytes: `lbo` = groups * 128 bytes between k chunks (2048 for a
+// 128-row operand, 4096 for the 256-column B block), 128 between row groups.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_byte_addr, uint32_t lbo)
 {
     uint64_t d = 0;
     d |= (uint64_t)((smem_byte_addr >> 4) & 0x3FFF);          // start address
-    d |= (uint64_t)(2048 >> 4) << 16;                         // leading byte offset: between the two k chunks of an MMA
+    d |= (uint64_t)(lbo >> 4) << 16;                          // leading byte offset: between the two k chunks of an MMA
     d |= (uint64_t)(128 >> 4) << 32;                          // stride byte offset: between 8-row groups
     d |= 1ull << 46;                                          // descriptor version of this architecture
     return d;                                                 // layout type 0: no swizzle
 }
 
-// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = 128
-constexpr uint32_t TC_IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate)
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(a_desc), "l"(b_desc), "r"(TC_IDESC), "r"(accumulate)
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -98,30 +109,32 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int K, int FAM>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
+template <int K, int FAM, bool WIDE>
+__global__ void __launch_bounds__(TcTile<WIDE>::THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
 {
+    using TT = TcTile<WIDE>;
+    constexpr int DW = TT::DECODE_WARPS, STAGES = TT::STAGES;
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* a_full = reinterpret_cast<uint64_t*>(smem);            // [stages]
-    uint64_t* b_full = a_full + TC_STAGES;
-    uint64_t* empty = b_full + TC_STAGES;
-    uint64_t* acc_full = empty + TC_STAGES;
+    uint64_t* b_full = a_full + STAGES;
+    uint64_t* empty = b_full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     unsigned char* stage0 = smem + 1024;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; s++) {
+        for (int s = 0; s < STAGES; s++) {
             ptx::mbar_init(&a_full[s], 1);
-            ptx::mbar_init(&b_full[s], TC_DECODE_WARPS);
+            ptx::mbar_init(&b_full[s], DW);
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(acc_full, 1);
-        ptx::mbar_init(acc_empty, TC_DECODE_WARPS);
+        ptx::mbar_init(acc_empty, DW);
         ptx::mbar_fence_init();
     }
-    if (warp == TC_DECODE_WARPS + 1) {
+    if (warp == DW + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_addr(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -131,7 +144,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
     const uint32_t tmem_base = *tmem_slot;
 
     const int KB = p.KG * 2;                           // reduction blocks of 64
-    const long long n_tiles = (long long)p.MS * p.NB;
+    const int MT = (p.rows + TT::ROWS - 1) / TT::ROWS; // row tiles
+    const int NT = p.NB / TT::NBLK;                    // column tiles
+    const long long n_tiles = (long long)MT * NT;
     bool failed = false;
     auto fail = [&]() {
         if (!failed) {
@@ -140,15 +155,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
         }
     };
 
-    if (warp < TC_DECODE_WARPS) {
+    if (warp < DW) {
         // ------------------------------------------------------------------ decode + epilogue
-        const int nt = warp, g = lane >> 2, q = lane & 3;
+        const int nt = warp & 7, nbh = warp >> 3, g = lane >> 2, q = lane & 3;
         const CodebookConst cbc = {p.mul, p.add};
         uint32_t it = 0, acc_round = 0;
         // The warp's words of the next reduction block are requested one block ahead, so their L2 latency hides
         // behind the decode of the current block.
         auto words_ptr = [&](long long tile, int kb) {
-            const int nb_ = (int)(tile / p.MS);
+            const int nb_ = (int)(tile / MT) * TT::NBLK + nbh;
             return p.packed + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
         };
         uint32_t Lnext[K];
@@ -158,10 +173,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
             for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
         }
         for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-            const int ms = (int)(t % p.MS), nb = (int)(t / p.MS);
+            const int ms = (int)(t % MT), ct = (int)(t / MT);
             for (int kb = 0; kb < KB; kb++, it++) {
-                const int s = it % TC_STAGES;
-                const uint32_t round = it / TC_STAGES;
+                const int s = it % STAGES;
+                const uint32_t round = it / STAGES;
                 uint32_t L[K];
 #pragma unroll
                 for (int i = 0; i < K; i++) L[i] = Lnext[i];
@@ -175,7 +190,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
                     }
                 }
                 if (round > 0 && !failed && !ptx::mbar_wait(&empty[s], (round - 1) & 1)) fail();
-                unsigned char* bst = stage0 + (size_t)s * TC_STAGE_BYTES + TC_A_STAGE_BYTES;
+                unsigned char* bst = stage0 + (size_t)s * TT::STAGE_BYTES + TT::A_STAGE_BYTES;
                 auto tile = [&](auto tconst) {
                     constexpr int T = decltype(tconst)::value;
                     uint32_t own[2];
@@ -190,11 +205,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
 #pragma unroll
                     for (int j = 0; j < 4; j++)
                         w[j] = FAM == FAM_HASH ? hash_pair_rounded(st[2 * j], st[2 * j + 1], cbc) : mul1_pair(st[2 * j], st[2 * j + 1], cbc);
-                    // pair j: k chunk 2T + (j & 1), column group 2nt + (j >> 1), row g of the core matrix, bytes 4q..4q+3
+                    // pair j: k chunk 2T + (j & 1), column group 2 * (8 * nbh + nt) + (j >> 1), row g of the core matrix, bytes 4q..4q+3
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        const int c = 2 * T + (j & 1), jn = 2 * nt + (j >> 1);
-                        *reinterpret_cast<uint32_t*>(bst + (c * 16 + jn) * 128 + g * 16 + q * 4) = w[j];
+                        const int c = 2 * T + (j & 1), jn = 2 * (8 * nbh + nt) + (j >> 1);
+                        *reinterpret_cast<uint32_t*>(bst + (c * (TT::NCOLS / 8) + jn) * 128 + g * 16 + q * 4) = w[j];
                     }
                 };
                 tile(std::integral_constant<int, 0>{});
@@ -205,20 +220,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&b_full[s]);
             }
-            // ---- epilogue of this tile: accumulators -> fp16 rows
+            // ---- epilogue of this tile: accumulators -> fp16 rows.  A warp reads the 32 tensor-memory lanes of its
+            // quarter (warp % 4) and 64 of the tile's columns.
             if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
             tc_fence_after();
-            const int quarter = warp & 3, half = warp >> 2;
+            const int quarter = warp & 3, cgroup = warp >> 2;
 #pragma unroll 1
-            for (int mt = 0; mt < TC_M_TILES; mt++) {
-                const int row = ms * TC_ROWS + mt * 128 + quarter * 32 + lane;
+            for (int mt = 0; mt < TT::M_TILES; mt++) {
+                const int row = ms * TT::ROWS + mt * 128 + quarter * 32 + lane;
 #pragma unroll 1
                 for (int cc = 0; cc < 2; cc++) {
-                    const int col = half * 64 + cc * 32;
+                    const int col = cgroup * 64 + cc * 32;
                     uint32_t r[32];
-                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * 128 + col), r);
+                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * TT::NCOLS + col), r);
                     if (row < p.rows) {
-                        __half* dst = p.out + (size_t)row * p.n_total + nb * 128 + col;
+                        __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
 #pragma unroll
                         for (int v = 0; v < 32; v += 8) {
                             uint4 o;
@@ -240,21 +256,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
             if (lane == 0) ptx::mbar_arrive(acc_empty);
             acc_round++;
         }
-    } else if (warp == TC_DECODE_WARPS) {
+    } else if (warp == DW) {
         // ------------------------------------------------------------------ A producer
         if (lane == 0) {
             uint32_t it = 0;
             for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-                const int ms = (int)(t % p.MS), nb = (int)(t / p.MS);
+                const int ms = (int)(t % MT), nb = (int)(t / MT) * TT::NBLK;
                 int shard = 0;
                 while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
+                // the A layout in global memory is in super tiles of 512 rows = four 128-row tiles per reduction block
+                const int row0 = ms * TT::ROWS;
+                const int super = row0 / TC_ROWS, mt0 = (row0 % TC_ROWS) >> 7;
                 for (int kb = 0; kb < KB; kb++, it++) {
-                    const int s = it % TC_STAGES;
-                    const uint32_t round = it / TC_STAGES;
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
                     if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
-                    const __half* src = p.xa + shard * p.xa_shard_stride + ((long long)ms * KB + kb) * (TC_A_STAGE_BYTES / 2);
-                    ptx::mbar_arrive_expect_tx(&a_full[s], TC_A_STAGE_BYTES);
-                    ptx::bulk_g2s(stage0 + (size_t)s * TC_STAGE_BYTES, src, TC_A_STAGE_BYTES, &a_full[s]);
+                    const __half* src = p.xa + shard * p.xa_shard_stride + (((long long)super * KB + kb) * 4 + mt0) * (TC_A_TILE_BYTES / 2);
+                    ptx::mbar_arrive_expect_tx(&a_full[s], TT::A_STAGE_BYTES);
+                    ptx::bulk_g2s(stage0 + (size_t)s * TT::STAGE_BYTES, src, TT::A_STAGE_BYTES, &a_full[s]);
                 }
             }
         }
@@ -266,19 +285,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
                 if (acc_round > 0 && !failed && !ptx::mbar_wait(acc_empty, (acc_round - 1) & 1)) fail();
                 tc_fence_after();
                 for (int kb = 0; kb < KB; kb++, it++) {
-                    const int s = it % TC_STAGES;
-                    const uint32_t round = it / TC_STAGES;
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
                     if (!failed && !ptx::mbar_wait(&a_full[s], round & 1)) fail();
                     if (!failed && !ptx::mbar_wait(&b_full[s], round & 1)) fail();
                     tc_fence_after();
-                    const uint32_t a_addr = ptx::smem_addr(stage0 + (size_t)s * TC_STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + TC_A_STAGE_BYTES;
+                    const uint32_t a_addr = ptx::smem_addr(stage0 + (size_t)s * TT::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TT::A_STAGE_BYTES;
 #pragma unroll
-                    for (int mt = 0; mt < TC_M_TILES; mt++)
+                    for (int mt = 0; mt < TT::M_TILES; mt++)
 #pragma unroll
                         for (int ks = 0; ks < TC_KB / 16; ks++)
-                            tc_mma(tmem_base + (uint32_t)(mt * 128), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096),
-                                   tc_smem_desc(b_addr + ks * 4096), (kb > 0 || ks > 0) ? 1u : 0u);
+                            tc_mma(tmem_base + (uint32_t)(mt * TT::NCOLS), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096, 2048),
+                                   tc_smem_desc(b_addr + ks * 2 * TT::B_LBO, TT::B_LBO), TT::IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
                     tc_commit(&empty[s]);               // stage reusable once these MMAs have read it
                 }
                 tc_commit(acc_full);                    // accumulators complete
@@ -289,7 +308,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmTcLaun
 
     tc_fence_before();
     __syncthreads();
-    if (warp == TC_DECODE_WARPS + 1) {
+    if (warp == DW + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
@@ -323,30 +342,35 @@ __global__ void had_in_tc_kernel(const void* __restrict__ x, int x_bf16, const _
     const int kb = kg * 2 + (kk >> 6), c = (kk & 63) >> 3, e0 = kk & 7;
     const int ms = row / TC_ROWS, mt = (row % TC_ROWS) >> 7, j = (row & 127) >> 3, rr = row & 7;
     const long long KB = (long long)kgs * 2;
-    const long long off = ((((((long long)ms * KB + kb) * TC_M_TILES + mt) * 8 + c) * 16 + j) * 8 + rr) * 8 + e0;
+    const long long off = ((((((long long)ms * KB + kb) * 4 + mt) * 8 + c) * 16 + j) * 8 + rr) * 8 + e0;
     *reinterpret_cast<uint2*>(xa + s * shard_stride + off) = *reinterpret_cast<uint2*>(h);
 }
 
-template <int K>
-static int launch_tc_k(const GemmTcLaunch& l, int fam, int grid, cudaStream_t st)
+template <int K, int FAM, bool WIDE>
+static int launch_tc_variant(const GemmTcLaunch& l, int sm_count, cudaStream_t st)
 {
-    if (fam == FAM_HASH) {
-        static bool attr_hash = false;
-        if (!attr_hash) {
-            if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_HASH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES))) return rc;
-            attr_hash = true;
-        }
-        gemm_tc_kernel<K, FAM_HASH><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(l);
-    } else {
-        static bool attr_mul1 = false;
-        if (!attr_mul1) {
-            if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_MUL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES))) return rc;
-            attr_mul1 = true;
-        }
-        gemm_tc_kernel<K, FAM_MUL1><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(l);
+    using TT = TcTile<WIDE>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TT::SMEM_BYTES)))
+            return rc;
+        attr_set = true;
     }
+    const long long tiles = (long long)((l.rows + TT::ROWS - 1) / TT::ROWS) * (l.NB / TT::NBLK);
+    const int grid = tiles < sm_count ? (int)tiles : sm_count;
+    gemm_tc_kernel<K, FAM, WIDE><<<grid, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
     return cuda_status(cudaGetLastError());
 }
+
+template <int K>
+static int launch_tc_k(const GemmTcLaunch& l, int fam, bool wide, int sm_count, cudaStream_t st)
+{
+    if (fam == FAM_HASH) return wide ? launch_tc_variant<K, FAM_HASH, true>(l, sm_count, st) : launch_tc_variant<K, FAM_HASH, false>(l, sm_count, st);
+    return wide ? launch_tc_variant<K, FAM_MUL1, true>(l, sm_count, st) : launch_tc_variant<K, FAM_MUL1, false>(l, sm_count, st);
+}
+
+static int g_tc_tiling = -1;          // -1 = choose; 0 = narrow (512 x 128); 1 = wide (256 x 256) where the shape allows
+void gemm_tc_set_tiling(int t) { g_tc_tiling = t; }
 
 size_t gemm_tc_activation_bytes(int rows, int k, int shards)
 {
@@ -381,18 +405,21 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
     const long long items = (long long)n_shards * rows * (k / 128);
     had_in_tc_kernel<<<(unsigned)((items + 7) / 8), 256, 0, st>>>(x, x_bf16, suh_cat, n_shards, rows, k, xa, l.xa_shard_stride);
     if (int rc = cuda_status(cudaGetLastError())) return rc;
-    const long long tiles = (long long)l.MS * l.NB;
-    int grid = d->sm_count;
-    if (tiles < grid) grid = (int)tiles;
+    // Wide tiles (256 x 256) need column blocks that pair up inside every shard.  They halve the rows that share a decoded
+    // weight block, which makes the decode the limiter at large row counts (measured: 823 against 851 TFLOP/s at 2048
+    // rows), but they waste no rows when there are at most 256 (703 against 457 TFLOP/s): chosen only then.
+    bool can_wide = (l.NB % 2) == 0;
+    for (int s = 0; s < n_shards - 1; s++) can_wide = can_wide && (shard_end_blocks[s] % 2) == 0;
+    const bool wide = can_wide && (g_tc_tiling >= 0 ? g_tc_tiling == 1 : rows <= 256);
     const int fam = codebook_family(codebook);
     switch (K) {
-        case 2: return launch_tc_k<2>(l, fam, grid, st);
-        case 3: return launch_tc_k<3>(l, fam, grid, st);
-        case 4: return launch_tc_k<4>(l, fam, grid, st);
-        case 5: return launch_tc_k<5>(l, fam, grid, st);
-        case 6: return launch_tc_k<6>(l, fam, grid, st);
-        case 7: return launch_tc_k<7>(l, fam, grid, st);
-        case 8: return launch_tc_k<8>(l, fam, grid, st);
+        case 2: return launch_tc_k<2>(l, fam, wide, d->sm_count, st);
+        case 3: return launch_tc_k<3>(l, fam, wide, d->sm_count, st);
+        case 4: return launch_tc_k<4>(l, fam, wide, d->sm_count, st);
+        case 5: return launch_tc_k<5>(l, fam, wide, d->sm_count, st);
+        case 6: return launch_tc_k<6>(l, fam, wide, d->sm_count, st);
+        case 7: return launch_tc_k<7>(l, fam, wide, d->sm_count, st);
+        case 8: return launch_tc_k<8>(l, fam, wide, d->sm_count, st);
     }
     return EXL3_ERR_UNSUPPORTED_K;
 }

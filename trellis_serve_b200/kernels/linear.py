@@ -306,6 +306,11 @@ def device_error(device: torch.device) -> None:
                        "exl3_device_error")
 
 
+def set_tc_tiling(tiling: int) -> None:
+    """Knob: output tiling of `run_tc`: -1 default, 0 tiles of 512 x 128, 1 tiles of 256 x 256 (where the shape allows)."""
+    _lib.load().exl3_set_tc_tiling(int(tiling))
+
+
 def set_gemv_mode(mode: int) -> None:
     """Knob: -1 default, 0 split (two fp16 summands per weight, added in fp32), 1 paired (weights rounded to fp16)."""
     _lib.load().exl3_set_gemv_mode(int(mode))
