@@ -87,7 +87,10 @@ exl3_status exl3_had_out(const void *y, int y_dtype, const uint16_t *svh, int ro
  * multiples of 128.  x_dtype: EXL3_F16 or EXL3_BF16; y_dtype: EXL3_F16, EXL3_BF16 (the fp16 result converted) or
  * EXL3_F32 (the fp32 accumulators unrounded, for accuracy measurements).  y must be 16-byte aligned.
  * Replaces exl3_linear_marlin_out / exl3_linear_marlin_multi_out (cuda/csrc/exl3_marlin.cu:489-527).
- * The workspace must be zero-filled once after allocation; every call leaves it reusable. */
+ * The workspace must be zero-filled once after allocation; every call leaves it reusable, also by calls with other
+ * shapes and by the MoE entry points: it starts with a 256-byte header and a fixed 512 KB of counters that every launch
+ * leaves zero, and only scratch lies behind them (so n_total / 128, and for the MoE kernel moe blocks x column blocks,
+ * may not exceed 131072: EXL3_ERR_BAD_SHAPE). */
 size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards);
 exl3_status exl3_linear(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
                         const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,

@@ -275,3 +275,28 @@ def test_unsupported_requests_raise():
         lin.prepare_matrix(torch.zeros((8, 8, 48), dtype=torch.int16))                   # CPU tensor: no fallback
     ok, why = lin.supports([torch.zeros((8, 8, 24), dtype=torch.int16)], [128], [0])
     assert not ok and "K" in why
+
+
+@pytest.mark.parametrize("rows", [1, 4, 9])
+def test_one_workspace_serves_calls_of_any_shape_in_any_order(rows):
+    """The workspace is shared by every call on a device.  The split-k counters must read zero at the start of each launch
+    whatever ran before: a wide matrix after a narrow one (whose scratch once lay where the wide one's counters are),
+    and back, gives the bits of the same call on a fresh workspace."""
+    dev = torch.device(DEV)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+
+    def make(k, n):
+        return random_packed(k, n, 3, gen, dev), random_signs(k, gen, dev, 1), (random_signs(n, gen, dev).view(-1) / 16).half()
+    narrow, wide = make(2048, 1024), make(1024, 34816)
+    xn = torch.randn((rows, 2048), device=dev, generator=gen).half()
+    xw = torch.randn((rows, 1024), device=dev, generator=gen).half()
+    lin._workspace.clear()
+    fresh_wide = lin.run(xw, *wide, [], 0).clone()
+    lin._workspace.clear()
+    fresh_narrow = lin.run(xn, *narrow, [], 0).clone()
+    for _ in range(2):
+        assert torch.equal(lin.run(xw, *wide, [], 0), fresh_wide)
+        assert torch.equal(lin.run(xn, *narrow, [], 0), fresh_narrow)
+    lin.device_error(dev)

@@ -181,6 +181,7 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
     if (!rotated && x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16 && !(y_dtype == EXL3_F32 && !rotated)) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
+    if ((size_t)(n_total / 128) > WS_MAX_COUNTERS) return EXL3_ERR_BAD_SHAPE;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
     if (!aligned(packed, 16) || !aligned(y, 16)) return EXL3_ERR_BAD_POINTER;
     if (rotated ? !aligned(xh_rowmajor, 2) : (!aligned(x, 2) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8)))
@@ -352,8 +353,8 @@ static MoeWorkspace moe_workspace(int cap, int n_total)
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t col_blocks = (size_t)(cap / MOE_BLOCK_ROWS) * (n_total / 128);
     MoeWorkspace w;
-    w.counters_off = 256;
-    w.partials_off = up(w.counters_off + col_blocks * sizeof(int));
+    w.counters_off = WS_HEADER_BYTES;
+    w.partials_off = WS_SCRATCH_OFF;
     w.total = up(w.partials_off + (GEMV_MAX_GRID + col_blocks) * MOE_BLOCK_ROWS * 128 * sizeof(float));
     return w;
 }
@@ -438,6 +439,7 @@ exl3_status exl3_moe_gemm(const uint32_t* xf, const uint32_t* packed, int K, int
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (cap < 0 || (cap % MOE_BLOCK_ROWS) || slots < 0 || shard_end < 0 || shard_end > n_total || (shard_end % 128)) return EXL3_ERR_BAD_SHAPE;
     if (cap == 0 || k == 0 || n_total == 0) return EXL3_OK;
+    if ((size_t)(cap / MOE_BLOCK_ROWS) * (size_t)(n_total / 128) > WS_MAX_COUNTERS) return EXL3_ERR_BAD_SHAPE;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
     if (!aligned(xf, 16) || !aligned(packed, 16) || !aligned(out, 8) || (svh && !aligned(svh, 8)) || !aligned(sorted_ids, 4) ||
         !aligned(expert_ids, 4) || !aligned(num_post, 4))

@@ -24,8 +24,8 @@ WorkspaceLayout workspace_layout(int rows, int k, int n_total, int n_shards)
     const int r = rows < GEMV_MAX_ROWS ? (rows < 1 ? 1 : rows) : GEMV_MAX_ROWS;
     WorkspaceLayout w;
     w.err_off = 0;
-    w.counters_off = 256;
-    w.xf_off = up(w.counters_off + (size_t)(n_total / 128) * sizeof(int));
+    w.counters_off = WS_HEADER_BYTES;
+    w.xf_off = WS_SCRATCH_OFF;
     w.partials_off = up(w.xf_off + (size_t)n_shards * (k / 16) * r * 4 * 4 * sizeof(uint32_t));
     w.total = up(w.partials_off + (size_t)(GEMV_MAX_GRID + n_total / 128) * r * 128 * sizeof(float));
     return w;

@@ -129,6 +129,13 @@ inline int launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return cuda_status(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 
+// Every workspace starts with a 256-byte header (error word, zeros) and a counters region of FIXED size: the counters
+// must read zero at the start of every launch whatever the shapes of the launches before it, so nothing else may ever be
+// laid over them; the regions behind are scratch that each launch overwrites.
+constexpr size_t WS_HEADER_BYTES = 256;
+constexpr size_t WS_MAX_COUNTERS = 131072;                       // column blocks (dense) or moe block x column block pairs
+constexpr size_t WS_SCRATCH_OFF = WS_HEADER_BYTES + WS_MAX_COUNTERS * sizeof(int);
+
 // Workspace carved up identically by every entry point that takes one.
 struct WorkspaceLayout {
     size_t err_off, counters_off, xf_off, partials_off, total;
