@@ -209,7 +209,7 @@ exl3_status exl3_device_error(void *workspace, size_t workspace_bytes, void *str
  * 1 = paired (weights rounded to fp16 first, as the reference decoder's table).  No counterpart in the reference. */
 void exl3_set_gemv_mode(int mode);
 /* Measurement / test knob: output tiling of exl3_linear_tc.  -1 = library default, 0 = 512 x 128 tiles, 1 = 256 x 256 tiles
- * (used only where the column blocks pair up inside every shard).  No counterpart in the reference. */
+ * (used only where the column blocks pair up inside every shard), 2 = 384 x 128 tiles.  No counterpart in the reference. */
 void exl3_set_tc_tiling(int tiling);
 
 #ifdef __cplusplus

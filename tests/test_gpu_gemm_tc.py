@@ -25,7 +25,7 @@ def _default_tiling():
     lin.set_tc_tiling(-1)
 
 
-@pytest.mark.parametrize("tiling", [0, 1])          # 512 x 128 tiles; 256 x 256 tiles (n = 384, 640 and 128 have an odd block: narrow)
+@pytest.mark.parametrize("tiling", [0, 1, 2])       # 512 x 128; 256 x 256 (n = 384, 640, 128 have an odd block: narrow); 384 x 128
 @pytest.mark.parametrize("K,cb,k,n,rows", [(4, 1, 256, 256, 130), (3, 0, 512, 384, 512), (4, 1, 1024, 640, 700),
                                            (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025),
                                            (3, 0, 384, 768, 300), (6, 1, 256, 512, 257)])

@@ -514,7 +514,7 @@ size_t exl3_static_workspace_bytes(void) { return EXL3_STATIC_WORKSPACE_BYTES; }
 /* Test / measurement knob: force how hash-codebook weights enter the MMA (-1 default, 0 split, 1 paired). */
 void exl3_set_gemv_mode(int mode) { gemv_set_mode_override(mode); }
 
-/* Test / measurement knob: output tiling of the many-row tensor-core GEMM (-1 choose, 0 narrow 512 x 128, 1 wide 256 x 256). */
+/* Test / measurement knob: output tiling of the many-row tensor-core GEMM (-1 choose, 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128). */
 void exl3_set_tc_tiling(int tiling) { gemm_tc_set_tiling(tiling); }
 
 }  // extern "C"

@@ -27,12 +27,13 @@ constexpr int TC_ROWS = 512;                  // rows of one super tile of the A
 constexpr int TC_KB = 64;                     // reduction block
 constexpr uint32_t TC_A_TILE_BYTES = 128 * TC_KB * 2;                 // 16 KB: one 128-row A tile of a reduction block
 
-// Two tilings of the output.  Narrow: 512 rows x 128 columns (four accumulators), 8 decode warps, 2 stages.  Wide: 256
-// rows x 256 columns (two accumulators of 256 columns), 16 decode warps, 3 stages: an MMA of N = 256 reads 12 KB of
+// Tilings of the output.  Narrow: MT x 128 rows by 128 columns (MT = 4 or 3 accumulators), 8 decode warps, 2 stages.  Wide:
+// 256 rows x 256 columns (two accumulators of 256 columns), 16 decode warps, 3 stages: an MMA of N = 256 reads 12 KB of
 // operands for twice the MACs of an N = 128 one (8 KB), which is what the shared-memory port of the SM can sustain.
-template <bool WIDE>
+template <int MT, bool WIDE>
 struct TcTile {
-    static constexpr int M_TILES = WIDE ? 2 : 4;
+    static_assert(!WIDE || MT == 2, "the wide tiling has two accumulators");
+    static constexpr int M_TILES = MT;
     static constexpr int NCOLS = WIDE ? 256 : 128;
     static constexpr int NBLK = NCOLS / 128;                                  // column blocks of 128 per tile
     static constexpr int ROWS = 128 * M_TILES;
@@ -109,10 +110,10 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int K, int FAM, bool WIDE>
-__global__ void __launch_bounds__(TcTile<WIDE>::THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
+template <int K, int FAM, int MT_, bool WIDE>
+__global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
 {
-    using TT = TcTile<WIDE>;
+    using TT = TcTile<MT_, WIDE>;
     constexpr int DW = TT::DECODE_WARPS, STAGES = TT::STAGES;
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* a_full = reinterpret_cast<uint64_t*>(smem);            // [stages]
@@ -264,16 +265,22 @@ __global__ void __launch_bounds__(TcTile<WIDE>::THREADS, 1) gemm_tc_kernel(const
                 const int ms = (int)(t % MT), nb = (int)(t / MT) * TT::NBLK;
                 int shard = 0;
                 while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
-                // the A layout in global memory is in super tiles of 512 rows = four 128-row tiles per reduction block
-                const int row0 = ms * TT::ROWS;
-                const int super = row0 / TC_ROWS, mt0 = (row0 % TC_ROWS) >> 7;
+                // The A layout in global memory is in super tiles of 512 rows = four 128-row tiles of 16 KB per reduction
+                // block; the tile's 128-row tiles are fetched one by one (a 384-row tile may straddle two super tiles, and
+                // its last 128-row tiles may lie beyond the padded rows: those are not fetched, their products are never stored).
+                const int t128 = ms * TT::M_TILES;
+                int present = p.MS * 4 - t128;
+                if (present > TT::M_TILES) present = TT::M_TILES;
                 for (int kb = 0; kb < KB; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
-                    const __half* src = p.xa + shard * p.xa_shard_stride + (((long long)super * KB + kb) * 4 + mt0) * (TC_A_TILE_BYTES / 2);
-                    ptx::mbar_arrive_expect_tx(&a_full[s], TT::A_STAGE_BYTES);
-                    ptx::bulk_g2s(stage0 + (size_t)s * TT::STAGE_BYTES, src, TT::A_STAGE_BYTES, &a_full[s]);
+                    ptx::mbar_arrive_expect_tx(&a_full[s], (uint32_t)present * TC_A_TILE_BYTES);
+                    for (int mt = 0; mt < present; mt++) {
+                        const int idx = t128 + mt;
+                        const __half* src = p.xa + shard * p.xa_shard_stride + (((long long)(idx >> 2) * KB + kb) * 4 + (idx & 3)) * (TC_A_TILE_BYTES / 2);
+                        ptx::bulk_g2s(stage0 + (size_t)s * TT::STAGE_BYTES + (size_t)mt * TC_A_TILE_BYTES, src, TC_A_TILE_BYTES, &a_full[s]);
+                    }
                 }
             }
         }
@@ -346,30 +353,38 @@ __global__ void had_in_tc_kernel(const void* __restrict__ x, int x_bf16, const _
     *reinterpret_cast<uint2*>(xa + s * shard_stride + off) = *reinterpret_cast<uint2*>(h);
 }
 
-template <int K, int FAM, bool WIDE>
+template <int K, int FAM, int MT, bool WIDE>
 static int launch_tc_variant(const GemmTcLaunch& l, int sm_count, cudaStream_t st)
 {
-    using TT = TcTile<WIDE>;
+    using TT = TcTile<MT, WIDE>;
     static bool attr_set = false;
     if (!attr_set) {
-        if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TT::SMEM_BYTES)))
+        if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, MT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TT::SMEM_BYTES)))
             return rc;
         attr_set = true;
     }
     const long long tiles = (long long)((l.rows + TT::ROWS - 1) / TT::ROWS) * (l.NB / TT::NBLK);
     const int grid = tiles < sm_count ? (int)tiles : sm_count;
-    gemm_tc_kernel<K, FAM, WIDE><<<grid, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
+    gemm_tc_kernel<K, FAM, MT, WIDE><<<grid, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
     return cuda_status(cudaGetLastError());
 }
 
-template <int K>
-static int launch_tc_k(const GemmTcLaunch& l, int fam, bool wide, int sm_count, cudaStream_t st)
+// tiling: 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128
+template <int K, int FAM>
+static int launch_tc_fam(const GemmTcLaunch& l, int tiling, int sm_count, cudaStream_t st)
 {
-    if (fam == FAM_HASH) return wide ? launch_tc_variant<K, FAM_HASH, true>(l, sm_count, st) : launch_tc_variant<K, FAM_HASH, false>(l, sm_count, st);
-    return wide ? launch_tc_variant<K, FAM_MUL1, true>(l, sm_count, st) : launch_tc_variant<K, FAM_MUL1, false>(l, sm_count, st);
+    if (tiling == 1) return launch_tc_variant<K, FAM, 2, true>(l, sm_count, st);
+    if (tiling == 2) return launch_tc_variant<K, FAM, 3, false>(l, sm_count, st);
+    return launch_tc_variant<K, FAM, 4, false>(l, sm_count, st);
 }
 
-static int g_tc_tiling = -1;          // -1 = choose; 0 = narrow (512 x 128); 1 = wide (256 x 256) where the shape allows
+template <int K>
+static int launch_tc_k(const GemmTcLaunch& l, int fam, int tiling, int sm_count, cudaStream_t st)
+{
+    return fam == FAM_HASH ? launch_tc_fam<K, FAM_HASH>(l, tiling, sm_count, st) : launch_tc_fam<K, FAM_MUL1>(l, tiling, sm_count, st);
+}
+
+static int g_tc_tiling = -1;          // -1 = choose; 0 = 512 x 128; 1 = 256 x 256 where the shape allows; 2 = 384 x 128
 void gemm_tc_set_tiling(int t) { g_tc_tiling = t; }
 
 size_t gemm_tc_activation_bytes(int rows, int k, int shards)
@@ -401,25 +416,37 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
     l.mul = c.mul;
     l.add = c.add;
     for (int i = 0; i <= 16; i++) l.pw.v[i] = 1u << i;
-    if (int rc = cuda_status(cudaMemsetAsync(xa, 0, gemm_tc_activation_bytes(rows, k, n_shards), st))) return rc;
+    // Rows beyond `rows` inside the last 512-row super tile must read as zeros; with whole super tiles there are none.
+    if (rows % TC_ROWS != 0)
+        if (int rc = cuda_status(cudaMemsetAsync(xa, 0, gemm_tc_activation_bytes(rows, k, n_shards), st))) return rc;
     const long long items = (long long)n_shards * rows * (k / 128);
     had_in_tc_kernel<<<(unsigned)((items + 7) / 8), 256, 0, st>>>(x, x_bf16, suh_cat, n_shards, rows, k, xa, l.xa_shard_stride);
     if (int rc = cuda_status(cudaGetLastError())) return rc;
     // Wide tiles (256 x 256) need column blocks that pair up inside every shard.  They halve the rows that share a decoded
     // weight block, which makes the decode the limiter at large row counts (measured: 823 against 851 TFLOP/s at 2048
-    // rows), but they waste no rows when there are at most 256 (703 against 457 TFLOP/s): chosen only then.
+    // rows), but they waste no rows when there are at most 256 (703 against 457 TFLOP/s): chosen only then.  Above that,
+    // 384-row tiles are taken instead of 512-row ones when they finish in less time: cost = waves of tiles over the SMs x
+    // rows per tile (160 tiles of 512 rows on 148 SMs are two waves; 240 tiles of 384 rows are two shorter ones).
     bool can_wide = (l.NB % 2) == 0;
     for (int s = 0; s < n_shards - 1; s++) can_wide = can_wide && (shard_end_blocks[s] % 2) == 0;
-    const bool wide = can_wide && (g_tc_tiling >= 0 ? g_tc_tiling == 1 : rows <= 256);
+    int tiling = g_tc_tiling;
+    if (tiling < 0) {
+        auto cost = [&](int mt) {
+            const long long tiles = (long long)((rows + 128 * mt - 1) / (128 * mt)) * l.NB;
+            return (tiles + d->sm_count - 1) / d->sm_count * mt;
+        };
+        tiling = rows <= 256 ? 1 : (cost(3) < cost(4) ? 2 : 0);
+    }
+    if (tiling == 1 && !can_wide) tiling = 0;
     const int fam = codebook_family(codebook);
     switch (K) {
-        case 2: return launch_tc_k<2>(l, fam, wide, d->sm_count, st);
-        case 3: return launch_tc_k<3>(l, fam, wide, d->sm_count, st);
-        case 4: return launch_tc_k<4>(l, fam, wide, d->sm_count, st);
-        case 5: return launch_tc_k<5>(l, fam, wide, d->sm_count, st);
-        case 6: return launch_tc_k<6>(l, fam, wide, d->sm_count, st);
-        case 7: return launch_tc_k<7>(l, fam, wide, d->sm_count, st);
-        case 8: return launch_tc_k<8>(l, fam, wide, d->sm_count, st);
+        case 2: return launch_tc_k<2>(l, fam, tiling, d->sm_count, st);
+        case 3: return launch_tc_k<3>(l, fam, tiling, d->sm_count, st);
+        case 4: return launch_tc_k<4>(l, fam, tiling, d->sm_count, st);
+        case 5: return launch_tc_k<5>(l, fam, tiling, d->sm_count, st);
+        case 6: return launch_tc_k<6>(l, fam, tiling, d->sm_count, st);
+        case 7: return launch_tc_k<7>(l, fam, tiling, d->sm_count, st);
+        case 8: return launch_tc_k<8>(l, fam, tiling, d->sm_count, st);
     }
     return EXL3_ERR_UNSUPPORTED_K;
 }

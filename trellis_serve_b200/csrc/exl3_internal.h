@@ -101,7 +101,7 @@ int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, in
 
 // exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
 size_t gemm_tc_activation_bytes(int rows, int k, int shards);
-void gemm_tc_set_tiling(int t);             // -1 = choose; 0 = 512 x 128 tiles; 1 = 256 x 256 tiles where the shape allows
+void gemm_tc_set_tiling(int t);             // -1 = choose; 0 = 512 x 128 tiles; 1 = 256 x 256 tiles where the shape allows; 2 = 384 x 128 tiles
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
                    int n_shards, int rows, int k, int n_total, __half* xa, __half* out, int* err, cudaStream_t st);
 
