@@ -362,6 +362,10 @@ def main() -> None:
         # (the step also contains the small activation-rotation kernels), so `achieved` is a lower bound.
         avg_launch_ms = ms_step / gemv_launches
         achieved = per_rank_bytes / gemv_launches / (avg_launch_ms * 1e-3) / 1e9
+        # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of the captured gate|up launch
+        # (profiles/gemv_kernel_27b_k3_batch1.md: 67.015 MB + 0.458 MB for 66.847 MB of packed weights) scaled to the
+        # average launch by its units; the kernel reads every weight byte exactly once, so traffic grows with the units.
+        traffic = (67.015e6 + 0.458e6) / 66.847e6 * per_rank_bytes / gemv_launches
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
                 "data": "synthetic",
@@ -371,7 +375,8 @@ def main() -> None:
                            "packed_bytes_per_step": total_bytes},
                 "tok_s": 1e3 / ms_step,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "gemv_kernel",
+                             "traffic": traffic, "traffic_unit": "bytes per launch, from one ncu capture scaled by units",
+                             "peak_source": f"of {peak_kind}", "kernel": "gemv_kernel",
                              "launches_per_step": gemv_launches, "avg_launch_ms_upper_bound": avg_launch_ms},
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": sum(h.numel() * h.element_size() for h in hx),
