@@ -11,7 +11,7 @@ registered as `torch.ops.exl3_b200.linear`, with a fake (meta) implementation so
 `trellis`, `suh`, `svh` (the stored tensors) are optional here: the resident layout alone serves every path.
 `dense` may hold resident decoded fp16 weights per matrix; `sliced` is accepted for schema compatibility and unused.
 
-Dispatch (there is a single backend, so it collapses to two paths, SURVEY of the reference: ops.py:79-95):
+Dispatch (there is a single backend, so the reference's ladder, ops.py:79-95, collapses to two paths):
 
   rows <  DENSE_ROWS        fused decode kernel (weights streamed once per 16 rows)
   rows >= DENSE_ROWS        many-row path: the fused tcgen05 kernel (`kernels.linear.run_tc`: weights decoded once per
