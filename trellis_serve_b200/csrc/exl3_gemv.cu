@@ -47,7 +47,7 @@ int gemv_init_device()
 }
 
 // Work split and shared-memory plan of one launch.  With `fused` the fragment slots of the in-kernel rotation are
-// budgeted first and the ring takes what is left; an error status when that leaves fewer than three stages.
+// budgeted first and the ring takes what is left; an error status when that leaves fewer than two stages.
 static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLaunch& l, size_t& smem)
 {
     l.a = a;
