@@ -183,3 +183,25 @@ def test_mixed_bitrate_layer_matches_the_float64_reference(tokens, zipf):
     assert orc.rel_norm(got, ref) <= 3e-3, orc.rel_norm(got, ref)
     assert orc.max_over_rms(got, ref) <= 8e-3, orc.max_over_rms(got, ref)
     assert torch.equal(moe.forward_mixed(xt, wt, it, pack), y)              # deterministic, alignment included
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_shares_add_up_to_the_layer(world):
+    """Expert parallelism emulated on one device: every rank's pack holds only its experts (slots of the others belong to
+    no class and add nothing), the ranks' outputs summed in fp32 are the whole layer."""
+    Ks = [3, 4, 3, 3, 4, 3, 4, 3, 3, 3]
+    E, hidden, inter, top_k, cb, tokens = len(Ks), 256, 128, 3, 0, 17
+    gate, up, down = _mixed_experts(8100, Ks, hidden, inter)
+    ids, w = _routing(tokens, top_k, E, 321)
+    x = np.random.default_rng(9).standard_normal((tokens, hidden)).astype(np.float16)
+    xt, wt, it = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV), torch.from_numpy(ids).to(DEV)
+    total = torch.zeros((tokens, hidden), dtype=torch.float32, device=DEV)
+    for rank in range(world):
+        share = moe.expert_partition(E, rank, world)
+        pack = moe.prepare_mixed(_to_dev(gate), _to_dev(up), _to_dev(down), cb, experts=share)
+        assert not pack.covers_all and sorted(int(e) for m in pack.expert_ids for e in m.tolist()) == list(share)
+        total += moe.forward_expert_parallel(xt, wt, it, pack, reduce=lambda t: t).float()
+    ref = orc.np_moe_layer(x, ids, w, gate, up, down, Ks, cb)
+    got = total.cpu().numpy()
+    assert orc.rel_norm(got, ref) <= 3e-3, orc.rel_norm(got, ref)
+    assert orc.max_over_rms(got, ref) <= 8e-3, orc.max_over_rms(got, ref)

@@ -118,6 +118,7 @@ class MixedPack:
     inter: int
     codebook: int
     expert_ids: list[torch.Tensor] = field(default_factory=list)    # int32 [E_c] per class: local id -> global id
+    covers_all: bool = True             # False: some experts belong to no class (another rank holds them)
 
     def __post_init__(self):
         if not self.expert_ids:
@@ -131,20 +132,36 @@ class MixedPack:
         return [moe_block_size(tokens, top_k, p.num_experts) for p in self.packs]
 
 
-def prepare_mixed(gate, up, down, codebook: int) -> MixedPack:
-    """Like `prepare`, for experts of mixed K (marlin_moe.py:164-181): experts are grouped by their bitrate."""
+def prepare_mixed(gate, up, down, codebook: int, experts=None) -> MixedPack:
+    """Like `prepare`, for experts of mixed K (marlin_moe.py:164-181): experts are grouped by their bitrate.  `experts`
+    (an iterable of global expert ids) restricts the pack to those experts: the slots of all others belong to no class,
+    which is how one rank of an expert-parallel layer holds its share (`expert_partition`)."""
     words = [w.shape[2] for w in gate[0]]
-    classes = sorted(set(words))
     e = len(words)
+    keep = sorted(set(range(e) if experts is None else experts))
+    if not keep or keep[0] < 0 or keep[-1] >= e:
+        raise ValueError(f"experts must be a non-empty subset of 0..{e - 1}")
+    classes = sorted({words[i] for i in keep})
     packs, maps = [], []
     for wd in classes:
-        ids = [i for i in range(e) if words[i] == wd]
+        ids = [i for i in keep if words[i] == wd]
         sub = lambda t: tuple([t[j][i] for i in ids] for j in range(3))
         packs.append(prepare(sub(gate), sub(up), sub(down), codebook))
         m = torch.full((e,), -1, dtype=torch.int32)
         m[ids] = torch.arange(len(ids), dtype=torch.int32)
         maps.append(m.to(packs[-1].w13.device))
-    return MixedPack(packs, maps, e, packs[0].hidden, packs[0].inter, codebook)
+    return MixedPack(packs, maps, e, packs[0].hidden, packs[0].inter, codebook, covers_all=len(keep) == e)
+
+
+def expert_partition(num_experts: int, rank: int, world: int) -> range:
+    """Experts of one rank under expert parallelism: contiguous shares, the first `num_experts % world` ranks take one
+    more.  Tokens are replicated, every rank computes the weighted contributions of its own experts and the outputs
+    [T, hidden] are summed by one all-reduce."""
+    if not 0 <= rank < world or num_experts < world:
+        raise ValueError(f"cannot split {num_experts} experts over rank {rank} of {world}")
+    q, r = divmod(num_experts, world)
+    lo = rank * q + min(rank, r)
+    return range(lo, lo + q + (1 if rank < r else 0))
 
 
 def align_capacity(slots: int, num_experts_class: int, block: int = 8) -> int:
@@ -260,7 +277,8 @@ def run_mixed(x, topk_weights, topk_ids, routings, pack: MixedPack, out: torch.T
     ids32 = topk_ids.reshape(-1).to(torch.int32).contiguous()
     wts = topk_weights.reshape(-1).to(torch.float32).contiguous()
     gu = torch.empty((slots, 2 * inter), dtype=torch.float16, device=dev)
-    yd = torch.empty((slots, hidden), dtype=torch.float16, device=dev)
+    # slots of experts that no class of this pack holds are never written: they must add nothing in the combine
+    yd = (torch.empty if pack.covers_all else torch.zeros)((slots, hidden), dtype=torch.float16, device=dev)
     for pk, (sorted_ids, expert_ids, num_post, block) in zip(pack.packs, routings):
         if block != 8:
             raise RuntimeError(f"the grouped GEMV works on 8-row moe blocks, got block = {block}")
@@ -284,6 +302,15 @@ def run_mixed(x, topk_weights, topk_ids, routings, pack: MixedPack, out: torch.T
 def forward_mixed(x, topk_weights, topk_ids, pack: MixedPack, out: torch.Tensor | None = None) -> torch.Tensor:
     """Whole mixed-K layer including the per-class routing alignment."""
     return run_mixed(x, topk_weights, topk_ids, align_decode(topk_ids, pack, x.shape[0], topk_ids.shape[1]), pack, out)
+
+
+def forward_expert_parallel(x, topk_weights, topk_ids, pack: MixedPack, reduce, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One rank of an expert-parallel layer: `pack` holds this rank's experts (`prepare_mixed(..., experts=
+    expert_partition(E, rank, world))`), tokens and routing are the same on every rank, `reduce` sums a tensor over the
+    ranks in place (`runtime.allreduce.PeerAllReduce` or `nccl_all_reduce`)."""
+    y = forward_mixed(x, topk_weights, topk_ids, pack, out)
+    reduce(y)
+    return y
 
 
 def run(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block: int, pack: ExpertPack,
