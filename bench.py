@@ -98,8 +98,8 @@ def cpu_sample(K: int, codebook: int, min_seconds: float = 8.0, max_reps: int = 
     """Oracle forward (decode + multiply fused, OpenMP) on the seven matrices of one 27B-shape layer, batch 1."""
     import numpy as np
     from oracle import exl3_oracle as orc
-    if threads:
-        orc.set_threads(threads)
+    # All usable host cores, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its workers).
+    orc.set_threads(threads or len(os.sched_getaffinity(0)))
     shapes = [(5120, 5120), (5120, 1024), (5120, 1024), (5120, 5120), (5120, 17408), (5120, 17408), (17408, 5120)]
     rng = np.random.default_rng(100)
     mats = []
