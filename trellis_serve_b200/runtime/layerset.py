@@ -99,6 +99,8 @@ class DecodeLayerSet:
         self.graph: torch.cuda.CUDAGraph | None = None
         # up to two rows the GEMV rotates its own input: one launch per group; otherwise rotation + GEMV
         self.launches_per_step = layers * 4 * (1 if rows <= 2 else 2)
+        if tp_size > 1 and allreduce is not None and not self.fused_exchange:
+            self.launches_per_step += layers * 2             # the stand-alone exchange kernel after o and down
 
     @property
     def packed_bytes(self) -> int:
