@@ -13,8 +13,8 @@ registered as `torch.ops.exl3_b200.linear`, with a fake (meta) implementation so
 
 Dispatch (there is a single backend, so the reference's ladder, ops.py:79-95, collapses to two paths):
 
-  rows <  DENSE_ROWS        fused decode kernel (weights streamed once per 16 rows)
-  rows >= DENSE_ROWS        many-row path: the fused tcgen05 kernel (`kernels.linear.run_tc`: weights decoded once per
+  few rows                  fused decode kernel (weights streamed once per 16 rows)
+  many rows                 many-row path: the fused tcgen05 kernel (`kernels.linear.run_tc`: weights decoded once per
                             512 rows into the tensor-core operand); when resident decoded weights are passed in `dense`,
                             `dense_group` instead (batched input rotation, library fp16 GEMM on the resident weight,
                             output rotation), which is the reference's many-row sequence
@@ -33,8 +33,27 @@ from ..kernels import linear as lin
 
 _lib = torch.library.Library("exl3_b200", "FRAGMENT")       # must stay alive at module scope
 
-# Rows from which decode-to-fp16 + GEMM beats streaming the packed weights once per 16 rows.
-DENSE_ROWS = int(os.environ.get("EXL3_B200_DENSE_ROWS", "33"))
+# Row count from which the many-row path is taken; 0 = decide per call with `prefers_decode` (the crossover depends on the
+# shape: 17 rows for a 5120 x 34816 group, ~100 for 17408 x 5120).
+DENSE_ROWS = int(os.environ.get("EXL3_B200_DENSE_ROWS", "0"))
+_SMS = 148
+
+
+def prefers_decode(rows: int, k: int, n_total: int) -> bool:
+    """Cost model fitted to measurements on B200 (microseconds).  The decode kernel streams the weights once per 16 rows:
+    ~14 + 0.38 per million weights for a full chunk, ~0.8 of that for a last chunk of up to 8 rows.  The tensor-core kernel
+    works through its tiles in waves over the SMs at ~1.1 per 64-deep reduction block (~1.6 for the 512-row tiles used above
+    256 rows), plus ~12 for the two rotation launches; below a wave's worth of tiles its time does not depend on the rows."""
+    mw = k * n_total / 1e6
+    chunk = 14.0 + 0.38 * mw
+    full, rem = divmod(rows, 16)
+    decode = full * chunk + (0.0 if rem == 0 else chunk * (0.8 if rem <= 8 else 1.0))
+    if rows <= 256:
+        tiles, per_block = -(-rows // 256) * max(n_total // 256, 1), 1.1
+    else:
+        tiles, per_block = -(-rows // 512) * (n_total // 128), 1.6
+    tensor = -(-tiles // _SMS) * (k / 64) * per_block + 12.0
+    return decode <= tensor
 # "tc": fused tcgen05 kernel; "library": decode to fp16 + library GEMM (the reference's sequence), for comparisons.
 PREFILL = os.environ.get("EXL3_B200_PREFILL", "tc")
 
@@ -73,7 +92,7 @@ def _linear(x: torch.Tensor, trellis: list[torch.Tensor], suh: list[torch.Tensor
     if h.shape[1] < k:                                   # stored input width is padded to 128
         h = torch.nn.functional.pad(h, (0, k - h.shape[1]))
     h = h.contiguous()
-    if h.shape[0] < DENSE_ROWS:
+    if (h.shape[0] < DENSE_ROWS) if DENSE_ROWS > 0 else prefers_decode(h.shape[0], k, n_total):
         y = lin.run(h, packed, suh_cat, svh_cat, ends, codebooks[0])
     elif dense or PREFILL == "library":
         y = torch.empty((h.shape[0], n_total), dtype=h.dtype, device=h.device)
