@@ -211,6 +211,9 @@ void exl3_set_gemv_mode(int mode);
 /* Measurement / test knob: output tiling of exl3_linear_tc.  -1 = library default, 0 = 512 x 128 tiles, 1 = 256 x 256 tiles
  * (used only where the column blocks pair up inside every shard), 2 = 384 x 128 tiles.  No counterpart in the reference. */
 void exl3_set_tc_tiling(int tiling);
+/* Measurement / test knob: upper bound of the parts the reduction of a tile is cut into when exl3_linear_tc has fewer
+ * tiles than SMs (0 = library default, 1 = never split).  No counterpart in the reference. */
+void exl3_set_tc_ksplit(int parts);
 
 #ifdef __cplusplus
 }

@@ -23,17 +23,20 @@ def _t(a):
 def _default_tiling():
     yield
     lin.set_tc_tiling(-1)
+    lin.set_tc_ksplit(0)
 
 
 @pytest.mark.parametrize("tiling", [0, 1, 2])       # 512 x 128; 256 x 256 (n = 384, 640, 128 have an odd block: narrow); 384 x 128
 @pytest.mark.parametrize("K,cb,k,n,rows", [(4, 1, 256, 256, 130), (3, 0, 512, 384, 512), (4, 1, 1024, 640, 700),
                                            (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025),
                                            (3, 0, 384, 768, 300), (6, 1, 256, 512, 257)])
-def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows, tiling):
+@pytest.mark.parametrize("ksplit", [0, 1, 3])     # reduction of a tile cut into parts when tiles are few: default, never, at most 3
+def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows, tiling, ksplit):
     tr, suh, svh = seeded_trellis(K * 7 + cb, k // 16, n // 16, K), seeded_signs(1, k), seeded_signs(2, n)
     x = np.random.default_rng(rows).standard_normal((rows, k)).astype(np.float16)
     packed = lin.prepare_matrix(_t(tr))
     lin.set_tc_tiling(tiling)
+    lin.set_tc_ksplit(ksplit)
     y = lin.run_tc(_t(x), packed, _t(suh).reshape(1, -1), _t(svh), [], cb)
     torch.cuda.synchronize()
     lin.device_error(torch.device(DEV))

@@ -55,6 +55,7 @@ SIGNATURES = {
     "exl3_device_error": (_i, [_vp, _sz, _vp]),
     "exl3_set_gemv_mode": (None, [_i]),
     "exl3_set_tc_tiling": (None, [_i]),
+    "exl3_set_tc_ksplit": (None, [_i]),
 }
 
 

@@ -299,7 +299,8 @@ static size_t tc_up(size_t v) { return (v + 255) & ~(size_t)255; }
 size_t exl3_gemm_tc_workspace_bytes(int rows, int k, int n_total, int n_shards)
 {
     if (rows < 0 || k < 0 || n_total < 0 || n_shards < 1) return 0;
-    return 256 + tc_up(gemm_tc_activation_bytes(rows, k, n_shards)) + tc_up((size_t)rows * n_total * sizeof(__half));
+    return 256 + tc_up(gemm_tc_activation_bytes(rows, k, n_shards)) + tc_up((size_t)rows * n_total * sizeof(__half)) +
+           tc_up(gemm_tc_part_bytes(rows, n_total));
 }
 
 exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat,
@@ -320,9 +321,14 @@ exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, i
     unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
     __half* xa = reinterpret_cast<__half*>(ws + 256);
     __half* rot = reinterpret_cast<__half*>(ws + 256 + tc_up(gemm_tc_activation_bytes(rows, k, n_shards)));
+    float* part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(rot) + tc_up((size_t)rows * n_total * sizeof(__half)));
+    int parts = 1;
     if (int rc = launch_gemm_tc(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), packed, K, codebook, a.shard_end_blocks,
-                                n_shards, rows, k, n_total, xa, rot, reinterpret_cast<int*>(ws), st))
+                                n_shards, rows, k, n_total, xa, rot, part, &parts, reinterpret_cast<int*>(ws), st))
         return rc;
+    if (parts > 1)
+        return launch_had_out_sum(part, parts, (long long)rows * n_total, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y,
+                                  y_dtype == EXL3_BF16, st);
     return launch_had_out(rot, 0, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y, n_total, y_dtype == EXL3_BF16, st);
 }
 
@@ -516,5 +522,8 @@ void exl3_set_gemv_mode(int mode) { gemv_set_mode_override(mode); }
 
 /* Test / measurement knob: output tiling of the many-row tensor-core GEMM (-1 choose, 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128). */
 void exl3_set_tc_tiling(int tiling) { gemm_tc_set_tiling(tiling); }
+
+/* Test / measurement knob: at most `parts` parts of the reduction per tile in exl3_linear_tc (0 choose, 1 no split). */
+void exl3_set_tc_ksplit(int parts) { gemm_tc_set_ksplit(parts); }
 
 }  // extern "C"

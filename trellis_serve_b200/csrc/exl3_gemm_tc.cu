@@ -62,6 +62,9 @@ struct GemmTcLaunch {
     int n_shards;
     long long xa_shard_stride;   // halves between shards
     uint32_t mul, add;
+    int ksplit;                  // > 1: the reduction of every tile is cut into this many parts, each on its own CTA
+    float* part;                 //      which stores its fp32 accumulators into slab [part index][rows][n_total]
+    long long part_slab;         //      floats per slab
     Pow2 pw;
 };
 
@@ -110,7 +113,9 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int K, int FAM, int MT_, bool WIDE>
+// SPLIT: the reduction of a tile may be cut into p.ksplit parts (work items); without it the part count is the constant 1
+// and the index arithmetic of the unsplit kernel folds away.
+template <int K, int FAM, int MT_, bool WIDE, bool SPLIT>
 __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
 {
     using TT = TcTile<MT_, WIDE>;
@@ -147,7 +152,10 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
     const int KB = p.KG * 2;                           // reduction blocks of 64
     const int MT = (p.rows + TT::ROWS - 1) / TT::ROWS; // row tiles
     const int NT = p.NB / TT::NBLK;                    // column tiles
-    const long long n_tiles = (long long)MT * NT;
+    const int KS = SPLIT ? p.ksplit : 1;
+    const long long n_tiles = (long long)MT * NT * KS;       // work items: (tile, part of its reduction), part fastest
+    auto kb_begin = [&](long long t) { return (int)((long long)KB * (t % KS) / KS); };
+    auto kb_end = [&](long long t) { return (int)((long long)KB * (t % KS + 1) / KS); };
     bool failed = false;
     auto fail = [&]() {
         if (!failed) {
@@ -163,29 +171,33 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
         uint32_t it = 0, acc_round = 0;
         // The warp's words of the next reduction block are requested one block ahead, so their L2 latency hides
         // behind the decode of the current block.
-        auto words_ptr = [&](long long tile, int kb) {
-            const int nb_ = (int)(tile / MT) * TT::NBLK + nbh;
+        // column block of a work item (64-bit divisions: once per work item, not per reduction block)
+        auto block_of = [&](long long tile) { return (int)((tile / KS) / MT) * TT::NBLK + nbh; };
+        auto words_ptr = [&](int nb_, int kb) {
             return p.packed + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
         };
         uint32_t Lnext[K];
         if ((long long)blockIdx.x < n_tiles) {
-            const uint32_t* src = words_ptr(blockIdx.x, 0);
+            const uint32_t* src = words_ptr(block_of(blockIdx.x), kb_begin(blockIdx.x));
 #pragma unroll
             for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
         }
         for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-            const int ms = (int)(t % MT), ct = (int)(t / MT);
-            for (int kb = 0; kb < KB; kb++, it++) {
+            const int ms = (int)((t / KS) % MT), ct = (int)((t / KS) / MT), sp = (int)(t % KS);
+            const int kb0 = kb_begin(t), kb1 = kb_end(t);
+            const long long t_next = t + gridDim.x;
+            const int nb_cur = block_of(t), nb_next = t_next < n_tiles ? block_of(t_next) : 0;
+            const int kb_next = t_next < n_tiles ? kb_begin(t_next) : 0;
+            for (int kb = kb0; kb < kb1; kb++, it++) {
                 const int s = it % STAGES;
                 const uint32_t round = it / STAGES;
                 uint32_t L[K];
 #pragma unroll
                 for (int i = 0; i < K; i++) L[i] = Lnext[i];
                 {
-                    const bool last = kb + 1 == KB;
-                    const long long tn = last ? t + gridDim.x : t;
-                    if (tn < n_tiles) {
-                        const uint32_t* src = words_ptr(tn, last ? 0 : kb + 1);
+                    const bool last = kb + 1 == kb1;
+                    if (!last || t_next < n_tiles) {
+                        const uint32_t* src = last ? words_ptr(nb_next, kb_next) : words_ptr(nb_cur, kb + 1);
 #pragma unroll
                         for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
                     }
@@ -234,7 +246,13 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                     const int col = cgroup * 64 + cc * 32;
                     uint32_t r[32];
                     tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * TT::NCOLS + col), r);
-                    if (row < p.rows) {
+                    if (row < p.rows && KS > 1) {
+                        // part of a split reduction: fp32 accumulators into this part's slab; the output rotation adds the slabs
+                        float* dst = p.part + (size_t)sp * p.part_slab + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
+#pragma unroll
+                        for (int v = 0; v < 32; v += 4)
+                            *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
+                    } else if (row < p.rows) {
                         __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
 #pragma unroll
                         for (int v = 0; v < 32; v += 8) {
@@ -262,7 +280,8 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
         if (lane == 0) {
             uint32_t it = 0;
             for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-                const int ms = (int)(t % MT), nb = (int)(t / MT) * TT::NBLK;
+                const int ms = (int)((t / KS) % MT), nb = (int)((t / KS) / MT) * TT::NBLK;
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
                 int shard = 0;
                 while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
                 // The A layout in global memory is in super tiles of 512 rows = four 128-row tiles of 16 KB per reduction
@@ -271,7 +290,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                 const int t128 = ms * TT::M_TILES;
                 int present = p.MS * 4 - t128;
                 if (present > TT::M_TILES) present = TT::M_TILES;
-                for (int kb = 0; kb < KB; kb++, it++) {
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
@@ -291,7 +310,8 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
             for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
                 if (acc_round > 0 && !failed && !ptx::mbar_wait(acc_empty, (acc_round - 1) & 1)) fail();
                 tc_fence_after();
-                for (int kb = 0; kb < KB; kb++, it++) {
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (!failed && !ptx::mbar_wait(&a_full[s], round & 1)) fail();
@@ -304,7 +324,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
 #pragma unroll
                         for (int ks = 0; ks < TC_KB / 16; ks++)
                             tc_mma(tmem_base + (uint32_t)(mt * TT::NCOLS), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096, 2048),
-                                   tc_smem_desc(b_addr + ks * 2 * TT::B_LBO, TT::B_LBO), TT::IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
+                                   tc_smem_desc(b_addr + ks * 2 * TT::B_LBO, TT::B_LBO), TT::IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
                     tc_commit(&empty[s]);               // stage reusable once these MMAs have read it
                 }
                 tc_commit(acc_full);                    // accumulators complete
@@ -353,20 +373,27 @@ __global__ void had_in_tc_kernel(const void* __restrict__ x, int x_bf16, const _
     *reinterpret_cast<uint2*>(xa + s * shard_stride + off) = *reinterpret_cast<uint2*>(h);
 }
 
-template <int K, int FAM, int MT, bool WIDE>
-static int launch_tc_variant(const GemmTcLaunch& l, int sm_count, cudaStream_t st)
+template <int K, int FAM, int MT, bool WIDE, bool SPLIT>
+static int launch_tc_kernel(const GemmTcLaunch& l, int sm_count, cudaStream_t st)
 {
     using TT = TcTile<MT, WIDE>;
     static bool attr_set = false;
     if (!attr_set) {
-        if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, MT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TT::SMEM_BYTES)))
+        if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, MT, WIDE, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      (int)TT::SMEM_BYTES)))
             return rc;
         attr_set = true;
     }
-    const long long tiles = (long long)((l.rows + TT::ROWS - 1) / TT::ROWS) * (l.NB / TT::NBLK);
-    const int grid = tiles < sm_count ? (int)tiles : sm_count;
-    gemm_tc_kernel<K, FAM, MT, WIDE><<<grid, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
+    const long long work = (long long)((l.rows + TT::ROWS - 1) / TT::ROWS) * (l.NB / TT::NBLK) * l.ksplit;
+    const int grid = work < sm_count ? (int)work : sm_count;
+    gemm_tc_kernel<K, FAM, MT, WIDE, SPLIT><<<grid, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
     return cuda_status(cudaGetLastError());
+}
+
+template <int K, int FAM, int MT, bool WIDE>
+static int launch_tc_variant(const GemmTcLaunch& l, int sm_count, cudaStream_t st)
+{
+    return l.ksplit > 1 ? launch_tc_kernel<K, FAM, MT, WIDE, true>(l, sm_count, st) : launch_tc_kernel<K, FAM, MT, WIDE, false>(l, sm_count, st);
 }
 
 // tiling: 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128
@@ -384,6 +411,9 @@ static int launch_tc_k(const GemmTcLaunch& l, int fam, int tiling, int sm_count,
     return fam == FAM_HASH ? launch_tc_fam<K, FAM_HASH>(l, tiling, sm_count, st) : launch_tc_fam<K, FAM_MUL1>(l, tiling, sm_count, st);
 }
 
+constexpr int TC_MAX_KSPLIT = 8;
+static int g_tc_ksplit = 0;           // 0 = choose; n >= 1 = at most n parts (1 switches the split off)
+void gemm_tc_set_ksplit(int n) { g_tc_ksplit = n; }
 static int g_tc_tiling = -1;          // -1 = choose; 0 = 512 x 128; 1 = 256 x 256 where the shape allows; 2 = 384 x 128
 void gemm_tc_set_tiling(int t) { g_tc_tiling = t; }
 
@@ -394,8 +424,16 @@ size_t gemm_tc_activation_bytes(int rows, int k, int shards)
 }
 
 // xa: gemm_tc_activation_bytes() of scratch.  out: [rows][n_total] fp16 in the rotated basis.
+size_t gemm_tc_part_bytes(int rows, int n_total)
+{
+    // Slabs of a split reduction: parts x rows x n_total floats with parts * tiles <= SMs, so never more than this.
+    const size_t want = (size_t)TC_MAX_KSPLIT * rows * n_total * sizeof(float);
+    const size_t cap = (size_t)160 * 512 * 128 * sizeof(float);
+    return want < cap ? want : cap;
+}
+
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
-                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, int* err, cudaStream_t st)
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, int* ksplit_out, int* err, cudaStream_t st)
 {
     const DeviceInfo* d = current_device_info();
     if (!d) return EXL3_ERR_NOT_INITIALISED;
@@ -438,6 +476,21 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
         tiling = rows <= 256 ? 1 : (cost(3) < cost(4) ? 2 : 0);
     }
     if (tiling == 1 && !can_wide) tiling = 0;
+    // Few tiles (narrow outputs at small row counts) leave most SMs idle: the reduction of every tile is then cut into
+    // parts that run on CTAs of their own and store fp32 slabs, which the output rotation adds in part order.
+    {
+        const int tile_rows = tiling == 1 ? 256 : tiling == 2 ? 384 : 512;
+        const long long tiles = (long long)((rows + tile_rows - 1) / tile_rows) * (l.NB / (tiling == 1 ? 2 : 1));
+        long long parts = tiles > 0 ? d->sm_count / tiles : 1;
+        if (parts > TC_MAX_KSPLIT) parts = TC_MAX_KSPLIT;
+        if (parts > l.KG * 2) parts = l.KG * 2;
+        while (parts > 1 && (size_t)parts * rows * n_total * sizeof(float) > gemm_tc_part_bytes(rows, n_total)) parts--;
+        if (g_tc_ksplit >= 1 && parts > g_tc_ksplit) parts = g_tc_ksplit;
+        l.ksplit = part && parts > 1 ? (int)parts : 1;
+        l.part = part;
+        l.part_slab = (long long)rows * n_total;
+        if (ksplit_out) *ksplit_out = l.ksplit;
+    }
     const int fam = codebook_family(codebook);
     switch (K) {
         case 2: return launch_tc_k<2>(l, fam, tiling, d->sm_count, st);

@@ -102,8 +102,13 @@ int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, in
 // exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
 size_t gemm_tc_activation_bytes(int rows, int k, int shards);
 void gemm_tc_set_tiling(int t);             // -1 = choose; 0 = 512 x 128 tiles; 1 = 256 x 256 tiles where the shape allows; 2 = 384 x 128 tiles
+size_t gemm_tc_part_bytes(int rows, int n_total);
+void gemm_tc_set_ksplit(int n);             // 0 = choose; n >= 1 = at most n parts of the reduction per tile
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
-                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, int* err, cudaStream_t st);
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, int* ksplit_out, int* err,
+                   cudaStream_t st);
+int launch_had_out_sum(const float* part, int parts, long long slab, const __half* svh, int rows, int n, void* out, int out_bf16,
+                       cudaStream_t st);
 
 // exl3_allreduce.cu -------------------------------------------------------------------------------------
 size_t allreduce_region_bytes(size_t max_elems);

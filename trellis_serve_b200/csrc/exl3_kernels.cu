@@ -283,6 +283,38 @@ __global__ void had_out_kernel(const void* __restrict__ y, const __half* __restr
     store_out4(out, (long long)row * out_stride + nb * 128 + 4 * lane, v, out_bf16 != 0);
 }
 
+// out[row, :] = Had128(fp16(sum over parts of part[s][row, :])) * svh: the output rotation of the many-row path when the
+// reduction was split over CTAs; the slabs are added in part order in fp32 and rounded to fp16 once, as the unsplit
+// kernel rounds its accumulators.
+__global__ void had_out_sum_kernel(const float* __restrict__ part, int parts, long long slab, const __half* __restrict__ svh, int rows,
+                                   int n, void* __restrict__ out, int out_bf16)
+{
+    const int lane = threadIdx.x & 31;
+    const int nbs = n >> 7;
+    long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)rows * nbs) return;
+    const int nb = (int)(item % nbs);
+    const int row = (int)(item / nbs);
+    const long long base = (long long)row * n + nb * 128 + 4 * lane;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < parts; s++) {
+        const float4 v = *reinterpret_cast<const float4*>(part + s * slab + base);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    float v[4] = {__half2float(__float2half_rn(acc.x)), __half2float(__float2half_rn(acc.y)), __half2float(__float2half_rn(acc.z)),
+                  __half2float(__float2half_rn(acc.w))};
+    fwht128(v[0], v[1], v[2], v[3], lane);
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        float sv = svh ? __half2float(svh[nb * 128 + 4 * lane + e]) : 1.0f;
+        v[e] = v[e] * HAD_SCALE * sv;
+    }
+    store_out4(out, base, v, out_bf16 != 0);
+}
+
 // ------------------------------------------------------------------------------------------------ launchers
 
 static inline unsigned blocks_for(long long items, int per_block) { return (unsigned)((items + per_block - 1) / per_block); }
@@ -369,6 +401,15 @@ int launch_had_out(const void* y, int y_f32, const __half* svh, int rows, int n,
     if (items == 0) return EXL3_OK;
     if (y_f32) had_out_kernel<true><<<blocks_for(items, 8), 256, 0, st>>>(y, svh, rows, n, out, out_stride, out_bf16);
     else had_out_kernel<false><<<blocks_for(items, 8), 256, 0, st>>>(y, svh, rows, n, out, out_stride, out_bf16);
+    return cuda_status(cudaGetLastError());
+}
+
+int launch_had_out_sum(const float* part, int parts, long long slab, const __half* svh, int rows, int n, void* out, int out_bf16,
+                       cudaStream_t st)
+{
+    long long items = (long long)rows * (n / 128);
+    if (items == 0) return EXL3_OK;
+    had_out_sum_kernel<<<blocks_for(items, 8), 256, 0, st>>>(part, parts, slab, svh, rows, n, out, out_bf16);
     return cuda_status(cudaGetLastError());
 }
 

@@ -311,6 +311,11 @@ def set_tc_tiling(tiling: int) -> None:
     _lib.load().exl3_set_tc_tiling(int(tiling))
 
 
+def set_tc_ksplit(parts: int) -> None:
+    """Knob: upper bound of the parts a tile's reduction is cut into in `run_tc` (0 default, 1 never split)."""
+    _lib.load().exl3_set_tc_ksplit(int(parts))
+
+
 def set_gemv_mode(mode: int) -> None:
     """Knob: -1 default, 0 split (two fp16 summands per weight, added in fp32), 1 paired (weights rounded to fp16)."""
     _lib.load().exl3_set_gemv_mode(int(mode))

@@ -34,7 +34,7 @@ from ..kernels import linear as lin
 _lib = torch.library.Library("exl3_b200", "FRAGMENT")       # must stay alive at module scope
 
 # Row count from which the many-row path is taken; 0 = decide per call with `prefers_decode` (the crossover depends on the
-# shape: 17 rows for a 5120 x 34816 group, ~100 for 17408 x 5120).
+# shape and, since narrow outputs split their reduction over the idle SMs, lies at 17 rows for the 27B-shape groups).
 DENSE_ROWS = int(os.environ.get("EXL3_B200_DENSE_ROWS", "0"))
 _SMS = 148
 
@@ -43,7 +43,8 @@ def prefers_decode(rows: int, k: int, n_total: int) -> bool:
     """Cost model fitted to measurements on B200 (microseconds).  The decode kernel streams the weights once per 16 rows:
     ~14 + 0.38 per million weights for a full chunk, ~0.8 of that for a last chunk of up to 8 rows.  The tensor-core kernel
     works through its tiles in waves over the SMs at ~1.1 per 64-deep reduction block (~1.6 for the 512-row tiles used above
-    256 rows), plus ~12 for the two rotation launches; below a wave's worth of tiles its time does not depend on the rows."""
+    256 rows); when the tiles are fewer than the SMs the reduction of each is cut into up to 8 parts on CTAs of their own;
+    ~12 more for the two rotation launches, ~8 for adding the parts."""
     mw = k * n_total / 1e6
     chunk = 14.0 + 0.38 * mw
     full, rem = divmod(rows, 16)
@@ -52,7 +53,8 @@ def prefers_decode(rows: int, k: int, n_total: int) -> bool:
         tiles, per_block = -(-rows // 256) * max(n_total // 256, 1), 1.1
     else:
         tiles, per_block = -(-rows // 512) * (n_total // 128), 1.6
-    tensor = -(-tiles // _SMS) * (k / 64) * per_block + 12.0
+    parts = max(1, min(8, _SMS // max(tiles, 1), k // 64))
+    tensor = -(-tiles // _SMS) * (k / 64) / parts * per_block + 12.0 + (8.0 if parts > 1 else 0.0) + 0.08 * min(rows, 256)
     return decode <= tensor
 # "tc": fused tcgen05 kernel; "library": decode to fp16 + library GEMM (the reference's sequence), for comparisons.
 PREFILL = os.environ.get("EXL3_B200_PREFILL", "tc")
