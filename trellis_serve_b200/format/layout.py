@@ -1,28 +1,32 @@
-"""Logical matrices of a fused run-time module (q|k|v, gate|up ...): an ordered group of independent EXL3 matrices
-that share an input and write adjacent output spans, each with its own suh, K and codebook.  Same description as
-core/src/trellis_core/format/layout.py of 0xSero/trellis-serve; how a group is launched is the backend's business.
+"""Fused run-time modules seen from the format side.
+
+An engine merges some projections into one module (q|k|v, gate|up): several stored EXL3 matrices read the same input and
+write neighbouring column spans of one output.  The matrices stay independent (own sign vectors, possibly own bitrate and
+codebook), so the description is just the ordered list with each matrix's true output width; how the group is launched
+is up to the backend.  Names follow core/src/trellis_core/format/layout.py of 0xSero/trellis-serve.
 """
 from __future__ import annotations
 
 import enum
+import itertools
 from dataclasses import dataclass
 from typing import Hashable, Sequence
 
 from .spec import MatrixSpec
 
 
+class FusionKind(enum.Enum):
+    SINGLE = "single"              # one matrix
+    UNIFORM = "uniform"            # same shape, bitrate and codebook throughout, nothing padded
+    SHARD_MAP = "shard_map"        # anything else that shares the input
+    SEQUENTIAL = "sequential"      # fallback a backend may choose: one launch per matrix
+
+
 @dataclass(frozen=True)
 class LogicalMatrix:
-    shard_id: Hashable
+    shard_id: Hashable             # the engine's name for this part of the module ("q", 0, None ...)
     spec: MatrixSpec
-    out_width: int
-
-
-class FusionKind(enum.Enum):
-    SINGLE = "single"
-    UNIFORM = "uniform"
-    SHARD_MAP = "shard_map"
-    SEQUENTIAL = "sequential"
+    out_width: int                 # true output columns (the stored width is padded to 128)
 
 
 @dataclass(frozen=True)
@@ -30,14 +34,14 @@ class FusedLayout:
     matrices: tuple[LogicalMatrix, ...]
 
     def __post_init__(self):
-        if not self.matrices:
+        if len(self.matrices) == 0:
             raise ValueError("a fused layout needs at least one matrix")
-        ks = sorted({m.spec.k for m in self.matrices})
-        if len(ks) != 1:
-            raise ValueError(f"fused matrices must share their input width, got {ks}")
-        for m in self.matrices:
-            if not 0 < m.out_width <= m.spec.n:
-                raise ValueError(f"{m.spec.key}: out_width {m.out_width} does not fit stored width {m.spec.n}")
+        widths_in = {m.spec.k for m in self.matrices}
+        if len(widths_in) > 1:
+            raise ValueError(f"fused matrices must share their input width, got {sorted(widths_in)}")
+        bad = next((m for m in self.matrices if m.out_width < 1 or m.out_width > m.spec.n), None)
+        if bad is not None:
+            raise ValueError(f"{bad.spec.key}: out_width {bad.out_width} does not fit stored width {bad.spec.n}")
 
     @property
     def in_width(self) -> int:
@@ -48,22 +52,23 @@ class FusedLayout:
         return sum(m.out_width for m in self.matrices)
 
     def spans(self) -> list[tuple[int, int]]:
-        spans, at = [], 0
-        for m in self.matrices:
-            spans.append((at, m.out_width))
-            at += m.out_width
-        return spans
+        """(first column, width) of every matrix in the module's output."""
+        widths = [m.out_width for m in self.matrices]
+        starts = itertools.accumulate([0] + widths[:-1])
+        return list(zip(starts, widths))
 
     @property
     def best_fusion(self) -> FusionKind:
-        if len(self.matrices) == 1:
+        first, rest = self.matrices[0], self.matrices[1:]
+        if not rest:
             return FusionKind.SINGLE
-        head = self.matrices[0].spec
-        uniform = all(m.spec.same_kernel_class(head) and m.out_width == m.spec.n for m in self.matrices)
-        return FusionKind.UNIFORM if uniform else FusionKind.SHARD_MAP
+        alike = all(m.spec.same_kernel_class(first.spec) for m in rest)
+        unpadded = all(m.out_width == m.spec.n for m in self.matrices)
+        return FusionKind.UNIFORM if alike and unpadded else FusionKind.SHARD_MAP
 
 
 def make_layout(shard_ids: Sequence[Hashable], specs: Sequence[MatrixSpec], out_widths: Sequence[int]) -> FusedLayout:
-    if not len(shard_ids) == len(specs) == len(out_widths):
+    if len({len(shard_ids), len(specs), len(out_widths)}) != 1:
         raise ValueError("shard_ids, specs and out_widths must have the same length")
-    return FusedLayout(tuple(LogicalMatrix(*t) for t in zip(shard_ids, specs, out_widths)))
+    parts = (LogicalMatrix(sid, spec, width) for sid, spec, width in zip(shard_ids, specs, out_widths))
+    return FusedLayout(tuple(parts))

@@ -60,97 +60,111 @@ class Manifest:
         }
 
 
-def _parents(key: str):
-    while "." in key:
-        key = key.rsplit(".", 1)[0]
-        yield key
+def _ancestors(key: str):
+    """'a.b.c' -> 'a.b', 'a'."""
+    parts = key.split(".")
+    for end in range(len(parts) - 1, 0, -1):
+        yield ".".join(parts[:end])
+
+
+def _live_tensors(headers: list, weight_map: dict, man: Manifest) -> dict:
+    """name -> TensorInfo over all model shards.  A name stored in two shards is an error unless the index names the shard
+    that counts; n-gram side tables are set aside into `man.ngram_tables`."""
+    live: dict[str, TensorInfo] = {}
+    duplicated = []
+    for header in headers:
+        if header.metadata.get("format") == NGRAM_FORMAT:
+            man.ngram_tables.append(NgramTable(header.file, header.metadata, header.tensors))
+            continue
+        for name, info in header.tensors.items():
+            seen = live.get(name)
+            if seen is None:
+                live[name] = info
+                continue
+            owner = weight_map.get(name)
+            if owner != seen.file and owner != header.file:
+                raise FormatError(f"tensor {name} appears in both {seen.file} and {header.file} "
+                                  f"and the index does not say which one is live")
+            duplicated.append(name)
+            if owner == header.file:
+                live[name] = info
+    if duplicated:
+        man.warnings.append(f"{len(duplicated)} tensors are stored in more than one shard (index decides), e.g. {duplicated[0]}")
+    return live
 
 
 def build_manifest(headers: list, quant_config: dict | None = None, weight_map: dict | None = None) -> Manifest:
-    """`weight_map` (model.safetensors.index.json) decides which copy is live when a tensor is stored in two shards."""
+    """Sorts the tensors of all shards into EXL3 linears (every key that has a `.trellis`) and the rest.  `weight_map`
+    (the `weight_map` of model.safetensors.index.json) decides between copies of a tensor stored twice."""
     man = Manifest(quant_config=dict(quant_config or {}))
-    weight_map = weight_map or {}
-    live: dict[str, TensorInfo] = {}
-    twice = []
-    for h in headers:
-        if h.metadata.get("format") == NGRAM_FORMAT:
-            man.ngram_tables.append(NgramTable(h.file, h.metadata, h.tensors))
-            continue
-        for name, info in h.tensors.items():
-            if name in live:
-                owner = weight_map.get(name)
-                if owner not in (live[name].file, h.file):
-                    raise FormatError(f"tensor {name} appears in both {live[name].file} and {h.file} "
-                                      f"and the index does not say which one is live")
-                twice.append(name)
-                if owner != h.file:
-                    continue
-            live[name] = info
-    if twice:
-        man.warnings.append(f"{len(twice)} tensors are stored in more than one shard (index decides), e.g. {twice[0]}")
+    live = _live_tensors(headers, weight_map or {}, man)
 
-    suffix = "." + REQUIRED_TRELLIS
-    keys = {name[: -len(suffix)] for name in live if name.endswith(suffix)}
-    for key in keys:
-        outer = next((k for k in _parents(key) if k in keys), None)
-        if outer is not None:
-            raise FormatError(f"{key}.trellis: unexpected tensor nested under EXL3 linear {outer}")
-    groups: dict[str, dict[str, TensorInfo]] = {}
+    tail = "." + REQUIRED_TRELLIS
+    linear_keys = {name[:-len(tail)] for name in live if name.endswith(tail)}
+
+    def enclosing_linear(key: str):
+        return next((a for a in _ancestors(key) if a in linear_keys), None)
+
+    by_key: dict[str, dict[str, TensorInfo]] = {key: {} for key in linear_keys}
     for name, info in live.items():
-        key, _, tail = name.rpartition(".")
-        if key in keys:
-            groups.setdefault(key, {})[tail] = info
-            continue
-        outer = next((k for k in _parents(key) if k in keys), None)
-        if outer is not None:
-            raise FormatError(f"{name}: unexpected tensor nested under EXL3 linear {outer}")
-        man.unquantized[name] = info
-    for key in sorted(groups):
-        man.matrices[key] = build_matrix_spec(key, groups[key])
+        owner, _, suffix = name.rpartition(".")
+        outer = enclosing_linear(owner)
+        if outer is not None:                     # something below a linear that is not one of its own tensors
+            what = f"{name}: unexpected tensor" if owner not in linear_keys else f"{owner}.trellis: unexpected tensor"
+            raise FormatError(f"{what} nested under EXL3 linear {outer}")
+        if owner in linear_keys:
+            by_key[owner][suffix] = info
+        else:
+            man.unquantized[name] = info
+    for key in sorted(by_key):
+        man.matrices[key] = build_matrix_spec(key, by_key[key])
 
     declared = man.quant_config.get("codebook")
-    if declared and man.matrices:
-        used = {m.codebook.value for m in man.matrices.values()}
-        if used != {declared}:
-            man.warnings.append(f"quantization_config.codebook={declared!r} but tensors use {sorted(used)}")
-    scale_names = INPUT_SCALE + OUTPUT_SCALE
-    stray = [n for n in man.unquantized if n.rpartition(".")[2] in scale_names and n.rpartition(".")[0] not in man.matrices]
-    if stray:
-        man.warnings.append(f"{len(stray)} scale tensors without a trellis, e.g. {stray[0]}")
+    stored = {spec.codebook.value for spec in man.matrices.values()}
+    if declared and stored and stored != {declared}:
+        man.warnings.append(f"quantization_config.codebook={declared!r} but tensors use {sorted(stored)}")
+    orphans = [name for name in man.unquantized if name.rpartition(".")[2] in INPUT_SCALE + OUTPUT_SCALE]
+    if orphans:
+        man.warnings.append(f"{len(orphans)} scale tensors without a trellis, e.g. {orphans[0]}")
     return man
 
 
 def _quant_config(model_dir: str) -> dict:
+    """quantization_config of config.json (also looked for under text_config); {} when there is none."""
     path = os.path.join(model_dir, "config.json")
     if not os.path.exists(path):
         return {}
     with open(path) as f:
-        cfg = json.load(f)
-    qc = cfg.get("quantization_config") or (cfg.get("text_config") or {}).get("quantization_config") or {}
-    if qc and qc.get("quant_method") != "exl3":
-        raise FormatError(f"{model_dir}: quant_method is {qc.get('quant_method')!r}, not 'exl3'")
-    return qc
+        config = json.load(f)
+    found = config.get("quantization_config") or (config.get("text_config") or {}).get("quantization_config") or {}
+    method = found.get("quant_method") if found else None
+    if found and method != "exl3":
+        raise FormatError(f"{model_dir}: quant_method is {method!r}, not 'exl3'")
+    return found
 
 
 def load_manifest(model_dir) -> Manifest:
-    """Manifest of a local checkpoint directory; reads headers only."""
+    """Manifest of a local checkpoint directory, from the headers of its *.safetensors files only."""
     model_dir = os.fspath(model_dir)
-    files = sorted(glob.glob(os.path.join(model_dir, "*.safetensors")))
-    if not files:
+    shard_paths = sorted(glob.glob(os.path.join(model_dir, "*.safetensors")))
+    if not shard_paths:
         raise FormatError(f"{model_dir}: no .safetensors files")
-    headers = [read_header(f) for f in files]
+    headers = [read_header(path) for path in shard_paths]
+    index_path = os.path.join(model_dir, "model.safetensors.index.json")
     weight_map = {}
-    index = os.path.join(model_dir, "model.safetensors.index.json")
-    if os.path.exists(index):
-        with open(index) as f:
+    if os.path.exists(index_path):
+        with open(index_path) as f:
             weight_map = json.load(f).get("weight_map", {})
     man = build_manifest(headers, _quant_config(model_dir), weight_map)
     if weight_map:
-        have = {n for h in headers if h.metadata.get("format") != NGRAM_FORMAT for n in h.tensors}
-        missing = sorted(set(weight_map) - have)
-        if missing:
-            raise FormatError(f"{len(missing)} tensors listed in the index are in no shard, e.g. {missing[0]}")
-        extra = sorted(have - set(weight_map))
-        if extra:
-            man.warnings.append(f"{len(extra)} tensors are not in model.safetensors.index.json, e.g. {extra[0]}")
+        stored = set()
+        for header in headers:
+            if header.metadata.get("format") != NGRAM_FORMAT:
+                stored.update(header.tensors)
+        absent = sorted(set(weight_map) - stored)
+        if absent:
+            raise FormatError(f"{len(absent)} tensors listed in the index are in no shard, e.g. {absent[0]}")
+        unlisted = sorted(stored - set(weight_map))
+        if unlisted:
+            man.warnings.append(f"{len(unlisted)} tensors are not in model.safetensors.index.json, e.g. {unlisted[0]}")
     return man
