@@ -87,6 +87,10 @@ exl3_status exl3_had_out(const void *y, int y_dtype, const uint16_t *svh, int ro
  * multiples of 128.  x_dtype: EXL3_F16 or EXL3_BF16; y_dtype: EXL3_F16, EXL3_BF16 (the fp16 result converted) or
  * EXL3_F32 (the fp32 accumulators unrounded, for accuracy measurements).  y must be 16-byte aligned.
  * Replaces exl3_linear_marlin_out / exl3_linear_marlin_multi_out (cuda/csrc/exl3_marlin.cu:489-527).
+ * packed, suh_cat and svh_cat are treated as constants: the kernel starts fetching them while the kernel ahead of it in the
+ * stream is still running (programmatic dependent launch), so they must be complete (the work that wrote them finished, or
+ * separated from this call by an event or a stream synchronisation) before the call is enqueued.  x and the workspace are
+ * read only after the kernel ahead has finished, as usual.
  * The workspace must be zero-filled once after allocation; every call leaves it reusable, also by calls with other
  * shapes and by the MoE entry points: it starts with a 256-byte header and a fixed 512 KB of counters that every launch
  * leaves zero, and only scratch lies behind them (so n_total / 128, and for the MoE kernel moe blocks x column blocks,
@@ -118,6 +122,8 @@ exl3_status exl3_linear_tc(const void *x, int x_dtype, const uint32_t *packed, i
  *   - All calls on a device share the one array, which keeps what the previous call left there (the library keeps
  *     the parts that must be zero at zero).  Two calls that overlap on the GPU (different streams) race on it:
  *     keep calls to this entry point in one stream order per device.
+ *   - A bounded device-side wait that gives up records its code in the array; exl3_device_error(NULL, 0, stream) reads and
+ *     clears it for the current device (no allocation either).
  * Results are identical to exl3_linear.  No counterpart in the reference. */
 #define EXL3_STATIC_WORKSPACE_BYTES (8u << 20)
 exl3_status exl3_linear_static(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook,
@@ -165,7 +171,9 @@ exl3_status exl3_allreduce(void *data, int dtype, size_t n, void *const *peer_re
  *
  * exl3_moe_align       replaces moe_align_decode (cuda/csrc/exl3_marlin_moe.cu:542-594) and the engine's
  *                      moe_align_block_size: sorted_ids [cap] (padding = slots), expert_ids [cap/8] (-1 past the
- *                      end), num_post [1] = padded row count.  cap >= exl3_moe_sorted_capacity().
+ *                      end), num_post [1] = padded row count.  cap >= exl3_moe_sorted_capacity().  At most 4064
+ *                      experts per alignment (EXL3_ERR_BAD_SHAPE beyond).  The later steps index the expert tensors
+ *                      with these lists unchecked: pass only lists written by exl3_moe_align / exl3_moe_align_mapped.
  * exl3_moe_had_in      replaces moe_had_in (exl3_marlin_moe.cu:210-225): per position Had128(fp16(x[token]) * suh[e, s])
  *                      for `shards` input rotations (gate and up), written as MMA fragments.  suh is [E, shards, hidden].
  * exl3_moe_gemm        replaces moe_gemm (exl3_marlin_moe.cu:376-408): per moe block, rows @ W[e] -> Had128 * svh[e] ->
@@ -201,6 +209,7 @@ exl3_status exl3_moe_combine(const uint16_t *yd, const float *topk_weights, cons
                              int hidden, int num_experts, void *y, int y_dtype, void *stream);
 
 /* Reads and clears the device-side error word kept in a workspace (set when a bounded wait in a kernel gave up).
+ * workspace == NULL with workspace_bytes == 0 means the built-in scratch of exl3_linear_static on the current device.
  * Synchronises `stream`.  Returns EXL3_OK or EXL3_ERR_DEVICE_WAIT. */
 exl3_status exl3_device_error(void *workspace, size_t workspace_bytes, void *stream);
 

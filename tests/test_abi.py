@@ -63,7 +63,7 @@ def test_argument_errors_are_statuses_not_launches():
     ends = (ctypes.c_int * 1)(64)
     assert lib.exl3_linear(p, 0, p, 3, 0, p, p, ends, 2, 1, 128, 256, p, 0, p, 4096, nul) == 1    # shard end not 128-aligned
     assert lib.exl3_linear(p, 0, p, 3, 0, p, p, None, 1, 0, 128, 256, p, 0, p, 4096, nul) == 0    # rows == 0
-    assert lib.exl3_device_error(nul, 0, nul) == 5
+    assert lib.exl3_device_error(nul, 64, nul) == 5                    # (NULL, 0) names the built-in scratch instead and needs a device
     # the exchange entry points: geometry of the rank set and of the regions is checked before anything runs
     regions = (ctypes.c_void_p * 2)(p, p)
     assert lib.exl3_allreduce(p, 0, 8, regions, 2, 2, 64, p, nul) == 1                             # rank outside the world

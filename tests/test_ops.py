@@ -80,5 +80,9 @@ def test_pad_trim_leading_dims_and_dtypes():
     assert orc.rel_norm(y.reshape(6, 350).cpu().numpy(), want) <= 2e-3
     yb = ops.linear(torch.from_numpy(xp).to(DEV).to(torch.bfloat16), [], [], [], [], [], 0, w, ends, [cb, cb], ns)
     assert yb.dtype == torch.bfloat16 and yb.shape == (6, 384)
-    with pytest.raises(RuntimeError, match="exceed"):
-        ops.linear(torch.from_numpy(xp).to(DEV), [], [], [], [], [], 0, w, ends, [cb, cb], [300, 128])
+    # logical widths beyond the stored ones: the extra columns read as zeros (reference ops.py:101-102, :117-121)
+    yw = ops.linear(torch.from_numpy(xp).to(DEV), [], [], [], [], [], 0, w, ends, [cb, cb], [300, 128])
+    assert yw.shape == (6, 428)
+    assert torch.count_nonzero(yw[:, 256:300]) == 0
+    full = ops.linear(torch.from_numpy(xp).to(DEV), [], [], [], [], [], 0, w, ends, [cb, cb], ns)
+    assert torch.equal(yw[:, :256], full[:, :256]) and torch.equal(yw[:, 300:], full[:, 256:])

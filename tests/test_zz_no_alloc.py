@@ -56,10 +56,20 @@ def test_static_scratch_entry_point_matches_the_workspace_one(K, cb, rows, dtype
     want_a = lin.run(xa, packed, suh_cat, svh_cat, ends, cb)
     want_b = lin.run(xb, packed, suh_cat, svh_cat, ends, cb)
     got_a = _static_linear(xa, packed, suh_cat, svh_cat, ends, K, cb, k, n)       # first call: looks the array up
-    got_b = _static_linear(xb, packed, suh_cat, svh_cat, ends, K, cb, k, n)       # second call: reuses its contents
+    lib, dt = _lib.load(), (_lib.F16 if dtype == torch.float16 else _lib.BF16)
+    got_b = torch.empty_like(got_a)                                               # the caller's output, made before measuring
     torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(dev)[0]
+    with torch.cuda.device(dev):                                                  # second call: reuses the array's contents
+        rc = lib.exl3_linear_static(_p(xb), dt, _p(packed), K, cb, _p(suh_cat), _p(svh_cat), _lib.int_array(ends), len(ends) + 1,
+                                    rows, k, n, _p(got_b), dt, torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(dev)[0] == free_before                         # the call took no device memory, from anyone
     assert torch.equal(got_a.view(torch.int16), want_a.view(torch.int16))
     assert torch.equal(got_b.view(torch.int16), want_b.view(torch.int16))
+    with torch.cuda.device(dev):                                                  # no bounded wait gave up inside the static calls
+        assert lib.exl3_device_error(None, 0, torch.cuda.current_stream(dev).cuda_stream) == 0
 
 
 def test_static_scratch_refuses_what_does_not_fit():

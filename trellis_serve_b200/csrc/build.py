@@ -16,12 +16,12 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-OUT = os.path.join(PKG, "libexl3_b200.so")
-OBJ = os.path.join(HERE, "build")
+OUT = os.environ.get("EXL3_B200_BUILD_OUT") or os.path.join(PKG, "libexl3_b200.so")
+OBJ = os.environ.get("EXL3_B200_BUILD_OBJ") or os.path.join(HERE, "build")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", 
-         "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+         "--expt-relaxed-constexpr", "-Xptxas", "-v", *os.environ.get("EXL3_B200_NVCC_FLAGS", "").split()]
 
 PLAIN = ["exl3_api.cu", "exl3_kernels.cu", "exl3_gemv.cu", "exl3_moe.cu", "exl3_gemm_tc.cu", "exl3_allreduce.cu"]
 PER_K = [("exl3_gemv_inst.cu", "EXL3_GEMV_K", range(2, 9)), ("exl3_moe_inst.cu", "EXL3_MOE_K", range(2, 9))]

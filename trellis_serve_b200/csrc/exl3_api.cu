@@ -94,6 +94,7 @@ exl3_status exl3_init_device(int device)
             d.ready = true;
             rc = gemv_init_device();
             if (rc == EXL3_OK) rc = moe_init_device();
+            if (rc == EXL3_OK) rc = gemm_tc_init_device();
             if (rc != EXL3_OK) d.ready = false;
         }
     }
@@ -280,8 +281,17 @@ exl3_status exl3_gemm_rotated(const uint16_t* xh, const uint32_t* packed, int K,
                          EXL3_F16, workspace, workspace_bytes, (cudaStream_t)stream, true);
 }
 
+static void* static_workspace_of_current_device(int* status);
+
 exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* stream)
 {
+    if (workspace == nullptr && workspace_bytes == 0) {
+        // The built-in scratch of exl3_linear_static on the current device (address looked up and cached, no allocation).
+        int rc = EXL3_OK;
+        workspace = static_workspace_of_current_device(&rc);
+        if (rc) return rc;
+        workspace_bytes = EXL3_STATIC_WORKSPACE_BYTES;
+    }
     if (!aligned(workspace, 256) || workspace_bytes < 256) return EXL3_ERR_WORKSPACE;
     int code = 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -380,7 +390,7 @@ size_t exl3_moe_sorted_capacity(int slots, int num_experts)
 exl3_status exl3_moe_align(const int32_t* topk_ids, int slots, int num_experts, int32_t* sorted_ids, int cap, int32_t* expert_ids,
                            int32_t* num_post, void* stream)
 {
-    if (slots < 0 || num_experts < 1 || num_experts > 4096 || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
+    if (slots < 0 || num_experts < 1 || num_experts > MOE_MAX_EXPERTS || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
     if ((size_t)cap < exl3_moe_sorted_capacity(slots, num_experts)) return EXL3_ERR_BAD_SHAPE;
     if (!aligned(num_post, 4) || (slots > 0 && !aligned(topk_ids, 4)) || (cap > 0 && (!aligned(sorted_ids, 4) || !aligned(expert_ids, 4))))
         return EXL3_ERR_BAD_POINTER;
@@ -391,7 +401,7 @@ exl3_status exl3_moe_align(const int32_t* topk_ids, int slots, int num_experts, 
 exl3_status exl3_moe_align_mapped(const int32_t* topk_ids, int slots, int num_experts, const int32_t* expert_map, int num_local,
                                   int32_t* sorted_ids, int cap, int32_t* expert_ids, int32_t* num_post, void* stream)
 {
-    if (slots < 0 || num_experts < 1 || num_local < 1 || num_local > 4096 || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
+    if (slots < 0 || num_experts < 1 || num_local < 1 || num_local > MOE_MAX_EXPERTS || cap < 0 || (cap % MOE_BLOCK_ROWS)) return EXL3_ERR_BAD_SHAPE;
     if ((size_t)cap < exl3_moe_sorted_capacity(slots, num_local)) return EXL3_ERR_BAD_SHAPE;
     if (!expert_map || !aligned(expert_map, 4) || !aligned(num_post, 4) || (slots > 0 && !aligned(topk_ids, 4)) ||
         (cap > 0 && (!aligned(sorted_ids, 4) || !aligned(expert_ids, 4))))
@@ -493,6 +503,30 @@ exl3_status exl3_moe_combine(const uint16_t* yd, const float* topk_weights, cons
 static __device__ __align__(256) unsigned char g_static_workspace[EXL3_STATIC_WORKSPACE_BYTES];
 static void* g_static_workspace_ptr[64];
 
+// In host code the array's name is only a handle, not a device address: the address has to be asked for, once per
+// device, with that device current.
+static void* static_workspace_of_current_device(int* status)
+{
+    int dev = -1;
+    *status = cuda_status(cudaGetDevice(&dev));
+    if (*status) return nullptr;
+    if (dev < 0 || dev >= 64) {
+        *status = EXL3_ERR_BAD_SHAPE;
+        return nullptr;
+    }
+    if (g_static_workspace_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        *status = cuda_status(cudaGetSymbolAddress(&ptr, g_static_workspace));
+        if (*status) return nullptr;
+        if (ptr == nullptr) {
+            *status = EXL3_ERR_CUDA;
+            return nullptr;
+        }
+        g_static_workspace_ptr[dev] = ptr;
+    }
+    return g_static_workspace_ptr[dev];
+}
+
 exl3_status exl3_linear_static(const void* x, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat,
                                const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y,
                                int y_dtype, void* stream)
@@ -500,19 +534,11 @@ exl3_status exl3_linear_static(const void* x, int x_dtype, const uint32_t* packe
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (rows < 0 || n_shards < 1) return EXL3_ERR_BAD_SHAPE;
     if (workspace_layout(rows, k, n_total, n_shards).total > EXL3_STATIC_WORKSPACE_BYTES) return EXL3_ERR_STATIC_WORKSPACE;
-    int dev = -1;
-    if (int rc = cuda_status(cudaGetDevice(&dev))) return rc;
-    if (dev < 0 || dev >= 64) return EXL3_ERR_BAD_SHAPE;
-    if (g_static_workspace_ptr[dev] == nullptr) {
-        // In host code the array's name is only a handle, not a device address: the address has to be asked for,
-        // once per device, with that device current.
-        void* ptr = nullptr;
-        if (int rc = cuda_status(cudaGetSymbolAddress(&ptr, g_static_workspace))) return rc;
-        if (ptr == nullptr) return EXL3_ERR_CUDA;
-        g_static_workspace_ptr[dev] = ptr;
-    }
+    int rc = EXL3_OK;
+    void* ws = static_workspace_of_current_device(&rc);
+    if (rc) return rc;
     return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
-                         y_dtype, g_static_workspace_ptr[dev], EXL3_STATIC_WORKSPACE_BYTES, (cudaStream_t)stream, false);
+                         y_dtype, ws, EXL3_STATIC_WORKSPACE_BYTES, (cudaStream_t)stream, false);
 }
 
 size_t exl3_static_workspace_bytes(void) { return EXL3_STATIC_WORKSPACE_BYTES; }

@@ -377,13 +377,6 @@ template <int K, int FAM, int MT, bool WIDE, bool SPLIT>
 static int launch_tc_kernel(const GemmTcLaunch& l, int sm_count, cudaStream_t st)
 {
     using TT = TcTile<MT, WIDE>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, MT, WIDE, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      (int)TT::SMEM_BYTES)))
-            return rc;
-        attr_set = true;
-    }
     const long long work = (long long)((l.rows + TT::ROWS - 1) / TT::ROWS) * (l.NB / TT::NBLK) * l.ksplit;
     const int grid = work < sm_count ? (int)work : sm_count;
     gemm_tc_kernel<K, FAM, MT, WIDE, SPLIT><<<grid, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
@@ -409,6 +402,43 @@ template <int K>
 static int launch_tc_k(const GemmTcLaunch& l, int fam, int tiling, int sm_count, cudaStream_t st)
 {
     return fam == FAM_HASH ? launch_tc_fam<K, FAM_HASH>(l, tiling, sm_count, st) : launch_tc_fam<K, FAM_MUL1>(l, tiling, sm_count, st);
+}
+
+// The opt-in to large dynamic shared memory is a per-device attribute of every kernel instance: set for all of them when a
+// device is initialised (before any capture), never on the run path.
+template <int K, int FAM, int MT, bool WIDE>
+static int tc_set_attr_tile()
+{
+    using TT = TcTile<MT, WIDE>;
+    int rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, MT, WIDE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TT::SMEM_BYTES));
+    if (rc == EXL3_OK)
+        rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM, MT, WIDE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TT::SMEM_BYTES));
+    return rc;
+}
+
+template <int K>
+static int tc_set_attr_k()
+{
+    int rc = EXL3_OK;
+    if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_HASH, 2, true>();
+    if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_HASH, 3, false>();
+    if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_HASH, 4, false>();
+    if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_MUL1, 2, true>();
+    if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_MUL1, 3, false>();
+    if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_MUL1, 4, false>();
+    return rc;
+}
+
+int gemm_tc_init_device()
+{
+    int rc = tc_set_attr_k<2>();
+    if (rc == EXL3_OK) rc = tc_set_attr_k<3>();
+    if (rc == EXL3_OK) rc = tc_set_attr_k<4>();
+    if (rc == EXL3_OK) rc = tc_set_attr_k<5>();
+    if (rc == EXL3_OK) rc = tc_set_attr_k<6>();
+    if (rc == EXL3_OK) rc = tc_set_attr_k<7>();
+    if (rc == EXL3_OK) rc = tc_set_attr_k<8>();
+    return rc;
 }
 
 constexpr int TC_MAX_KSPLIT = 8;

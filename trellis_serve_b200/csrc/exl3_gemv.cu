@@ -4,6 +4,18 @@
 namespace exl3 {
 
 static int g_mode_override = -1;
+[[maybe_unused]] static int g_tl_next_slot = 0;
+
+#ifdef EXL3_TIMELINE
+__device__ unsigned long long g_timeline[TL_SLOTS][TL_CTAS][TL_POINTS];
+static unsigned long long* g_tl_base = nullptr;
+extern "C" int exl3_debug_timeline(unsigned long long* host_out, int* next_slot)
+{
+    if (next_slot) *next_slot = g_tl_next_slot;
+    return (int)cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(g_timeline));
+}
+extern "C" void exl3_debug_timeline_reset(void) { g_tl_next_slot = 0; }
+#endif
 
 
 int gemv_default_mode(int codebook)
@@ -51,6 +63,7 @@ int gemv_init_device()
 static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLaunch& l, size_t& smem)
 {
     l.a = a;
+    l.tl = nullptr;
     l.KG = a.k / 128;
     l.NB = a.n_total / 128;
     const long long units = (long long)l.KG * l.NB;
@@ -118,6 +131,10 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     GemvLaunch l;
     size_t smem = 0;
     if (int rc = plan_gemv(a, d, a.x != nullptr, l, smem)) return rc;
+#ifdef EXL3_TIMELINE
+    if (!g_tl_base) cudaGetSymbolAddress(reinterpret_cast<void**>(&g_tl_base), g_timeline);
+    l.tl = g_tl_base + (size_t)(g_tl_next_slot++ % TL_SLOTS) * TL_CTAS * TL_POINTS;
+#endif
     switch (a.K) {
         case 2: return launch_gemv_for_k<2>(l, smem, st);
         case 3: return launch_gemv_for_k<3>(l, smem, st);

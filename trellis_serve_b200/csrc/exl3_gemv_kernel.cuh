@@ -34,8 +34,23 @@ constexpr int GEMV_CTAS_PER_SM = 2;         // two resident CTAs per SM: twice t
 enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2, GEMV_ERR_PEER_WAIT = 3 };    // 2: the grouped MoE kernel's copy warp
 constexpr uint32_t GEMV_PEER_MAX_POLLS = 1u << 20;       // bounded wait for a peer's words: about a second
 
+#ifdef EXL3_TIMELINE
+// Measurement build only: thread 0 of every CTA stamps %globaltimer at a few points of the kernel.
+constexpr int TL_POINTS = 8, TL_SLOTS = 128, TL_CTAS = 512;
+__device__ __forceinline__ unsigned long long tl_now()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define EXL3_STAMP(i) do { if (threadIdx.x == 0) p.tl[(blockIdx.x) * TL_POINTS + (i)] = tl_now(); } while (0)
+#else
+#define EXL3_STAMP(i) do { } while (0)
+#endif
+
 struct GemvLaunch {
     GemvArgs a;
+    unsigned long long* tl;     // measurement builds only: where this launch stamps its timeline
     int KG, NB, grid;
     int units_q, units_r;       // units per CTA: the first units_r CTAs take units_q + 1
     int stages;
@@ -203,6 +218,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         ptx::mbar_arrive_expect_tx(&full[slot], bytes);
         ptx::bulk_g2s(stage0 + (size_t)slot * p.stage_stride, p.a.packed + (long long)u * (512 * K), bytes, &full[slot]);
     };
+    EXL3_STAMP(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             ptx::mbar_init(&full[s], 1);
@@ -222,6 +238,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     // Everything below reads or writes memory other kernels write (activations, workspace, output) and so comes after
     // the wait for the kernel ahead; with the in-kernel rotation the (constant) sign vectors are fetched before it.
     if constexpr (XR == 0) ptx::grid_dependency_wait();
+    if constexpr (XR == 0) EXL3_STAMP(1);
     const int nt = warp & 7, kq = warp >> 3;
     const int g = lane >> 2, q = lane & 3;
     const CodebookConst cbc = {p.mul, p.add};
@@ -319,6 +336,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 flag[0] = last;
             }
             ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            EXL3_STAMP(6);
             finish = flag[0] != 0;
             if (finish) {                                 // the last CTA to arrive adds up in a fixed order
                 __threadfence();
@@ -331,6 +349,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
         }
         if (finish) epilogue(fnb);
+        if (finish) EXL3_STAMP(7);
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
 #pragma unroll
@@ -387,6 +406,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             if (!waited) {
                 ptx::grid_dependency_wait();
                 waited = true;
+                EXL3_STAMP(1);
             }
 #pragma unroll
             for (int b = 0; b < BATCH; b++) {
@@ -425,6 +445,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         }
         if (!waited) ptx::grid_dependency_wait();
         ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+        EXL3_STAMP(2);
         const bool ok = g < XR;
         xaddr = ptx::smem_addr(xs) + (ok ? GEMV_XS_ZERO_BYTES + (uint32_t)(kq * 4 * XR + g) * 4u * FW * 4u + (uint32_t)q * FW * 4u : 0u);
         xstep = ok ? XS_SLOT : 0u;
@@ -456,6 +477,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     }
     int remaining = (int)(u1 - u0);
     if (remaining > 0) wait_stage(0, 0);
+    EXL3_STAMP(3);
 
     while (remaining > 0) {
         int run = p.KG - kg;
@@ -545,7 +567,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             }
         }
     }
+    EXL3_STAMP(4);
     if (kg != 0 && u1 > u0) flush(nb);
+    EXL3_STAMP(5);
     if (p.a.tp.world > 1) {
         // The call number moves on once every CTA of this launch has read it: the last CTA to get here bumps it.
         ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);

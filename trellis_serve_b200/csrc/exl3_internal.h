@@ -100,6 +100,7 @@ int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, in
                        int y_bf16, cudaStream_t st);
 
 // exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
+int gemm_tc_init_device();
 size_t gemm_tc_activation_bytes(int rows, int k, int shards);
 void gemm_tc_set_tiling(int t);             // -1 = choose; 0 = 512 x 128 tiles; 1 = 256 x 256 tiles where the shape allows; 2 = 384 x 128 tiles
 size_t gemm_tc_part_bytes(int rows, int n_total);

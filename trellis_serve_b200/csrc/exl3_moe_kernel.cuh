@@ -18,6 +18,9 @@
 namespace exl3 {
 
 constexpr int MOE_BLOCK_ROWS = 8;
+// Largest expert count of one routing alignment: its single CTA keeps three counters per expert in the default 48 KB of
+// shared memory ((3 * E + 1) * 4 bytes + 132 static).
+constexpr int MOE_MAX_EXPERTS = 4064;
 
 struct MoeGemmLaunch {
     const uint32_t* packed;          // [E][NB][KG][...] resident expert stack

@@ -140,7 +140,11 @@ def prepare(trellis: list[torch.Tensor], suh: list[torch.Tensor], svh: list[torc
     k = trellis[0].shape[0] * 16
     n_total = sum(t.shape[1] * 16 for t in trellis)
     reserve_workspace(b.device, workspace_bytes(MAX_ROWS, k, n_total, len(trellis)))
-    return b, torch.stack(suh).contiguous(), torch.cat(svh).contiguous(), ends
+    suh_cat, svh_cat = torch.stack(suh).contiguous(), torch.cat(svh).contiguous()
+    # The run path starts fetching the resident weights and sign vectors while the kernel ahead of it is still running
+    # (programmatic dependent launch), so they must be complete before the first `run` is enqueued: load time pays for that.
+    torch.cuda.current_stream(b.device).synchronize()
+    return b, suh_cat, svh_cat, ends
 
 
 def _geometry(packed: torch.Tensor) -> tuple[int, int, int]:

@@ -2,9 +2,11 @@
 
 `PeerAllReduce` owns one symmetric region per rank (allocated and exchanged through torch's symmetric-memory
 rendezvous: plumbing only) and calls `exl3_allreduce` (csrc/exl3_allreduce.cu), the library's own kernel: every rank
-publishes its vector, raises a flag at every peer, waits for the peers' flags with a bounded spin and adds all
-vectors in rank order with ordinary peer loads over NVLink.  Every rank gets the same bits.  `nccl_all_reduce` is the
-library-collective alternative, kept for comparison.
+pushes its values into its slot at every peer with ordinary peer stores over NVLink, each 32-bit pair of values in one
+64-bit word together with the call number, then polls its OWN memory (bounded) until the words of every rank carry that
+call number and adds them in rank order in fp32.  No flags, no fences, no peer loads, no multicast; every rank gets the
+same bits.  `exl3_linear_allreduce` runs the same protocol inside the epilogue of a row-parallel linear.
+`nccl_all_reduce` is the library-collective alternative, kept for comparison.
 """
 from __future__ import annotations
 
@@ -41,7 +43,7 @@ class PeerAllReduce:
         self.peer_regions = (ctypes.c_void_p * self.world)(*ptrs)
         self.state = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
-        dist.barrier(group=self.group)                 # every region is zero before anyone raises a flag
+        dist.barrier(group=self.group)                 # every region is zero before anyone stores into a peer
 
     def __call__(self, t: torch.Tensor) -> torch.Tensor:
         if self.world == 1:

@@ -103,9 +103,15 @@ def _linear(x: torch.Tensor, trellis: list[torch.Tensor], suh: list[torch.Tensor
         y = lin.run_tc(h, packed, suh_cat, svh_cat, ends, codebooks[0])
     bounds = [0, *ends, n_total]
     stored = [b - a for a, b in zip(bounds[:-1], bounds[1:])]
-    if any(w > s for w, s in zip(out_widths, stored)):
-        raise RuntimeError(f"out_widths {list(out_widths)} exceed the stored widths {stored}")
-    if list(out_widths) != stored:                       # stored output columns beyond the true width are dropped
+    if any(w > s for w, s in zip(out_widths, stored)):   # logical widths beyond the stored ones read as zeros (ops.py:117-121)
+        padded = torch.zeros((y.shape[0], sum(out_widths)), dtype=y.dtype, device=y.device)
+        col = 0
+        for a, w, s in zip(bounds[:-1], out_widths, stored):
+            keep = min(w, s)
+            padded[:, col:col + keep] = y[:, a:a + keep]
+            col += w
+        y = padded
+    elif list(out_widths) != stored:                     # stored output columns beyond the true width are dropped
         y = torch.cat([y[:, a:a + w] for a, w in zip(bounds[:-1], out_widths)], dim=1)
     return y.to(x.dtype).view(*x.shape[:-1], y.shape[1])
 
