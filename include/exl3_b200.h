@@ -53,6 +53,9 @@ int exl3_version(void);
 /* Per-device state (SM count, kernel attributes).  Call once per device before any other entry point and
  * before any CUDA-graph capture.  Replaces init_device (cuda/csrc/exl3_marlin.cu:99-112, :537). */
 exl3_status exl3_init_device(int device);
+/* Multiprocessor count recorded by exl3_init_device for `device` (0 if it has not run): what the persistent grids and the
+ * host's choice between the decode and the tensor-core kernel are sized by.  No counterpart in the reference. */
+int exl3_device_sm_count(int device);
 
 /* ---- resident layout ------------------------------------------------------------------------------------
  * Stored trellis: int16 [k/16, n/16, 16K].  Resident layout: uint32, same number of bytes, a permutation of

@@ -25,6 +25,7 @@ SIGNATURES = {
     "exl3_last_cuda_error": (_i, []),
     "exl3_version": (_i, []),
     "exl3_init_device": (_i, [_i]),
+    "exl3_device_sm_count": (_i, [_i]),
     "exl3_packed_bytes": (_sz, [_i, _i, _i]),
     "exl3_repack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "exl3_unpack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
@@ -96,6 +97,12 @@ def init_device(index: int) -> None:
     if index not in _initialised:
         check(load().exl3_init_device(index), "exl3_init_device")
         _initialised.add(index)
+
+
+def sm_count(index: int) -> int:
+    """Multiprocessors of device `index` as recorded at initialisation."""
+    init_device(index)
+    return int(load().exl3_device_sm_count(index))
 
 
 def int_array(values):

@@ -102,6 +102,12 @@ exl3_status exl3_init_device(int device)
     return rc;
 }
 
+int exl3_device_sm_count(int device)
+{
+    if (device < 0 || device >= 64 || !g_devices[device].ready) return 0;
+    return g_devices[device].sm_count;
+}
+
 size_t exl3_packed_bytes(int k, int n, int K)
 {
     if (k < 0 || n < 0 || K < 2 || K > 8) return 0;

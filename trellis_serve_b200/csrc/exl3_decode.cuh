@@ -162,16 +162,24 @@ __device__ __forceinline__ uint32_t window(const LaneTile<K>& t)
 
 // ---------------------------------------------------------------------------------------------- pipe-balanced windows
 //
-// On sm_100 shifts, logic ops and byte permutes all issue on the 64-lane ALU pipe while integer multiply-add
-// issues on the 64-lane FMA pipe.  A shift-and-mask extraction costs two ALU slots per weight on top of the
-// codebook's logic op, so the ALU pipe alone bounds the decode rate.  Here a window is instead cut out with one
-// multiply by a power of two (drops the bits above the window, FMA pipe) and one shift right by 16 (drops the
-// bits below, ALU pipe): E is re-read as 32-bit registers R_j = E[16j, 16j+32), so every window lies inside one
-// of them.  The powers of two come from kernel parameters (constant bank) so the multiply stays a multiply.
+// On sm_100 shifts, logic ops and byte permutes all issue on the ALU pipe (16 lanes per scheduler) while integer
+// multiply-add issues on the equally wide FMA pipe, and the ALU pipe is what bounds the decode.  A shift-and-mask
+// extraction costs two ALU slots per weight on top of the codebook's logic op.  Here a window is instead cut out with one
+// multiply by a power of two (drops the bits above the window, FMA pipe) and one shift right by 16 (drops the bits below,
+// ALU pipe): E is re-read as 32-bit registers R_j = E[16j, 16j+32), so every window lies inside one of them.  Windows
+// that start on a byte boundary (all of them at K = 8, half at K = 4) take a single mask or byte permute.  The powers of
+// two come from kernel parameters (constant bank) so that the multiply stays a multiply.
 
 struct Pow2 {
-    uint32_t v[17];          // v[c] = 1 << c
+    uint32_t v[32];          // v[c] = 1 << c
 };
+
+__host__ inline Pow2 make_pow2()
+{
+    Pow2 p;
+    for (int c = 0; c < 32; c++) p.v[c] = 1u << c;
+    return p;
+}
 
 template <int K>
 struct LaneRegs {
@@ -203,8 +211,9 @@ __device__ __forceinline__ LaneRegs<K> lane_regs(const uint32_t (&own)[2], uint3
     return R;
 }
 
+// 16-bit trellis state of element P (0..7) of the lane, bits above it cleared.
 template <int K, int P>
-__device__ __forceinline__ uint32_t window_mul(const LaneRegs<K>& R, const Pow2& pw)
+__device__ __forceinline__ uint32_t window_low(const LaneRegs<K>& R, const Pow2& pw)
 {
     constexpr int lo = K * (7 - P);
     constexpr int j = lo / 16;
@@ -212,6 +221,8 @@ __device__ __forceinline__ uint32_t window_mul(const LaneRegs<K>& R, const Pow2&
     static_assert(j < 4, "window outside the lane registers");
     if constexpr (sh == 0) {
         return R.r[j] & 0xFFFFu;
+    } else if constexpr (sh == 8) {
+        return prmt(R.r[j], 0u, 0x4421);          // byte-aligned window (K = 2, 4, 6, 8): one permute
     } else {
         return (R.r[j] * pw.v[16 - sh]) >> 16;
     }

@@ -211,9 +211,9 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                     const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
                     const LaneRegs<K> R = lane_regs<K>(own, prev0);
                     uint32_t st[8];
-                    st[0] = window_mul<K, 0>(R, p.pw); st[1] = window_mul<K, 1>(R, p.pw); st[2] = window_mul<K, 2>(R, p.pw);
-                    st[3] = window_mul<K, 3>(R, p.pw); st[4] = window_mul<K, 4>(R, p.pw); st[5] = window_mul<K, 5>(R, p.pw);
-                    st[6] = window_mul<K, 6>(R, p.pw); st[7] = window_mul<K, 7>(R, p.pw);
+                    st[0] = window_low<K, 0>(R, p.pw); st[1] = window_low<K, 1>(R, p.pw); st[2] = window_low<K, 2>(R, p.pw);
+                    st[3] = window_low<K, 3>(R, p.pw); st[4] = window_low<K, 4>(R, p.pw); st[5] = window_low<K, 5>(R, p.pw);
+                    st[6] = window_low<K, 6>(R, p.pw); st[7] = window_low<K, 7>(R, p.pw);
                     uint32_t w[4];
 #pragma unroll
                     for (int j = 0; j < 4; j++)
@@ -483,7 +483,7 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
     const CodebookConst c = codebook_const(codebook);
     l.mul = c.mul;
     l.add = c.add;
-    for (int i = 0; i <= 16; i++) l.pw.v[i] = 1u << i;
+    l.pw = make_pow2();
     // Rows beyond `rows` inside the last 512-row super tile must read as zeros; with whole super tiles there are none.
     if (rows % TC_ROWS != 0)
         if (int rc = cuda_status(cudaMemsetAsync(xa, 0, gemm_tc_activation_bytes(rows, k, n_shards), st))) return rc;

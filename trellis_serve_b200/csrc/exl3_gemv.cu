@@ -105,7 +105,7 @@ static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLau
     l.mul = c.mul;
     l.add = c.add;
     l.xf_shard_stride = (long long)(a.k / 16) * a.rows * 4 * fw;
-    for (int c = 0; c <= 16; c++) l.pw.v[c] = 1u << c;
+    l.pw = make_pow2();
     l.zeros = reinterpret_cast<const unsigned char*>(a.err) + 64;      // the workspace header stays zero past the error word
     return EXL3_OK;
 }

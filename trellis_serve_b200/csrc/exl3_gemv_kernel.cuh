@@ -20,33 +20,14 @@
 //     (atomic counter, no spinning) adds them in a fixed order, applies Had128 * svh and stores.  Results are
 //     therefore deterministic.
 #pragma once
-#include "exl3_internal.h"
-#include "exl3_ptx.cuh"
+#include "exl3_gemv_common.cuh"
 
 namespace exl3 {
 
 constexpr int GEMV_CONSUMER_WARPS = 16;
 constexpr int GEMV_THREADS = GEMV_CONSUMER_WARPS * 32;             // no copy warp: 512 threads leave 64 registers each
-constexpr int MOE_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;        // the grouped MoE kernel keeps a copy warp
 constexpr int GEMV_MAX_STAGES = 12;
 constexpr int GEMV_CTAS_PER_SM = 2;         // two resident CTAs per SM: twice the warps to hide instruction latency
-
-enum { GEMV_ERR_FULL_WAIT = 1, GEMV_ERR_EMPTY_WAIT = 2, GEMV_ERR_PEER_WAIT = 3 };    // 2: the grouped MoE kernel's copy warp
-constexpr uint32_t GEMV_PEER_MAX_POLLS = 1u << 20;       // bounded wait for a peer's words: about a second
-
-#ifdef EXL3_TIMELINE
-// Measurement build only: thread 0 of every CTA stamps %globaltimer at a few points of the kernel.
-constexpr int TL_POINTS = 8, TL_SLOTS = 128, TL_CTAS = 512;
-__device__ __forceinline__ unsigned long long tl_now()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define EXL3_STAMP(i) do { if (threadIdx.x == 0) p.tl[(blockIdx.x) * TL_POINTS + (i)] = tl_now(); } while (0)
-#else
-#define EXL3_STAMP(i) do { } while (0)
-#endif
 
 struct GemvLaunch {
     GemvArgs a;
@@ -69,118 +50,6 @@ constexpr int GEMV_FUSED_ROWS = 2;
 // one slot of fragments per unit of the CTA.
 constexpr uint32_t GEMV_XS_ZERO_BYTES = 512;
 __host__ __device__ constexpr uint32_t gemv_xs_slot_bytes(int mode, int rows) { return 8u * rows * 4u * gemv_frag_words(mode) * 4u; }
-
-// Unit indices fit 32 bits (the host refuses matrices with 2^31 or more units).
-__host__ __device__ inline long long gemv_first_unit(int cta, int q, int r) { return (long long)cta * q + (cta < r ? cta : r); }
-
-__device__ __forceinline__ int gemv_cta_of_unit(long long u, int q, int r)
-{
-    long long boundary = (long long)r * (q + 1);
-    return u < boundary ? (int)(u / (q + 1)) : r + (int)((u - boundary) / q);
-}
-
-template <int K, int MODE, int FAM>
-__device__ __forceinline__ void decode_tile_regs(const LaneRegs<K>& R, const Pow2& pw, CodebookConst cbc, uint32_t (&w)[8])
-{
-    uint32_t s[8];
-    s[0] = window_mul<K, 0>(R, pw); s[1] = window_mul<K, 1>(R, pw); s[2] = window_mul<K, 2>(R, pw); s[3] = window_mul<K, 3>(R, pw);
-    s[4] = window_mul<K, 4>(R, pw); s[5] = window_mul<K, 5>(R, pw); s[6] = window_mul<K, 6>(R, pw); s[7] = window_mul<K, 7>(R, pw);
-    if constexpr (MODE == GEMV_SPLIT) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) w[j] = hash_pair(s[j], cbc);
-    } else if constexpr (FAM == FAM_HASH) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) w[j] = hash_pair_rounded(s[2 * j], s[2 * j + 1], cbc);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 4; j++) w[j] = mul1_pair(s[2 * j], s[2 * j + 1], cbc);
-    }
-}
-
-__device__ __forceinline__ float gemv_load_x(const void* p, long long idx, bool bf16)
-{
-    // bf16 inputs are first converted to fp16 (round to nearest even), as the stand-alone rotation kernel does.
-    if (bf16) return __half2float(__float2half_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx])));
-    return __half2float(reinterpret_cast<const __half*>(p)[idx]);
-}
-
-// Row-parallel shard: 4 consecutive columns (index o) of one output row are a partial sum.  They go, rounded to the
-// output type and tagged with the call number, into this rank's slot at every peer (single 64-bit peer stores); then
-// the same words of all ranks are awaited here (bounded), added in rank order in fp32 and rounded once: the bits a
-// separate all-reduce of the rounded outputs gives.  Kept out of line: it runs once per 128 outputs and must not
-// weigh on the register allocation of the decode loop.
-static __device__ __noinline__ void gemv_exchange_store(const TpExchange& tp, uint32_t tp_epoch, bool bf, const float (&v)[4], long long o,
-                                                 uint16_t* out, int* err)
-{
-    uint32_t w2[2];
-#pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const __half2 hh = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-        if (bf) {
-            const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(hh), __high2float(hh));
-            w2[e] = *reinterpret_cast<const uint32_t*>(&bb);
-        } else {
-            w2[e] = *reinterpret_cast<const uint32_t*>(&hh);
-        }
-    }
-    const size_t set_off = (size_t)TP_HEADER_BYTES + (size_t)(tp_epoch & 1u) * tp.world * tp.slot_bytes;
-    const size_t word = (size_t)(o >> 1);                    // 32-bit word of two values inside a slot
-    const unsigned long long tag = (unsigned long long)tp_epoch << 32;
-    for (int r = 0; r < tp.world; r++) {
-        unsigned long long* dst = reinterpret_cast<unsigned long long*>(tp.base[r] + set_off + (size_t)tp.rank * tp.slot_bytes) + word;
-        ptx::st_relaxed_sys_v2u64(dst, tag | w2[0], tag | w2[1]);          // word is even: 16-byte aligned
-    }
-    float a[4] = {0.f, 0.f, 0.f, 0.f};
-    const unsigned char* own = tp.base[tp.rank] + set_off;
-    bool gave_up = *reinterpret_cast<volatile int*>(err) != 0;       // a wait that already ran out is not repeated block after block
-    constexpr int BATCH = 4;                      // ranks whose words are requested together: their latencies overlap
-    for (int r0 = 0; r0 < tp.world; r0 += BATCH) {
-        unsigned long long got[BATCH][2];
-#pragma unroll
-        for (int j = 0; j < BATCH; j++) {
-            const int r = r0 + j < tp.world ? r0 + j : tp.world - 1;
-            const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)r * tp.slot_bytes) + word;
-            ptx::ld_relaxed_sys_v2u64(src, got[j][0], got[j][1]);
-        }
-#pragma unroll
-        for (int j = 0; j < BATCH; j++) {
-            if (r0 + j < tp.world) {
-                const unsigned long long* src = reinterpret_cast<const unsigned long long*>(own + (size_t)(r0 + j) * tp.slot_bytes) + word;
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    uint32_t polls = 0;
-                    while ((uint32_t)(got[j][e] >> 32) != tp_epoch && !gave_up) {
-                        if (++polls > GEMV_PEER_MAX_POLLS) {
-                            gave_up = true;
-                            atomicExch(err, GEMV_ERR_PEER_WAIT);
-                            break;
-                        }
-                        got[j][e] = ptx::ld_relaxed_sys_u64(src + e);
-                    }
-                    const uint32_t lo = (uint32_t)got[j][e];
-                    if (bf) {
-                        const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&lo);
-                        a[2 * e] += __low2float(bb);
-                        a[2 * e + 1] += __high2float(bb);
-                    } else {
-                        const __half2 hh = *reinterpret_cast<const __half2*>(&lo);
-                        a[2 * e] += __low2float(hh);
-                        a[2 * e + 1] += __high2float(hh);
-                    }
-                }
-            }
-        }
-    }
-    uint2 res;
-    if (bf) {
-        const __nv_bfloat162 b0 = __floats2bfloat162_rn(a[0], a[1]), b1 = __floats2bfloat162_rn(a[2], a[3]);
-        res = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
-    } else {
-        const __half2 h0 = __floats2half2_rn(a[0], a[1]), h1 = __floats2half2_rn(a[2], a[3]);
-        res = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-    }
-    *reinterpret_cast<uint2*>(out + o) = res;
-}
 
 // MODE: GEMV_SPLIT / GEMV_PAIRED.  FAM: FAM_HASH / FAM_MUL1 (split implies hash).  MB: 8-row groups (1 or 2).
 // XR: 0 = activation fragments come from the workspace (written by the rotation kernel ahead of this launch);
@@ -261,7 +130,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 #pragma unroll
             for (int e = 0; e < 4; e++) v[e] = P[m * 128 + 4 * lane + e];
             const long long o = (long long)m * p.a.n_total + fnb * 128 + 4 * lane;
-            if (p.a.rotated) {
+            if (p.a.rotated && p.a.out_dtype == EXL3_F32) {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.a.out) + o) = make_float4(v[0], v[1], v[2], v[3]);
+            } else if (p.a.rotated) {
                 __half h[4];
 #pragma unroll
                 for (int e = 0; e < 4; e++) h[e] = __float2half_rn(v[e]);
@@ -340,9 +211,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             finish = flag[0] != 0;
             if (finish) {                                 // the last CTA to arrive adds up in a fixed order
                 __threadfence();
+                const float* base = p.a.partials + (size_t)fnb * nelem;
                 for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) {
                     float sum = 0.f;
-                    for (int c = c_first; c <= c_last; c++) sum += __ldcg(p.a.partials + (size_t)(c + fnb) * rows * 128 + e);
+                    int c = c_first;
+                    for (; c + 3 <= c_last; c += 4) {     // four loads in flight; the additions keep their order
+                        const float a0 = __ldcg(base + (size_t)c * nelem + e), a1 = __ldcg(base + (size_t)(c + 1) * nelem + e);
+                        const float a2 = __ldcg(base + (size_t)(c + 2) * nelem + e), a3 = __ldcg(base + (size_t)(c + 3) * nelem + e);
+                        sum += a0;
+                        sum += a1;
+                        sum += a2;
+                        sum += a3;
+                    }
+                    for (; c <= c_last; c++) sum += __ldcg(base + (size_t)c * nelem + e);
                     P[e] = sum;
                 }
             }
@@ -478,6 +359,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     int remaining = (int)(u1 - u0);
     if (remaining > 0) wait_stage(0, 0);
     EXL3_STAMP(3);
+    EXL3_STAMP_CLK(8);
+    EXL3_STAMP_SM(10);
 
     while (remaining > 0) {
         int run = p.KG - kg;
@@ -568,6 +451,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         }
     }
     EXL3_STAMP(4);
+    EXL3_STAMP_CLK(9);
     if (kg != 0 && u1 > u0) flush(nb);
     EXL3_STAMP(5);
     if (p.a.tp.world > 1) {

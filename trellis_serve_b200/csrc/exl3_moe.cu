@@ -287,7 +287,7 @@ int launch_moe_gemm(MoeGemmLaunch l, int K, int codebook, int mode, cudaStream_t
 {
     const DeviceInfo* d = current_device_info();
     if (!d) return EXL3_ERR_NOT_INITIALISED;
-    int grid = d->sm_count * GEMV_CTAS_PER_SM;
+    int grid = d->sm_count * MOE_CTAS_PER_SM;
     if (grid > GEMV_MAX_GRID) grid = GEMV_MAX_GRID;
     const uint32_t unit_bytes = 2048u * K;
     int ups = (int)((24u * 1024u + unit_bytes - 1) / unit_bytes);
@@ -297,15 +297,15 @@ int launch_moe_gemm(MoeGemmLaunch l, int K, int codebook, int mode, cudaStream_t
     l.stage_stride = (uint32_t)ups * unit_bytes;
     const size_t fixed = 256 + GEMV_MAX_ROWS * 128 * 4;
     int stages = (int)((96u * 1024u) / l.stage_stride);
-    const int cap = (int)((d->max_smem_optin / GEMV_CTAS_PER_SM - 2048 - fixed) / l.stage_stride);
+    const int cap = (int)((d->max_smem_optin / MOE_CTAS_PER_SM - 2048 - fixed) / l.stage_stride);
     if (stages > cap) stages = cap;
-    if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
+    if (stages > MOE_MAX_STAGES) stages = MOE_MAX_STAGES;
     if (stages < 2) return EXL3_ERR_UNSUPPORTED_ROWS;
     l.stages = stages;
     const CodebookConst c = codebook_const(codebook);
     l.mul = c.mul;
     l.add = c.add;
-    for (int i = 0; i <= 16; i++) l.pw.v[i] = 1u << i;
+    l.pw = make_pow2();
     const size_t smem = fixed + (size_t)stages * l.stage_stride;
     const int fam = codebook_family(codebook);
     switch (K) {

@@ -13,11 +13,15 @@
 // stage never crosses a moe block (the next block is another expert's matrix), activation fragments always hold 8
 // rows per block (padding rows are zero), the epilogue uses the expert's svh and scatters rows to their slots.
 #pragma once
-#include "exl3_gemv_kernel.cuh"
+#include "exl3_gemv_common.cuh"
 
 namespace exl3 {
 
 constexpr int MOE_BLOCK_ROWS = 8;
+constexpr int MOE_CONSUMER_WARPS = 16;
+constexpr int MOE_THREADS = (MOE_CONSUMER_WARPS + 1) * 32;        // 16 decode warps and a copy warp
+constexpr int MOE_MAX_STAGES = 12;
+constexpr int MOE_CTAS_PER_SM = 2;
 // Largest expert count of one routing alignment: its single CTA keeps three counters per expert in the default 48 KB of
 // shared memory ((3 * E + 1) * 4 bytes + 132 static).
 constexpr int MOE_MAX_EXPERTS = 4064;
@@ -45,15 +49,15 @@ struct MoeGemmLaunch {
 int launch_moe_gemm(MoeGemmLaunch l, int K, int codebook, int mode, cudaStream_t st);
 
 template <int K, int MODE, int FAM>
-__global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel(const MoeGemmLaunch p)
+__global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(const MoeGemmLaunch p)
 {
     constexpr int FW = gemv_frag_words(MODE);
     constexpr uint32_t W_BYTES = 2048u * K;
     using Frag = typename std::conditional<FW == 4, uint4, uint2>::type;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-    uint64_t* empty = full + GEMV_MAX_STAGES;
-    int* flag = reinterpret_cast<int*>(smem + 2 * GEMV_MAX_STAGES * 8);
+    uint64_t* empty = full + MOE_MAX_STAGES;
+    int* flag = reinterpret_cast<int*>(smem + 2 * MOE_MAX_STAGES * 8);
     float* P = reinterpret_cast<float*>(smem + 256);                              // [8][128]
     unsigned char* stage0 = smem + 256 + GEMV_MAX_ROWS * 128 * 4;
 
@@ -62,7 +66,7 @@ __global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
+            ptx::mbar_init(&empty[s], MOE_CONSUMER_WARPS);
         }
         flag[0] = 0;
         ptx::mbar_fence_init();
@@ -83,7 +87,7 @@ __global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel
     int b = (int)(u0 / UB);
     int in_blk = (int)(u0 - (long long)b * UB);
 
-    if (warp == GEMV_CONSUMER_WARPS) {
+    if (warp == MOE_CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             int s = 0;
@@ -137,7 +141,7 @@ __global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel
     };
 
     auto flush = [&]() {
-        ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+        ptx::named_bar_sync(1, MOE_CONSUMER_WARPS * 32);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
             if (kq == half) {
@@ -147,7 +151,7 @@ __global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel
                     *dst = half == 0 ? acc[e] : *dst + acc[e];
                 }
             }
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            ptx::named_bar_sync(1, MOE_CONSUMER_WARPS * 32);
         }
         const int gb = b * p.NB + nb;                           // global column block
         const long long ub = (long long)gb * p.KG;
@@ -158,8 +162,8 @@ __global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel
         bool finish = true;
         if (c_first != c_last) {
             float* slot = p.partials + (size_t)(cta + gb) * nelem;
-            for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) slot[e] = P[e];
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            for (int e = tid; e < nelem; e += MOE_CONSUMER_WARPS * 32) slot[e] = P[e];
+            ptx::named_bar_sync(1, MOE_CONSUMER_WARPS * 32);
             if (tid == 0) {
                 __threadfence();          // publishes every thread's stores (ordered before it by the barrier) ahead of the counter
                 const int old = atomicAdd(&p.counters[gb], 1);
@@ -167,17 +171,17 @@ __global__ void __launch_bounds__(MOE_THREADS, GEMV_CTAS_PER_SM) moe_gemm_kernel
                 if (last) p.counters[gb] = 0;
                 flag[0] = last;
             }
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            ptx::named_bar_sync(1, MOE_CONSUMER_WARPS * 32);
             finish = flag[0] != 0;
             if (finish) {
                 __threadfence();
-                for (int e = tid; e < nelem; e += GEMV_CONSUMER_WARPS * 32) {
+                for (int e = tid; e < nelem; e += MOE_CONSUMER_WARPS * 32) {
                     float sum = 0.f;
                     for (int c = c_first; c <= c_last; c++) sum += __ldcg(p.partials + (size_t)(c + gb) * nelem + e);
                     P[e] = sum;
                 }
             }
-            ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+            ptx::named_bar_sync(1, MOE_CONSUMER_WARPS * 32);
         }
         if (finish && warp < MOE_BLOCK_ROWS) {
             const int slot_id = p.sorted_ids[b * MOE_BLOCK_ROWS + warp];

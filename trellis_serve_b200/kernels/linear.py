@@ -152,9 +152,24 @@ def _geometry(packed: torch.Tensor) -> tuple[int, int, int]:
     return kg * 128, nb * 128, K
 
 
+def _own_or_given(workspace: torch.Tensor | None, device: torch.device, need: int, table: dict) -> torch.Tensor:
+    """The caller's scratch when one is handed in (it must be large enough: nothing is allocated on its behalf), else the
+    per-device one of this module, grown if needed."""
+    if workspace is not None:
+        if workspace.numel() * workspace.element_size() < need:
+            raise RuntimeError(f"workspace holds {workspace.numel() * workspace.element_size()} bytes, this call needs {need}")
+        return workspace
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    cur = table.get(idx)
+    if cur is None or cur.numel() < need:
+        cur = table[idx] = torch.zeros(need, dtype=torch.uint8, device=torch.device("cuda", idx))
+    return cur
+
+
 def run(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int],
-        codebook: int, out: torch.Tensor | None = None, exchange=None) -> torch.Tensor:
+        codebook: int, out: torch.Tensor | None = None, exchange=None, workspace: torch.Tensor | None = None) -> torch.Tensor:
     """x fp16 | bf16 [rows, k] contiguous -> y (same dtype) [rows, n_total].  Only y is allocated (unless `out`).
+    `workspace`: caller-owned zero-filled scratch of at least `workspace_bytes(...)` (default: this module's own).
     An fp32 `out` receives the unrounded accumulators (accuracy measurements).  `exchange` (a
     `runtime.allreduce.PeerAllReduce`): the matrix is a row-parallel shard and y is summed over the ranks inside the
     kernel, the same bits as `exchange(run(...))`."""
@@ -169,7 +184,7 @@ def run(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.
     y = out if out is not None else torch.empty((rows, n_total), dtype=x.dtype, device=x.device)
     if rows == 0:
         return y
-    ws = reserve_workspace(x.device, workspace_bytes(rows, k, n_total, shards))
+    ws = _own_or_given(workspace, x.device, workspace_bytes(rows, k, n_total, shards), _workspace)
     with torch.cuda.device(x.device):
         if exchange is not None and exchange.world > 1:
             _lib.check(lib.exl3_linear_allreduce(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
@@ -184,9 +199,14 @@ def run(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.
     return y
 
 
+def tc_workspace_bytes(rows: int, k: int, n_total: int, shards: int) -> int:
+    return int(_lib.load().exl3_gemm_tc_workspace_bytes(rows, k, n_total, shards))
+
+
 def run_tc(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int],
-           codebook: int, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Many-row version of `run` on the tcgen05 tensor cores: weights decoded once per 512 rows into the MMA operand."""
+           codebook: int, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Many-row version of `run` on the tcgen05 tensor cores: weights decoded once per 512 rows into the MMA operand.
+    `workspace`: caller-owned scratch of at least `tc_workspace_bytes(...)` whose first 256 bytes are zero."""
     _require_cuda(x, "x")
     lib = _lib.load()
     _lib.init_device(x.device.index if x.device.index is not None else torch.cuda.current_device())
@@ -198,10 +218,7 @@ def run_tc(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: tor
     y = out if out is not None else torch.empty((rows, n_total), dtype=x.dtype, device=x.device)
     if rows == 0:
         return y
-    need = int(lib.exl3_gemm_tc_workspace_bytes(rows, k, n_total, shards))
-    ws = _tc_workspace.get(x.device.index)
-    if ws is None or ws.numel() < need:
-        ws = _tc_workspace[x.device.index] = torch.zeros(need, dtype=torch.uint8, device=x.device)
+    ws = _own_or_given(workspace, x.device, tc_workspace_bytes(rows, k, n_total, shards), _tc_workspace)
     with torch.cuda.device(x.device):
         _lib.check(lib.exl3_linear_tc(_ptr(x), _dtype_code(x), _ptr(b), K, codebook, _ptr(suh_cat), _ptr(svh_cat),
                                       _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(y), _dtype_code(y), _ptr(ws),

@@ -313,6 +313,83 @@ def forward_expert_parallel(x, topk_weights, topk_ids, pack: MixedPack, reduce, 
     return y
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# One layer with every temporary carved out of a caller-owned workspace: the form the backend contract asks for
+# (cuda/src/sglang_exl3/kernels/base.py:74-80: after warm-up the run path never allocates).
+
+def _up256(n: int) -> int:
+    return (n + 255) & ~255
+
+
+def _layer_regions(num_experts_per_class: list[int], hidden: int, inter: int, codebook: int, tokens: int, top_k: int):
+    """[(name, nbytes)] of one layer's temporaries, in workspace order; per class: routing triple and fragment buffers."""
+    lib = _lib.load()
+    slots = tokens * top_k
+    regions = [("ids32", slots * 4), ("wts", slots * 4), ("gu", slots * 2 * inter * 2), ("yd", slots * hidden * 2)]
+    gemv = 0
+    for c, e in enumerate(num_experts_per_class):
+        cap = int(lib.exl3_moe_sorted_capacity(slots, e))
+        regions += [(f"sorted{c}", cap * 4), (f"experts{c}", max(cap // 8, 1) * 4), (f"post{c}", 4),
+                    (f"xf13_{c}", int(lib.exl3_moe_fragment_bytes(cap, hidden, 2, codebook))),
+                    (f"xf2_{c}", int(lib.exl3_moe_fragment_bytes(cap, inter, 1, codebook)))]
+        gemv = max(gemv, int(lib.exl3_moe_workspace_bytes(cap, 2 * inter)), int(lib.exl3_moe_workspace_bytes(cap, hidden)))
+    return [("gemv", gemv)] + regions       # the GEMV workspace first: its header and counters must stay zero
+
+
+def layer_workspace_bytes(num_experts_per_class: list[int], hidden: int, inter: int, codebook: int, tokens: int, top_k: int) -> int:
+    """Bytes `run_layer` needs for up to `tokens` tokens (zero-filled once by the caller)."""
+    return sum(_up256(n) for _, n in _layer_regions(num_experts_per_class, hidden, inter, codebook, tokens, top_k))
+
+
+def run_layer(x, topk_weights, topk_ids, pack: MixedPack, out: torch.Tensor, workspace: torch.Tensor,
+              expert_maps: list[torch.Tensor] | None = None) -> torch.Tensor:
+    """One MoE layer (alignment included) that allocates nothing: `workspace` is a zero-filled uint8 tensor of at least
+    `layer_workspace_bytes(...)`; `expert_maps` replaces the pack's per-class maps (expert parallelism with an engine's
+    global -> local map composed in).  Same kernels and the same bits as `forward_mixed`."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
+    tokens, hidden = x.shape
+    top_k, inter = topk_ids.shape[1], pack.inter
+    slots = tokens * top_k
+    if tokens == 0:
+        return out
+    dev, st = x.device, _stream(x.device)
+    maps = expert_maps if expert_maps is not None else pack.expert_maps
+    views, off = {}, 0
+    for name, n in _layer_regions([p.num_experts for p in pack.packs], hidden, inter, pack.codebook, tokens, top_k):
+        views[name] = workspace[off:off + n]
+        off += _up256(n)
+    if off > workspace.numel():
+        raise RuntimeError(f"MoE workspace holds {workspace.numel()} bytes, this call needs {off}")
+    ids32, wts = views["ids32"].view(torch.int32), views["wts"].view(torch.float32)
+    ids32.copy_(topk_ids.reshape(-1))
+    wts.copy_(topk_weights.reshape(-1))
+    gu, yd, ws = views["gu"], views["yd"], views["gemv"]
+    if not pack.covers_all or expert_maps is not None:
+        yd.zero_()                        # slots of experts held elsewhere are never written and must add nothing
+    with torch.cuda.device(dev):
+        for c, (pk, emap) in enumerate(zip(pack.packs, maps)):
+            sorted_ids, expert_ids, num_post = views[f"sorted{c}"], views[f"experts{c}"], views[f"post{c}"]
+            xf13, xf2 = views[f"xf13_{c}"], views[f"xf2_{c}"]
+            cap = sorted_ids.numel() // 4
+            K = pk.bits
+            _lib.check(lib.exl3_moe_align_mapped(_ptr(ids32), slots, emap.numel(), _ptr(emap), pk.num_experts, _ptr(sorted_ids), cap,
+                                                 _ptr(expert_ids), _ptr(num_post), st), "exl3_moe_align_mapped")
+            _lib.check(lib.exl3_moe_had_in(_ptr(x), _dtype_code(x), _ptr(pk.suh13), 2, hidden, top_k, slots, _ptr(sorted_ids), cap,
+                                           _ptr(expert_ids), _ptr(num_post), pk.codebook, _ptr(xf13), st), "exl3_moe_had_in")
+            _lib.check(lib.exl3_moe_gemm(_ptr(xf13), _ptr(pk.w13), K, pk.codebook, _ptr(pk.svh13), _ptr(sorted_ids), _ptr(expert_ids),
+                                         _ptr(num_post), cap, slots, hidden, 2 * inter, inter, _ptr(gu), _ptr(ws), ws.numel(), st),
+                       "exl3_moe_gemm")
+            _lib.check(lib.exl3_moe_glu_had_in(_ptr(gu), _ptr(pk.suh2), inter, slots, _ptr(sorted_ids), cap, _ptr(expert_ids),
+                                               _ptr(num_post), pk.codebook, _ptr(xf2), st), "exl3_moe_glu_had_in")
+            _lib.check(lib.exl3_moe_gemm(_ptr(xf2), _ptr(pk.w2), K, pk.codebook, _ptr(pk.svh2), _ptr(sorted_ids), _ptr(expert_ids),
+                                         _ptr(num_post), cap, slots, inter, hidden, 0, _ptr(yd), _ptr(ws), ws.numel(), st),
+                       "exl3_moe_gemm")
+        _lib.check(lib.exl3_moe_combine(_ptr(yd), _ptr(wts), _ptr(ids32), tokens, top_k, hidden, maps[0].numel(), _ptr(out),
+                                        _dtype_code(out), st), "exl3_moe_combine")
+    return out
+
+
 def run(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block: int, pack: ExpertPack,
         out: torch.Tensor | None = None) -> torch.Tensor:
     return run_tensors(x, topk_weights, topk_ids, sorted_ids, expert_ids, num_post_padded, block, *pack.tensors(),

@@ -29,6 +29,7 @@ import os
 
 import torch
 
+from .._lib import sm_count as lib_sm_count
 from ..kernels import linear as lin
 
 _lib = torch.library.Library("exl3_b200", "FRAGMENT")       # must stay alive at module scope
@@ -36,11 +37,10 @@ _lib = torch.library.Library("exl3_b200", "FRAGMENT")       # must stay alive at
 # Row count from which the many-row path is taken; 0 = decide per call with `prefers_decode` (the crossover depends on the
 # shape and, since narrow outputs split their reduction over the idle SMs, lies at 17 rows for the 27B-shape groups).
 DENSE_ROWS = int(os.environ.get("EXL3_B200_DENSE_ROWS", "0"))
-_SMS = 148
 
 
-def prefers_decode(rows: int, k: int, n_total: int) -> bool:
-    """Cost model fitted to measurements on B200 (microseconds).  The decode kernel streams the weights once per 16 rows:
+def prefers_decode(rows: int, k: int, n_total: int, sms: int = 148) -> bool:
+    """Cost model fitted to measurements on B200 (microseconds); `sms` is the device's multiprocessor count.  The decode kernel streams the weights once per 16 rows:
     ~14 + 0.38 per million weights for a full chunk, ~0.8 of that for a last chunk of up to 8 rows.  The tensor-core kernel
     works through its tiles in waves over the SMs at ~1.1 per 64-deep reduction block (~1.6 for the 512-row tiles used above
     256 rows); when the tiles are fewer than the SMs the reduction of each is cut into up to 8 parts on CTAs of their own;
@@ -53,8 +53,8 @@ def prefers_decode(rows: int, k: int, n_total: int) -> bool:
         tiles, per_block = -(-rows // 256) * max(n_total // 256, 1), 1.1
     else:
         tiles, per_block = -(-rows // 512) * (n_total // 128), 1.6
-    parts = max(1, min(8, _SMS // max(tiles, 1), k // 64))
-    tensor = -(-tiles // _SMS) * (k / 64) / parts * per_block + 12.0 + (8.0 if parts > 1 else 0.0) + 0.08 * min(rows, 256)
+    parts = max(1, min(8, sms // max(tiles, 1), k // 64))
+    tensor = -(-tiles // sms) * (k / 64) / parts * per_block + 12.0 + (8.0 if parts > 1 else 0.0) + 0.08 * min(rows, 256)
     return decode <= tensor
 # "tc": fused tcgen05 kernel; "library": decode to fp16 + library GEMM (the reference's sequence), for comparisons.
 PREFILL = os.environ.get("EXL3_B200_PREFILL", "tc")
@@ -94,7 +94,8 @@ def _linear(x: torch.Tensor, trellis: list[torch.Tensor], suh: list[torch.Tensor
     if h.shape[1] < k:                                   # stored input width is padded to 128
         h = torch.nn.functional.pad(h, (0, k - h.shape[1]))
     h = h.contiguous()
-    if (h.shape[0] < DENSE_ROWS) if DENSE_ROWS > 0 else prefers_decode(h.shape[0], k, n_total):
+    sms = lib_sm_count(h.device.index if h.device.index is not None else torch.cuda.current_device())
+    if (h.shape[0] < DENSE_ROWS) if DENSE_ROWS > 0 else prefers_decode(h.shape[0], k, n_total, sms):
         y = lin.run(h, packed, suh_cat, svh_cat, ends, codebooks[0])
     elif dense or PREFILL == "library":
         y = torch.empty((h.shape[0], n_total), dtype=h.dtype, device=h.device)
