@@ -14,6 +14,12 @@ fixed: "strong" scaling.
 
 `--impl reference` times the CPU implementation of the same path (the oracle port of the reference decoder,
 multi-threaded C) on a bounded sample: the seven matrices of one layer.
+
+The timed region is repeated in BLOCKS of `--steps` steps (each block bracketed by a barrier and a synchronise); the
+median block gives `ms_per_step`, and the clock sampler sees seconds of load instead of a tenth of one.
+Secondary workloads: `--workload c1` (one 4096x4096 K=4 3INST linear at batch 1 over a ring of distinct matrices larger
+than L2), `--workload prefill`, `--workload moe`.  The default line also carries `sweep` (batch 4 / 16 of the same step,
+and K = 2..8 on the 17408x5120 shape), measured outside the timed region.
 """
 from __future__ import annotations
 
@@ -125,6 +131,32 @@ def cpu_sample(K: int, codebook: int, min_seconds: float = 8.0, max_reps: int = 
             "seconds_per_layer": best, "tok_s": 1.0 / (best * 64)}
 
 
+BLOCKS = 10          # timed blocks of `--steps` steps; the median block is reported
+
+
+def workload_config(args, world: int, total_bytes: float) -> dict:
+    """The `config` object: identical in the repo's arm and the reference arm for the same command line."""
+    return {"workload": WORKLOAD, "layers": args.layers, "bits": args.bits, "codebook": "3inst", "rows": args.rows,
+            "parallelism": f"tp{world}", "allreduce": (args.allreduce if world > 1 else None),
+            "l2": "inputs larger than L2, no flush", "packed_bytes_per_step": total_bytes}
+
+
+def packed_bytes_per_step(layers: int, K: int) -> float:
+    weights = 5120 * (5120 + 2 * 1024) + 5120 * 5120 + 3 * 5120 * 17408
+    return float(layers * weights * K // 8)
+
+
+def traffic_ratio() -> tuple[float | None, str]:
+    """DRAM bytes moved per algorithmic byte of the dominant kernel, from the ncu capture whose figures sit beside its
+    summary (read + write of one gate|up launch over its packed-weight bytes)."""
+    path = os.path.join(ROOT, "profiles", "gemv_kernel_27b_k3_batch1.traffic.json")
+    if not os.path.exists(path):
+        return None, "no capture recorded"
+    with open(path) as f:
+        t = json.load(f)
+    return (t["dram_bytes_read"] + t["dram_bytes_write"]) / t["algorithmic_bytes"], t.get("source", path)
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -136,22 +168,22 @@ def run_reference(args) -> None:
     for _ in range(args.steps):
         runs.append(cpu_sample(K, cb, min_seconds=0.0, max_reps=1))
     best = max(runs, key=lambda r: r["value"])
-    ms = best["seconds_per_layer"] * 1e3
+    # One step of the workload is `layers` layers; the sample timed one layer, every layer costs the same.
+    ms = best["seconds_per_layer"] * 1e3 * args.layers
     line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": args.layers, "bits": K, "codebook": "3inst", "rows": args.rows,
-                       "parallelism": f"tp{args.gpus}", "l2": "inputs larger than L2, no flush",
-                       "packed_bytes_per_step": 64 * 123863040.0 if K == 3 else None},
+            "config": workload_config(args, args.gpus, packed_bytes_per_step(args.layers, K)),
+            "ms_per_step_note": f"{args.layers} x the measured time of one layer ({best['seconds_per_layer'] * 1e3:.1f} ms)",
             "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "tok_s": best["tok_s"], "gpu_launches": 0}
+            "tok_s": 1e3 / ms, "gpu_launches": 0}
     print(json.dumps(line))
 
 
 def run_prefill(args) -> None:
-    """Secondary workload (BASELINE config 3): the four fused groups of one 27B-shape layer at M = 2048 rows, K = 4,
-    MCG codebook, through the fused tcgen05 kernel.  One step = one layer.  Tensor-pipe roofline."""
+    """Secondary workload: the four fused groups of one 27B-shape layer at M = 2048 rows, K = 4, MCG codebook, through the
+    fused tcgen05 kernel.  One step = one layer.  Tensor-pipe roofline."""
     import torch
     from trellis_serve_b200.kernels import linear as lin
     from trellis_serve_b200.runtime.layerset import random_packed, random_signs
@@ -201,8 +233,8 @@ def run_prefill(args) -> None:
 
 
 def run_moe(args) -> None:
-    """Secondary workload (BASELINE config 4): one MoE layer, hidden 2048, 256 experts, intermediate 512, top-8, K = 3,
-    softmax-of-N(0,1) routing, captured in a CUDA graph.  GB/s on the packed bytes of the distinct routed experts."""
+    """Secondary workload: one MoE layer, hidden 2048, 256 experts, intermediate 512, top-8, K = 3, softmax-of-N(0,1)
+    routing, captured in a CUDA graph.  GB/s on the packed bytes of the distinct routed experts."""
     import torch
     from trellis_serve_b200 import _lib
     from trellis_serve_b200.kernels import moe
@@ -253,6 +285,149 @@ def run_moe(args) -> None:
                       "gpu_launches": 6 * args.steps, "clocks": clocks.summary()}))
 
 
+def _graph_ring_time(run_one, ring: int, reps: int = 5) -> float:
+    """Milliseconds per launch of `run_one(i)` for i in range(ring), captured as one CUDA graph over distinct weights
+    (larger than L2 together) and replayed `reps` times: best replay."""
+    import torch
+    for i in range(min(ring, 2)):
+        run_one(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(ring):
+            run_one(i)
+    g.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / ring)
+    return best
+
+
+def single_matrix_rate(dev, k: int, n: int, K: int, rows: int, codebook: int = 0, seed: int = 1) -> dict:
+    """One k x n linear at `rows` rows: microseconds per launch and GB/s on packed bytes, over a ring of distinct weights."""
+    import torch
+    from trellis_serve_b200.kernels import linear as lin
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    nbytes = k * n * K // 8
+    ring = max(2, min(64, int(600e6 // nbytes) + 1))
+    ws = [random_packed(k, n, K, gen, dev) for _ in range(ring)]
+    suh, svh = random_signs(k, gen, dev, 1), random_signs(n, gen, dev).view(-1)
+    x = torch.randn((rows, k), device=dev, generator=gen).half()
+    out = torch.empty((rows, n), dtype=torch.float16, device=dev)
+    ms = _graph_ring_time(lambda i: lin.run(x, ws[i], suh, svh, [], codebook, out=out), ring)
+    del ws
+    torch.cuda.empty_cache()
+    return {"us_per_launch": ms * 1e3, "gbs": nbytes / ms / 1e6, "ring": ring, "packed_bytes": nbytes}
+
+
+def run_c1(args) -> None:
+    """Secondary workload: ONE 4096 x 4096 linear, K = 4, 3INST, batch 1, timed over a ring of 64 distinct matrices
+    (537 MB, larger than L2) chained in one CUDA graph.  One step = one launch."""
+    import torch
+    from trellis_serve_b200.kernels import linear as lin
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    with ClockSampler(0) as clocks:
+        r = single_matrix_rate(dev, 4096, 4096, 4, 1)
+    lin.device_error(dev)
+    peak, kind = measured_peak_hbm()
+    print(json.dumps({"metric": "exl3_gemv_hbm_gbs_packed_bytes_4096x4096_k4_batch1", "value": r["gbs"], "unit": UNIT, "n_gpus": 1,
+                      "steps": r["ring"], "warmup": args.warmup, "ms_per_step": r["us_per_launch"] / 1e3, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "single EXL3 linear 4096x4096, K=4 3INST, batch 1, ring of 64 distinct matrices in one graph",
+                                 "l2": "ring of 64 x 8.4 MB = 537 MB, larger than L2"},
+                      "roofline": {"bound": "hbm", "achieved": r["gbs"], "peak": peak, "unit": "GB/s", "frac": r["gbs"] / peak,
+                                   "traffic": None, "peak_source": f"of {kind}", "kernel": "gemv_kernel"},
+                      "gpu_launches": r["ring"], "clocks": clocks.summary()}))
+
+
+def decode_sweep(dev, args) -> dict:
+    """Outside the timed region: the same captured step at 4 and 16 rows (8 layers, scaled), and every bit rate on the
+    17408 x 5120 shape at batch 1."""
+    import torch
+    from trellis_serve_b200.runtime.layerset import DecodeLayerSet
+    peak, _ = measured_peak_hbm()
+    out = {"rows": {}, "bits_17408x5120": {}}
+    layers = min(args.layers, 8)
+    for rows in (4, 16):
+        ls = DecodeLayerSet(layers, args.bits, 0, rows, device=dev, seed=900)
+        ls.capture(warmup=2)
+        for _ in range(3):
+            ls.replay()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            ls.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms_layer = e0.elapsed_time(e1) / 10 / layers
+        out["rows"][str(rows)] = {"ms_per_64_layers": ms_layer * 64, "gbs": ls.packed_bytes / layers / ms_layer / 1e6,
+                                  "frac": ls.packed_bytes / layers / ms_layer / 1e6 / peak, "layers_timed": layers}
+        del ls
+        torch.cuda.empty_cache()
+    for K in range(2, 9):
+        r = single_matrix_rate(dev, 17408, 5120, K, 1, seed=10 + K)
+        out["bits_17408x5120"][str(K)] = {"us_per_launch": r["us_per_launch"], "gbs": r["gbs"], "frac": r["gbs"] / peak}
+    return out
+
+
+def tp_check(dev, rank: int, world: int, reducer, dist) -> dict:
+    """Outside the timed region, N > 1: one row-parallel linear (17408 -> 5120, K = 3, every rank slices ITS rows out of the
+    same seeded matrix) summed three ways -- exchange fused into the kernel, the library's stand-alone all-reduce, NCCL --
+    and compared with each other and with the unsharded linear computed on every rank."""
+    import torch
+    from trellis_serve_b200.kernels import linear as lin
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    k, n, K, cb = 17408, 5120, 3, 0
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4242)                                         # the same on every rank
+    full = random_packed(k, n, K, gen, dev)                      # [n/128, k/128, ...]
+    suh = random_signs(k, gen, dev, 1)
+    svh = (random_signs(n, gen, dev).view(-1) / 64).half()
+    x = torch.randn((1, k), device=dev, generator=gen).half()
+    kg = k // 128 // world
+    shard = full[:, rank * kg:(rank + 1) * kg].contiguous()
+    xs, suhs = x[:, rank * kg * 128:(rank + 1) * kg * 128].contiguous(), suh[:, rank * kg * 128:(rank + 1) * kg * 128].contiguous()
+    torch.cuda.synchronize(dev)
+    whole = lin.run(x, full, suh, svh, [], cb).float()
+    y_fused = lin.run(xs, shard, suhs, svh, [], cb, exchange=reducer) if reducer is not None else None
+    y_peer = lin.run(xs, shard, suhs, svh, [], cb)
+    y_nccl = y_peer.clone()
+    if reducer is not None:
+        reducer(y_peer)
+    dist.all_reduce(y_nccl)
+    torch.cuda.synchronize(dev)
+    rms = float(whole.pow(2).mean().sqrt())
+    res = {"shape": f"{k}x{n} K={K}", "max_rel_nccl_vs_unsharded": float((y_nccl.float() - whole).abs().max()) / rms}
+    flags = torch.ones(2, dtype=torch.int32, device=dev)
+    if reducer is not None:
+        flags[0] = int(torch.equal(y_fused.view(torch.int16), y_peer.view(torch.int16)))
+        res["max_rel_vs_nccl"] = float((y_fused.float() - y_nccl.float()).abs().max()) / rms
+        gathered = [torch.empty_like(y_fused) for _ in range(world)]
+        dist.all_gather(gathered, y_fused)
+        flags[1] = int(all(torch.equal(g.view(torch.int16), gathered[0].view(torch.int16)) for g in gathered))
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    worst = torch.tensor([res["max_rel_nccl_vs_unsharded"], res.get("max_rel_vs_nccl", 0.0)], dtype=torch.float64, device=dev)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    res["max_rel_nccl_vs_unsharded"], worst_nccl = worst.tolist()
+    if reducer is not None:
+        res["max_rel_vs_nccl"] = worst_nccl
+        res["fused_eq_peer"] = bool(flags[0].item())
+        res["same_bits_on_every_rank"] = bool(flags[1].item())
+    del full, shard
+    torch.cuda.empty_cache()
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -265,8 +440,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "peer", "nccl"],
                     help="exchange step of row-parallel layers at N > 1: the library's one-shot peer-memory kernel, or NCCL")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
-                    help="decode = the headline 27B-shape layer set (default); prefill / moe = secondary single-GPU workloads")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe", "c1"],
+                    help="decode = the headline 27B-shape layer set (default); prefill / moe / c1 = secondary single-GPU workloads")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the batch and bit-rate sweep appended to the default line")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -278,6 +454,9 @@ def main() -> None:
         return
     if args.workload == "moe":
         run_moe(args)
+        return
+    if args.workload == "c1":
+        run_c1(args)
         return
 
     import torch
@@ -293,6 +472,10 @@ def main() -> None:
     dev = torch.device("cuda", local)
     dist = None
     if world > 1:
+        # Neither the kernels here nor the exchange use multicast or multimem: keep every library off NVLink multicast
+        # objects too (the rank processes leave without tearing the communicator down).
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     K, cb = args.bits, 0
@@ -317,14 +500,16 @@ def main() -> None:
     for _ in range(args.warmup):
         ls.replay()
     barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    block_ms = []
     with ClockSampler(local) as clocks:
-        start.record()
-        for _ in range(args.steps):
-            ls.replay()
-        stop.record()
-        barrier()
-    ms_total = start.elapsed_time(stop)
+        for _ in range(BLOCKS):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(args.steps):
+                ls.replay()
+            stop.record()
+            barrier()
+            block_ms.append(start.elapsed_time(stop))
     lin.device_error(dev)
     if reducer is not None:
         reducer.check()
@@ -335,21 +520,28 @@ def main() -> None:
     for _ in range(args.warmup):
         ls.forward_host(*hx, hy)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        ls.forward_host(*hx, hy)
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
+    e2e_ms = []
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            ls.forward_host(*hx, hy)
+        e1.record()
+        barrier()
+        e2e_ms.append(e0.elapsed_time(e1))
 
-    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    # every block: the slowest rank's time; then the median block
+    t = torch.tensor(block_ms + e2e_ms, dtype=torch.float64, device=dev)
     nbytes = torch.tensor([float(ls.packed_bytes)], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)
-    ms_total, ms_e2e = t.tolist()
+    t = t.tolist()
+    block_ms, e2e_ms = t[:BLOCKS], t[BLOCKS:]
+    ms_total, ms_e2e = statistics.median(block_ms), statistics.median(e2e_ms)
     total_bytes = nbytes.item()
+    check = tp_check(dev, rank, world, reducer, dist) if dist is not None else None
+    sweep = decode_sweep(dev, args) if (world == 1 and not args.no_sweep) else None
     if rank == 0:
         ms_step = ms_total / args.steps
         value = total_bytes / (ms_step * 1e-3) / 1e9
@@ -362,20 +554,21 @@ def main() -> None:
         # (the step also contains the small activation-rotation kernels), so `achieved` is a lower bound.
         avg_launch_ms = ms_step / gemv_launches
         achieved = per_rank_bytes / gemv_launches / (avg_launch_ms * 1e-3) / 1e9
-        # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of the captured gate|up launch
-        # (profiles/gemv_kernel_27b_k3_batch1.md: 67.015 MB + 0.458 MB for 66.847 MB of packed weights) scaled to the
-        # average launch by its units; the kernel reads every weight byte exactly once, so traffic grows with the units.
-        traffic = (67.015e6 + 0.458e6) / 66.847e6 * per_rank_bytes / gemv_launches
+        # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of one captured gate|up launch,
+        # scaled to the average launch by its units; the kernel reads every weight byte exactly once, so traffic grows
+        # with the units.
+        ratio, traffic_source = traffic_ratio()
+        traffic = ratio * per_rank_bytes / gemv_launches if ratio is not None else None
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
                 "data": "synthetic",
-                "config": {"workload": WORKLOAD, "layers": args.layers, "bits": K, "codebook": "3inst", "rows": args.rows,
-                           "parallelism": f"tp{world}", "allreduce": (args.allreduce if world > 1 else None),
-                           "l2": "inputs larger than L2, no flush",
-                           "packed_bytes_per_step": total_bytes},
+                "config": workload_config(args, world, total_bytes),
                 "tok_s": 1e3 / ms_step,
+                "timing": {"blocks": BLOCKS, "steps_per_block": args.steps, "block_ms": [round(b, 4) for b in block_ms],
+                           "reported": "median block, slowest rank per block"},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "traffic": traffic, "traffic_unit": "bytes per launch, from one ncu capture scaled by units",
+                             "traffic_source": traffic_source,
                              "peak_source": f"of {peak_kind}", "kernel": "gemv_kernel",
                              "launches_per_step": gemv_launches, "avg_launch_ms_upper_bound": avg_launch_ms},
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
@@ -383,6 +576,10 @@ def main() -> None:
                         "d2h_bytes_per_step": hy.numel() * hy.element_size(), "tok_s": 1e3 / (ms_e2e / args.steps)},
                 "gpu_launches": ls.launches_per_step * args.steps,
                 "clocks": clocks.summary()}
+        if check is not None:
+            line["tp_check"] = check
+        if sweep is not None:
+            line["sweep"] = sweep
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = {k: v for k, v in cpu_sample(K, cb).items() if k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))

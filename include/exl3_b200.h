@@ -140,6 +140,12 @@ size_t exl3_static_workspace_bytes(void);
 exl3_status exl3_gemm_rotated(const uint16_t *xh, const uint32_t *packed, int K, int codebook, const int *shard_ends,
                               int n_shards, int rows, int k, int n_total, uint16_t *out, void *workspace,
                               size_t workspace_bytes, void *stream);
+/* The same product with the fp32 accumulators stored unrounded: followed by exl3_had_out (y_dtype EXL3_F32) it is the
+ * "output transform in a launch of its own" that the fused epilogue of exl3_linear must equal bit for bit, the check of
+ * cuda/src/sglang_exl3/parity/marlin_parity.py:114-127. */
+exl3_status exl3_gemm_rotated_f32(const uint16_t *xh, const uint32_t *packed, int K, int codebook, const int *shard_ends,
+                                  int n_shards, int rows, int k, int n_total, float *out, void *workspace,
+                                  size_t workspace_bytes, void *stream);
 
 /* ---- tensor-parallel exchange step -------------------------------------------------------------------------
  * Row-parallel shards (o_proj, down_proj) produce partial sums (core/src/trellis_core/format/geometry.py:62-66); this

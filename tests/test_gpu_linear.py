@@ -93,7 +93,7 @@ def test_identity_rows_read_the_decoded_weights_out_exactly(K, cb, mode):
 
 
 def test_full_size_decode_checksum_against_the_oracle():
-    """BASELINE-size matrix (4096 x 4096, K = 4, 3INST): every decoded weight equal to the oracle's."""
+    """The 4096 x 4096, K = 4, 3INST configuration: every decoded weight equal to the oracle's."""
     K, cb = 4, 0
     tr = seeded_trellis(0, 256, 256, K)
     want = orc.c_reconstruct(tr, K, cb).view(np.uint16)
@@ -177,6 +177,26 @@ def test_fused_group_equals_its_matrices():
         single = lin.linear(_t(x), lin.prepare_matrix(_t(tr)), _t(suh), _t(svh), cb)
         assert torch.equal(single.cpu(), torch.from_numpy(y[:, col:col + n]).half())     # same bits as a lone launch
         col += n
+
+
+@pytest.mark.parametrize("rows,dtype", [(1, torch.float16), (2, torch.bfloat16), (5, torch.float16), (16, torch.bfloat16)])
+def test_output_transform_inside_the_launch_equals_a_launch_of_its_own(rows, dtype):
+    """exl3_linear (rotations fused into the GEMV where the row count allows) == exl3_had_in -> exl3_gemm_rotated_f32 ->
+    exl3_had_out, bit for bit, fp16 and bf16 (the reference's check_inlaunch, cuda/src/sglang_exl3/parity/marlin_parity.py:114-127)."""
+    K, cb, k, ns = 3, 0, 1024, [640, 384]
+    parts = [_case(1400 + i, k, n, K, rows, sign_only=False) for i, n in enumerate(ns)]
+    x = _t(parts[0][3]).to(dtype)
+    b, suh_cat, svh_cat, ends = lin.prepare([_t(p[0]) for p in parts], [_t(p[1]) for p in parts], [_t(p[2]) for p in parts])
+    fused = lin.run(x, b, suh_cat, svh_cat, ends, cb)
+    xh = lin.had_in_group(x, suh_cat)
+    rot = lin.gemm_rotated_group(xh, b, ends, cb, out=torch.empty((rows, sum(ns)), dtype=torch.float32, device=DEV))
+    apart = torch.empty((rows, sum(ns)), dtype=dtype, device=DEV)
+    col = 0
+    for n in ns:
+        lin.had_out_into(rot[:, col:col + n].contiguous(), svh_cat[col:col + n], apart, col)
+        col += n
+    torch.cuda.synchronize()
+    assert torch.equal(fused.view(torch.int16), apart.view(torch.int16))
 
 
 # ------------------------------------------------------------------------------------------------ promises

@@ -86,7 +86,7 @@ def test_layer_matches_the_float64_reference(tokens, zipf, K, cb):
 
 
 def test_config_shape_layer_batch_1_and_64():
-    """BASELINE's MoE shape scaled in expert count only: hidden 2048, intermediate 512, top-8, K = 3; 16 experts
+    """The 256-expert layer's shape scaled in expert count only: hidden 2048, intermediate 512, top-8, K = 3; 16 experts
     keep the float64 reference fast.  Batch 1 and 64."""
     E, hidden, inter, top_k, K, cb = 16, 2048, 512, 8, 3, 0
     gate, up, down = _experts(4242, E, hidden, inter, K, out_scale=1 / 32)

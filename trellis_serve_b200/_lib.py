@@ -40,6 +40,7 @@ SIGNATURES = {
     "exl3_linear_static": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp]),
     "exl3_static_workspace_bytes": (_sz, []),
     "exl3_gemm_rotated": (_i, [_vp, _vp, _i, _i, _ip, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "exl3_gemm_rotated_f32": (_i, [_vp, _vp, _i, _i, _ip, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "exl3_allreduce_region_bytes": (_sz, [_sz]),
     "exl3_allreduce": (_i, [_vp, _i, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),
     "exl3_linear_allreduce": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),

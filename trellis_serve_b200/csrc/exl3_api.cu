@@ -186,7 +186,7 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
     memset(&a, 0, sizeof(a));
     if (int rc = fill_shards(a, shard_ends, n_shards, n_total)) return rc;
     if (!rotated && x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
-    if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16 && !(y_dtype == EXL3_F32 && !rotated)) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (y_dtype != EXL3_F16 && y_dtype != EXL3_F32 && !(y_dtype == EXL3_BF16 && !rotated)) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
     if ((size_t)(n_total / 128) > WS_MAX_COUNTERS) return EXL3_ERR_BAD_SHAPE;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
@@ -288,6 +288,13 @@ exl3_status exl3_gemm_rotated(const uint16_t* xh, const uint32_t* packed, int K,
 }
 
 static void* static_workspace_of_current_device(int* status);
+
+exl3_status exl3_gemm_rotated_f32(const uint16_t* xh, const uint32_t* packed, int K, int codebook, const int* shard_ends, int n_shards,
+                                  int rows, int k, int n_total, float* out, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return linear_common(nullptr, EXL3_F16, xh, packed, K, codebook, nullptr, nullptr, shard_ends, n_shards, rows, k, n_total, out,
+                         EXL3_F32, workspace, workspace_bytes, (cudaStream_t)stream, true);
+}
 
 exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* stream)
 {

@@ -278,7 +278,7 @@ __global__ void had_out_kernel(const void* __restrict__ y, const __half* __restr
 #pragma unroll
     for (int e = 0; e < 4; e++) {
         float sv = svh ? __half2float(svh[nb * 128 + 4 * lane + e]) : 1.0f;
-        v[e] = v[e] * HAD_SCALE * sv;
+        v[e] = v[e] * (HAD_SCALE * sv);          // the same order as the epilogues fused into the GEMV kernels
     }
     store_out4(out, (long long)row * out_stride + nb * 128 + 4 * lane, v, out_bf16 != 0);
 }
@@ -310,7 +310,7 @@ __global__ void had_out_sum_kernel(const float* __restrict__ part, int parts, lo
 #pragma unroll
     for (int e = 0; e < 4; e++) {
         float sv = svh ? __half2float(svh[nb * 128 + 4 * lane + e]) : 1.0f;
-        v[e] = v[e] * HAD_SCALE * sv;
+        v[e] = v[e] * (HAD_SCALE * sv);          // the same order as the epilogues fused into the GEMV kernels
     }
     store_out4(out, base, v, out_bf16 != 0);
 }

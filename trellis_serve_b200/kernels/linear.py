@@ -281,7 +281,8 @@ def had_out_into(y: torch.Tensor, svh: torch.Tensor, out: torch.Tensor, col0: in
 
 def gemm_rotated_group(xh_all: torch.Tensor, packed: torch.Tensor, shard_ends, codebook: int,
                        out: torch.Tensor | None = None) -> torch.Tensor:
-    """Rotated-basis product of a fused group; xh_all is (shards * rows, k) fp16, slab s feeds shard s."""
+    """Rotated-basis product of a fused group; xh_all is (shards * rows, k) fp16, slab s feeds shard s.  An fp32 `out`
+    receives the accumulators unrounded."""
     _require_cuda(xh_all, "xh")
     lib = _lib.load()
     _lib.init_device(xh_all.device.index if xh_all.device.index is not None else torch.cuda.current_device())
@@ -293,10 +294,10 @@ def gemm_rotated_group(xh_all: torch.Tensor, packed: torch.Tensor, shard_ends, c
     if rows == 0:
         return out
     ws = reserve_workspace(xh_all.device, workspace_bytes(rows, k, n_total, shards))
+    fn = lib.exl3_gemm_rotated_f32 if out.dtype == torch.float32 else lib.exl3_gemm_rotated
     with torch.cuda.device(xh_all.device):
-        _lib.check(lib.exl3_gemm_rotated(_ptr(xh_all), _ptr(packed), K, codebook, _lib.int_array(shard_ends), shards, rows,
-                                         k, n_total, _ptr(out), _ptr(ws), ws.numel(), _stream(xh_all.device)),
-                   "exl3_gemm_rotated")
+        _lib.check(fn(_ptr(xh_all), _ptr(packed), K, codebook, _lib.int_array(shard_ends), shards, rows,
+                      k, n_total, _ptr(out), _ptr(ws), ws.numel(), _stream(xh_all.device)), "exl3_gemm_rotated")
     return out
 
 
