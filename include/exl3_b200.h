@@ -103,6 +103,35 @@ exl3_status exl3_linear(const void *x, int x_dtype, const uint32_t *packed, int 
                         const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
                         int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- decode step: the kernels between the linears hand the next linear its rotated input ------------------------
+ * In a decode step every EXL3 linear is preceded by an element-wise kernel (residual add + RMSNorm ahead of q|k|v and
+ * gate|up, SiLU(gate) * up ahead of down, nothing but the rotation ahead of o).  These entry points fuse the linear's input
+ * rotation into that kernel: it writes Had128(fp16(activation) * suh[s]) for every matrix s of the following fused group as
+ * tensor-core fragments into `workspace`, once, and exl3_linear_prerotated runs the group from there (up to two rows its
+ * CTAs copy the fragments of their units into shared memory with bulk copies; 3..16 rows read them tile by tile).  The
+ * fragments, and so the results, are bit-identical to exl3_linear on the same activation.  rows <= 16; the workspace is the
+ * one exl3_linear_workspace_bytes(rows, k, n_total, n_shards) sizes, shared by the whole chain in stream order.
+ * The reference runs these steps as separate kernels ahead of had_in_group_marlin (cuda/csrc/exl3_marlin.cu:283-290,
+ * group launch :507-527); the fusion has no counterpart there.
+ *   exl3_rotate_fragments   activation x [rows, k] as it is.
+ *   exl3_rmsnorm_rotate     residual (in/out, may be NULL) += x; a = rmsnorm(residual or x, eps) * weight, rounded to `dtype`;
+ *                           `normed` (may be NULL) receives a.  x, residual, weight, normed share `dtype` (fp16 / bf16).
+ *   exl3_silu_mul_rotate    a = silu(gate) * up of gate_up [rows, 2 * inter] (gate | up), rounded to `dtype`; `act` (may be
+ *                           NULL) receives a [rows, inter].
+ *   exl3_linear_prerotated  the fused group on those fragments; world > 1: row-parallel shard, summed over the ranks inside
+ *                           the kernel as exl3_linear_allreduce does (peer arguments as there; world <= 1 ignores them). */
+exl3_status exl3_rotate_fragments(const void *x, int x_dtype, const uint16_t *suh_cat, int n_shards, int rows, int k,
+                                  int codebook, void *workspace, size_t workspace_bytes, void *stream);
+exl3_status exl3_rmsnorm_rotate(const void *x, void *residual, const void *weight, float eps, int dtype,
+                                const uint16_t *suh_cat, int n_shards, int rows, int k, int codebook, void *normed,
+                                void *workspace, size_t workspace_bytes, void *stream);
+exl3_status exl3_silu_mul_rotate(const void *gate_up, int dtype, const uint16_t *suh, int rows, int inter, int codebook,
+                                 void *act, void *workspace, size_t workspace_bytes, void *stream);
+exl3_status exl3_linear_prerotated(const uint32_t *packed, int K, int codebook, const uint16_t *svh_cat, const int *shard_ends,
+                                   int n_shards, int rows, int k, int n_total, void *y, int y_dtype, void *workspace,
+                                   size_t workspace_bytes, void *const *peer_regions, int rank, int world, size_t max_elems,
+                                   int *state, void *stream);
+
 /* ---- fused linear for many rows (prefill) on the tcgen05 tensor cores -----------------------------------
  * Same contract as exl3_linear (fused group, dtypes, shard ends); built for hundreds to thousands of rows: the
  * weights are decoded once per 512 rows straight into the shared-memory operand of tcgen05.mma, accumulators live in

@@ -1,0 +1,131 @@
+"""The decode step around the linears: the fused producers (residual + RMSNorm + rotation, SiLU(gate) * up + rotation, plain
+rotation) feed exl3_linear_prerotated the same fragments a stand-alone exl3_linear builds for itself -- so results must be
+equal bit for bit -- and a small two-layer `DecodeStep` (RoPE, KV cache, attention, residuals) agrees with a float64
+restatement built on the oracle's decoder."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import exl3_oracle as orc
+from trellis_serve_b200.kernels import linear as lin
+from trellis_serve_b200.runtime.decode_step import DecodeStep, ModelShape
+from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _group(k, ns, K, seed):
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(seed)
+    packed = torch.cat([random_packed(k, n, K, gen, DEV) for n in ns])
+    suh = random_signs(k, gen, DEV, len(ns))
+    svh = (random_signs(sum(ns), gen, DEV).view(-1).float() / 32).half()
+    ends = [sum(ns[:i + 1]) for i in range(len(ns) - 1)]
+    ws = torch.zeros(lin.workspace_bytes(16, k, sum(ns), len(ns)), dtype=torch.uint8, device=DEV)
+    return packed, suh, svh, ends, ws, gen
+
+
+@pytest.mark.parametrize("rows,dtype,K,cb", [(1, torch.float16, 3, 0), (2, torch.bfloat16, 4, 1), (5, torch.float16, 3, 2), (16, torch.bfloat16, 5, 0)])
+def test_fused_producers_give_the_bits_of_the_stand_alone_linear(rows, dtype, K, cb):
+    k, ns = 1024, [640, 384]
+    packed, suh, svh, ends, ws, gen = _group(k, ns, K, 11 * rows + K)
+    x = torch.randn((rows, k), device=DEV, generator=gen).to(dtype)
+    out = torch.empty((rows, sum(ns)), dtype=dtype, device=DEV)
+    # plain rotation ahead of the linear
+    lin.rotate_fragments(x, suh, cb, ws)
+    lin.run_prerotated(rows, packed, svh, ends, cb, out, ws)
+    assert torch.equal(out.view(torch.int16), lin.run(x, packed, suh, svh, ends, cb).view(torch.int16))
+    # residual add + RMSNorm + rotation
+    res0 = torch.randn((rows, k), device=DEV, generator=gen).to(dtype)
+    weight = (1.0 + 0.1 * torch.randn(k, device=DEV, generator=gen)).to(dtype)
+    residual, normed = res0.clone(), torch.empty_like(x)
+    lin.rmsnorm_rotate(x, residual, weight, 1e-6, suh, cb, ws, normed=normed)
+    lin.run_prerotated(rows, packed, svh, ends, cb, out, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(residual, (x.float() + res0.float()).to(dtype))
+    want = torch.nn.functional.rms_norm(residual.float(), (k,), weight.float(), 1e-6)
+    assert float((normed.float() - want).abs().max()) <= (2e-2 if dtype == torch.bfloat16 else 3e-3)
+    assert torch.equal(out.view(torch.int16), lin.run(normed, packed, suh, svh, ends, cb).view(torch.int16))
+    # no residual: the input itself is normalised and stays untouched
+    x_before = x.clone()
+    lin.rmsnorm_rotate(x, None, weight, 1e-6, suh, cb, ws, normed=normed)
+    assert torch.equal(x, x_before)
+    want = torch.nn.functional.rms_norm(x.float(), (k,), weight.float(), 1e-6)
+    assert float((normed.float() - want).abs().max()) <= (2e-2 if dtype == torch.bfloat16 else 3e-3)
+    lin.device_error(DEV)
+
+
+@pytest.mark.parametrize("rows,dtype", [(1, torch.float16), (2, torch.bfloat16), (7, torch.float16)])
+def test_silu_mul_rotation_feeds_the_down_projection(rows, dtype):
+    inter, n, K, cb = 768, 512, 3, 0
+    packed, suh, svh, ends, ws, gen = _group(inter, [n], K, 90 + rows)
+    gu = torch.randn((rows, 2 * inter), device=DEV, generator=gen).to(dtype)
+    act, out = torch.empty((rows, inter), dtype=dtype, device=DEV), torch.empty((rows, n), dtype=dtype, device=DEV)
+    lin.silu_mul_rotate(gu, suh, cb, ws, act=act)
+    lin.run_prerotated(rows, packed, svh, ends, cb, out, ws)
+    want = torch.nn.functional.silu(gu[:, :inter].float()) * gu[:, inter:].float()
+    assert float((act.float() - want).abs().max()) <= (3e-2 if dtype == torch.bfloat16 else 4e-3)
+    assert torch.equal(out.view(torch.int16), lin.run(act, packed, suh, svh, ends, cb).view(torch.int16))
+
+
+def _ref_linear(x64, packed, suh, svh, K, cb, col0, n):
+    """float64 forward of columns [col0, col0 + n) of a fused group on the oracle's decoded weights."""
+    tr = lin.unprepare_matrix(packed[col0 // 128:(col0 + n) // 128].contiguous()).cpu().numpy().view(np.uint16)
+    return orc.np_linear_forward(x64, tr, suh.cpu().numpy().astype(np.float64), svh[col0:col0 + n].cpu().numpy().astype(np.float64), K, cb,
+                                 np.float64, reconstruct=orc.c_reconstruct)
+
+
+def test_two_layer_decode_step_against_a_float64_restatement():
+    shape = ModelShape(hidden=256, q_heads=2, kv_heads=1, head_dim=128, ffn=512, layers=2)
+    K, cb, ctx = 4, 1, 24
+    step = DecodeStep(shape, K, cb, ctx, rows=1, device=DEV, seed=77)
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(5)
+    step.h_in.copy_(torch.randn((1, shape.hidden), device=DEV, generator=gen).half())
+    kv0 = step.kv.clone()
+    eager = step.step().clone()
+    step.kv.copy_(kv0)
+    step.capture()
+    step.kv.copy_(kv0)
+    replayed = step.replay().clone()
+    torch.cuda.synchronize()
+    lin.device_error(DEV)
+    assert torch.equal(eager, replayed)
+
+    def rms(v, w):
+        return v / np.sqrt((v ** 2).mean(-1, keepdims=True) + shape.eps) * w
+
+    def rope(t, heads):
+        x = t.reshape(1, heads, shape.head_dim)
+        c, s = step.cos.double().cpu().numpy(), step.sin.double().cpu().numpy()
+        x1, x2 = x[..., :64], x[..., 64:]
+        return np.concatenate([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+    h = step.h_in.double().cpu().numpy()
+    residual = np.zeros_like(h)
+    q, kv, f = shape.q_out, shape.kv_out, shape.ffn
+    for i, (qkv, o, gu, down, norms) in enumerate(step.layers):
+        nw = norms.double().cpu().numpy()
+        residual = residual + h
+        a = rms(residual, nw[0])
+        y = np.concatenate([_ref_linear(a, qkv.packed, qkv.suh[j], qkv.svh, K, cb, c0, w) for j, (c0, w) in enumerate([(0, q), (q, kv), (q + kv, kv)])], 1)
+        qh, kh, vh = rope(y[:, :q], shape.q_heads), rope(y[:, q:q + kv], shape.kv_heads), y[:, q + kv:].reshape(1, 1, 128)
+        kc, vc = kv0[i, 0, 0].double().cpu().numpy().copy(), kv0[i, 1, 0].double().cpu().numpy().copy()      # [kv heads, ctx + 1, d]
+        kc[:, ctx], vc[:, ctx] = kh[0], vh[0]
+        att = np.zeros((1, shape.q_heads, 128))
+        for hd in range(shape.q_heads):
+            sc = kc[0] @ qh[0, hd] / np.sqrt(128.0)
+            p = np.exp(sc - sc.max())
+            att[0, hd] = (p / p.sum()) @ vc[0]
+        oo = _ref_linear(att.reshape(1, q), o.packed, o.suh[0], o.svh, K, cb, 0, shape.hidden)
+        residual = residual + oo
+        a = rms(residual, nw[1])
+        g = np.concatenate([_ref_linear(a, gu.packed, gu.suh[j], gu.svh, K, cb, j * f, f) for j in range(2)], 1)
+        act = g[:, :f] / (1 + np.exp(-g[:, :f])) * g[:, f:]
+        h = _ref_linear(act, down.packed, down.suh[0], down.svh, K, cb, 0, shape.hidden)
+    want = rms(residual + h, step.final_norm.double().cpu().numpy())
+    got = eager.double().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert orc.rel_norm(got, want) <= 1.5e-2, orc.rel_norm(got, want)

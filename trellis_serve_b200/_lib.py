@@ -35,6 +35,10 @@ SIGNATURES = {
     "exl3_had_out": (_i, [_vp, _i, _vp, _i, _i, _vp, _i64, _i, _vp]),
     "exl3_linear_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_linear": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "exl3_rotate_fragments": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "exl3_rmsnorm_rotate": (_i, [_vp, _vp, _vp, ctypes.c_float, _i, _vp, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "exl3_silu_mul_rotate": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "exl3_linear_prerotated": (_i, [_vp, _i, _i, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),
     "exl3_gemm_tc_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_linear_tc": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "exl3_linear_static": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp]),

@@ -178,20 +178,22 @@ size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards)
 static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor, const uint32_t* packed, int K, int codebook,
                          const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k,
                          int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated,
-                         const TpExchange* tp = nullptr)
+                         const TpExchange* tp = nullptr, bool prerotated = false)
 {
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (rows < 0) return EXL3_ERR_BAD_SHAPE;
     GemvArgs a;
     memset(&a, 0, sizeof(a));
     if (int rc = fill_shards(a, shard_ends, n_shards, n_total)) return rc;
-    if (!rotated && x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (!rotated && !prerotated && x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (prerotated && rows > GEMV_MAX_ROWS) return EXL3_ERR_UNSUPPORTED_ROWS;
     if (y_dtype != EXL3_F16 && y_dtype != EXL3_F32 && !(y_dtype == EXL3_BF16 && !rotated)) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
     if ((size_t)(n_total / 128) > WS_MAX_COUNTERS) return EXL3_ERR_BAD_SHAPE;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
     if (!aligned(packed, 16) || !aligned(y, 16)) return EXL3_ERR_BAD_POINTER;
-    if (rotated ? !aligned(xh_rowmajor, 2) : (!aligned(x, 2) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8)))
+    if (prerotated ? !aligned(svh_cat, 8)
+                   : rotated ? !aligned(xh_rowmajor, 2) : (!aligned(x, 2) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8)))
         return EXL3_ERR_BAD_POINTER;
     const WorkspaceLayout wl = workspace_layout(rows, k, n_total, n_shards);
     if (!aligned(workspace, 256) || workspace_bytes < wl.total) return EXL3_ERR_WORKSPACE;
@@ -217,7 +219,13 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
         a.rows = r;
         a.out = reinterpret_cast<unsigned char*>(y) + (size_t)r0 * n_total * osz;
         int rc;
-        if (rotated) {
+        if (prerotated) {
+            // The fragments are in the workspace already (exl3_rotate_fragments, exl3_rmsnorm_rotate, exl3_silu_mul_rotate):
+            // up to two rows the kernel copies those of its units into shared memory once, else it reads them tile by tile.
+            a.x = nullptr;
+            a.xf_staged = 1;
+            if (!gemv_rotates_input(a)) a.xf_staged = 0;
+        } else if (rotated) {
             // shard s reads slab s of xh: rows [s*rows + r0, s*rows + r0 + r)
             for (int s = 0; s < n_shards; s++) {
                 const __half* src = reinterpret_cast<const __half*>(xh_rowmajor) + ((size_t)s * rows + r0) * k;
@@ -313,6 +321,88 @@ exl3_status exl3_device_error(void* workspace, size_t workspace_bytes, void* str
     if (code == 0) return EXL3_OK;
     if (int rc = cuda_status(cudaMemsetAsync(workspace, 0, sizeof(int), st))) return rc;
     return EXL3_ERR_DEVICE_WAIT;
+}
+
+/* ---- decode step: rotated fragments written by the kernel ahead of the linear -------------------------------------- */
+
+static int fragment_mode(int codebook) { return gemv_default_mode(codebook) == GEMV_SPLIT ? 1 : 2; }
+
+static int fragment_region(int rows, int k, int n_shards, void* workspace, size_t workspace_bytes, uint32_t** xf)
+{
+    if (rows < 0 || rows > GEMV_MAX_ROWS) return EXL3_ERR_UNSUPPORTED_ROWS;
+    if (k < 0 || (k % 128) || n_shards < 1 || n_shards > GEMV_MAX_SHARDS) return EXL3_ERR_BAD_SHAPE;
+    const WorkspaceLayout wl = workspace_layout(rows, k, 128, n_shards);
+    if (!aligned(workspace, 256) || workspace_bytes < wl.partials_off) return EXL3_ERR_WORKSPACE;
+    *xf = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(workspace) + wl.xf_off);
+    return EXL3_OK;
+}
+
+exl3_status exl3_rotate_fragments(const void* x, int x_dtype, const uint16_t* suh_cat, int n_shards, int rows, int k, int codebook,
+                                  void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    uint32_t* xf = nullptr;
+    if (int rc = fragment_region(rows, k, n_shards, workspace, workspace_bytes, &xf)) return rc;
+    if (rows == 0 || k == 0) return EXL3_OK;
+    if (!aligned(x, 2) || !aligned(suh_cat, 8)) return EXL3_ERR_BAD_POINTER;
+    return launch_had_in(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, rows, k, xf, fragment_mode(codebook),
+                         (cudaStream_t)stream);
+}
+
+exl3_status exl3_rmsnorm_rotate(const void* x, void* residual, const void* weight, float eps, int dtype, const uint16_t* suh_cat,
+                                int n_shards, int rows, int k, int codebook, void* normed, void* workspace, size_t workspace_bytes,
+                                void* stream)
+{
+    if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    uint32_t* xf = nullptr;
+    if (int rc = fragment_region(rows, k, n_shards, workspace, workspace_bytes, &xf)) return rc;
+    if (rows == 0 || k == 0) return EXL3_OK;
+    if (!aligned(x, 8) || !aligned(weight, 2) || !aligned(suh_cat, 8) || (residual && !aligned(residual, 8)) || (normed && !aligned(normed, 8)))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_rmsnorm_rotate(x, residual, weight, eps, dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, rows, k,
+                                 normed, xf, fragment_mode(codebook), (cudaStream_t)stream);
+}
+
+exl3_status exl3_silu_mul_rotate(const void* gate_up, int dtype, const uint16_t* suh, int rows, int inter, int codebook, void* act,
+                                 void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+    uint32_t* xf = nullptr;
+    if (int rc = fragment_region(rows, inter, 1, workspace, workspace_bytes, &xf)) return rc;
+    if (rows == 0 || inter == 0) return EXL3_OK;
+    if (!aligned(gate_up, 2) || !aligned(suh, 8) || (act && !aligned(act, 8))) return EXL3_ERR_BAD_POINTER;
+    return launch_silu_mul_rotate(gate_up, dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh), rows, inter, act, xf,
+                                  fragment_mode(codebook), (cudaStream_t)stream);
+}
+
+exl3_status exl3_linear_prerotated(const uint32_t* packed, int K, int codebook, const uint16_t* svh_cat, const int* shard_ends,
+                                   int n_shards, int rows, int k, int n_total, void* y, int y_dtype, void* workspace,
+                                   size_t workspace_bytes, void* const* peer_regions, int rank, int world, size_t max_elems, int* state,
+                                   void* stream)
+{
+    if (world <= 1)
+        return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
+                             y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, true);
+    if (world > TP_MAX_WORLD || rank < 0 || rank >= world) return EXL3_ERR_BAD_SHAPE;
+    if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    const size_t slot_bytes = (max_elems * 4 + 255) & ~(size_t)255;
+    if ((size_t)(rows < 0 ? 0 : rows) * (size_t)(n_total < 0 ? 0 : n_total) > max_elems || slot_bytes > 0xFFFFFFFFu) return EXL3_ERR_BAD_SHAPE;
+    if (!peer_regions || !state || !aligned(state, 4)) return EXL3_ERR_BAD_POINTER;
+    TpExchange tp;
+    memset(&tp, 0, sizeof(tp));
+    for (int r = 0; r < world; r++) {
+        if (!aligned(peer_regions[r], 256)) return EXL3_ERR_BAD_POINTER;
+        tp.base[r] = reinterpret_cast<unsigned char*>(peer_regions[r]);
+    }
+    tp.rank = rank;
+    tp.world = world;
+    tp.slot_bytes = (unsigned int)slot_bytes;
+    tp.state = state;
+    return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
+                         y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, true);
 }
 
 /* ---- many-row (prefill) fused GEMM on tcgen05 ------------------------------------------------------------- */

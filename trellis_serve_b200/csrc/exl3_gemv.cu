@@ -113,7 +113,7 @@ static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLau
 bool gemv_rotates_input(const GemvArgs& a)
 {
     const DeviceInfo* d = current_device_info();
-    if (!d || !a.x || !a.suh || a.rotated || a.rows < 1 || a.rows > GEMV_FUSED_ROWS) return false;
+    if (!d || (a.x ? !a.suh : !a.xf_staged) || a.rotated || a.rows < 1 || a.rows > GEMV_FUSED_ROWS) return false;
     if (a.k < 128 || a.n_total < 128) return false;
     GemvLaunch l;
     size_t smem;
@@ -130,7 +130,7 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st)
     if (units >= (1ll << 31)) return EXL3_ERR_BAD_SHAPE;
     GemvLaunch l;
     size_t smem = 0;
-    if (int rc = plan_gemv(a, d, a.x != nullptr, l, smem)) return rc;
+    if (int rc = plan_gemv(a, d, a.x != nullptr || a.xf_staged, l, smem)) return rc;
 #ifdef EXL3_TIMELINE
     if (!g_tl_base) cudaGetSymbolAddress(reinterpret_cast<void**>(&g_tl_base), g_timeline);
     l.tl = g_tl_base + (size_t)(g_tl_next_slot++ % TL_SLOTS) * TL_CTAS * TL_POINTS;

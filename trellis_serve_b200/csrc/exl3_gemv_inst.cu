@@ -34,7 +34,7 @@ static int set_attr(int max_smem)
 template <int K, int MODE, int FAM>
 static int launch_variant(const GemvLaunch& l, size_t smem, cudaStream_t st)
 {
-    if (l.a.x) {                                  // the kernel rotates the input itself
+    if (l.a.x || l.a.xf_staged) {                 // the kernel rotates the input itself, or stages ready-made fragments
         if (l.a.rows == 1) return launch_one<K, MODE, FAM, 1, 1>(l, smem, st);
         if (l.a.rows == 2) return launch_one<K, MODE, FAM, 1, 2>(l, smem, st);
         return EXL3_ERR_UNSUPPORTED_ROWS;

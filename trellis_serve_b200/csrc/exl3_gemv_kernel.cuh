@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     int* released = reinterpret_cast<int*>(smem + GEMV_MAX_STAGES * 8);           // per stage: warps that are done with it
     int* flag = reinterpret_cast<int*>(smem + 2 * GEMV_MAX_STAGES * 8);          // [0] last-arriver flag, [1] abort
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + 2 * GEMV_MAX_STAGES * 8 + 16);   // staged fragments have landed
     float* P = reinterpret_cast<float*>(smem + 256);                              // [16][128]
     unsigned char* stage0 = smem + 256 + GEMV_MAX_ROWS * 128 * 4;
 
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         }
         flag[0] = 0;
         flag[1] = 0;
+        if constexpr (XR > 0) ptx::mbar_init(xbar, 1);
         ptx::mbar_fence_init();
         // Weights are constants: the first lap of copies starts before the kernel ahead of this one has finished.
         for (int j = 0; j < p.stages && j < n_fills; j++) issue_fill(j, j);
@@ -261,10 +263,33 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         unsigned char* xs = smem + p.xs_off;
         uint32_t* slots = reinterpret_cast<uint32_t*>(xs + GEMV_XS_ZERO_BYTES);
         if (threadIdx.x < GEMV_XS_ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xs)[threadIdx.x] = 0u;
+        bool waited = false;
+        if (p.a.xf_staged) {
+            // The kernel ahead in the stream (a normalisation, an activation, a plain rotation) has written the fragments
+            // of every (shard, row block) once; this CTA copies those of its units into its slots: units are consecutive
+            // row blocks of a column block, so one bulk copy per column block touched.
+            ptx::grid_dependency_wait();
+            EXL3_STAMP(1);
+            if (threadIdx.x == 0) {
+                ptx::mbar_arrive_expect_tx(xbar, (uint32_t)(u1 - u0) * XS_SLOT);
+                int u = (int)u0;
+                while (u < (int)u1) {
+                    const int unb = u / p.KG, ukg = u - unb * p.KG;
+                    int n = p.KG - ukg;
+                    if (n > (int)u1 - u) n = (int)u1 - u;
+                    int s = 0;
+                    while (s < p.a.n_shards - 1 && unb >= p.a.shard_end_blocks[s]) s++;
+                    ptx::bulk_g2s(slots + (size_t)(u - (int)u0) * (XS_SLOT / 4), p.a.xf + s * p.xf_shard_stride + (long long)ukg * (XS_SLOT / 4),
+                                  (uint32_t)n * XS_SLOT, xbar);
+                    u += n;
+                }
+            }
+            if (!ptx::mbar_wait(xbar, 0) && lane == 0) atomicExch(p.a.err, GEMV_ERR_FULL_WAIT);
+            waited = true;
+        } else {
         const int items = (int)(u1 - u0) * XR;
         const bool bf16 = p.a.x_bf16 != 0;
         constexpr int BATCH = 3;                      // rotations in flight per warp: their loads overlap
-        bool waited = false;
         for (int it0 = warp; it0 < items; it0 += GEMV_CONSUMER_WARPS * BATCH) {
             float v[BATCH][4];
             long long xi[BATCH];
@@ -323,6 +348,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                     }
                 }
             }
+        }
         }
         if (!waited) ptx::grid_dependency_wait();
         ptx::named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);

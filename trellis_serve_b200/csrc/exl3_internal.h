@@ -64,6 +64,8 @@ struct GemvArgs {
     const void* x;              // in-kernel rotation (rows <= 2): raw activations [rows, k], else nullptr
     const __half* suh;          //   and the input sign vectors [n_shards][k]
     int x_bf16;
+    int xf_staged;              // rows <= 2 without x: the fragments in xf are copied to shared memory once (bulk copies)
+                                //   instead of being read from global memory tile by tile
     const __half* svh;          // [n_total]; unused when rotated
     void* out;                  // [rows, n_total]
     float* partials;            // [(grid + NB)][rows][128]
@@ -98,6 +100,12 @@ int launch_moe_glu_had_in(const __half* gu, const __half* suh2, int inter, int n
                           const int* expert_ids, const int* num_post, uint32_t* xf, int mode, cudaStream_t st);
 int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, int tokens, int top_k, int hidden, int E, void* y,
                        int y_bf16, cudaStream_t st);
+
+// exl3_step.cu ------------------------------------------------------------------------------------------
+int launch_rmsnorm_rotate(const void* x, void* residual, const void* weight, float eps, int bf16, const __half* suh, int shards, int rows,
+                          int k, void* normed, uint32_t* xf, int mode, cudaStream_t st);
+int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows, int inter, void* act, uint32_t* xf, int mode,
+                           cudaStream_t st);
 
 // exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
 int gemm_tc_init_device();

@@ -227,6 +227,77 @@ def run_tc(x: torch.Tensor, b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: tor
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# Decode step: the kernel ahead of a linear writes the linear's rotated input (residual / normalisation / activation fused
+# with the input rotation), the linear runs from those fragments.  All four share one workspace in stream order.
+
+def _step_workspace(device: torch.device, rows: int, k: int, shards: int, workspace: torch.Tensor) -> torch.Tensor:
+    """The chain's workspace is the caller's (zero-filled once, `workspace_bytes` of the largest group): the fragments one
+    call leaves there are what the next call reads, so no call may swap the buffer for a larger one on its own."""
+    if workspace is None:
+        raise RuntimeError("the decode-step calls share one caller-owned workspace: pass it to every call of the chain")
+    _lib.init_device(device.index if device.index is not None else torch.cuda.current_device())
+    return _own_or_given(workspace, device, workspace_bytes(rows, k, 128, shards), _workspace)
+
+
+def rotate_fragments(x: torch.Tensor, suh_cat: torch.Tensor, codebook: int, workspace: torch.Tensor) -> None:
+    """Fragments of Had128(fp16(x) * suh[s]) for every matrix s of the following group, into the workspace."""
+    _require_cuda(x, "x")
+    rows, k = x.shape
+    shards = suh_cat.numel() // k
+    ws = _step_workspace(x.device, rows, k, shards, workspace)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().exl3_rotate_fragments(_ptr(x), _dtype_code(x), _ptr(suh_cat), shards, rows, k, codebook, _ptr(ws),
+                                                     ws.numel(), _stream(x.device)), "exl3_rotate_fragments")
+
+
+def rmsnorm_rotate(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float, suh_cat: torch.Tensor,
+                   codebook: int, workspace: torch.Tensor, normed: torch.Tensor | None = None) -> None:
+    """residual += x (in place, when given); a = rmsnorm(residual or x) * weight; fragments of a for the following group;
+    `normed` receives a when given.  All tensors share x's dtype (fp16 / bf16)."""
+    _require_cuda(x, "x")
+    rows, k = x.shape
+    shards = suh_cat.numel() // k
+    ws = _step_workspace(x.device, rows, k, shards, workspace)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().exl3_rmsnorm_rotate(_ptr(x), _ptr(residual), _ptr(weight), float(eps), _dtype_code(x), _ptr(suh_cat), shards,
+                                                   rows, k, codebook, _ptr(normed), _ptr(ws), ws.numel(), _stream(x.device)),
+                   "exl3_rmsnorm_rotate")
+
+
+def silu_mul_rotate(gate_up: torch.Tensor, suh: torch.Tensor, codebook: int, workspace: torch.Tensor,
+                    act: torch.Tensor | None = None) -> None:
+    """a = silu(gate) * up of gate_up [rows, 2 * inter]; fragments of a for the following (down) matrix."""
+    _require_cuda(gate_up, "gate_up")
+    rows, two = gate_up.shape
+    inter = two // 2
+    ws = _step_workspace(gate_up.device, rows, inter, 1, workspace)
+    with torch.cuda.device(gate_up.device):
+        _lib.check(_lib.load().exl3_silu_mul_rotate(_ptr(gate_up), _dtype_code(gate_up), _ptr(suh), rows, inter, codebook, _ptr(act),
+                                                    _ptr(ws), ws.numel(), _stream(gate_up.device)), "exl3_silu_mul_rotate")
+
+
+def run_prerotated(rows: int, b: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int], codebook: int, out: torch.Tensor,
+                   workspace: torch.Tensor, exchange=None) -> torch.Tensor:
+    """The fused group on the fragments the kernel ahead left in the workspace; `out` [rows, n_total] fp16 / bf16 (fp32:
+    unrounded accumulators).  `exchange`: row-parallel shard, summed over the ranks inside the kernel."""
+    lib = _lib.load()
+    _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
+    k, n_total, K = _geometry(b)
+    shards = len(shard_ends) + 1
+    if workspace is None:
+        raise RuntimeError("run_prerotated reads the fragments from the workspace the producing call wrote: pass that workspace")
+    ws = _own_or_given(workspace, b.device, workspace_bytes(rows, k, n_total, shards), _workspace)
+    ex = exchange if exchange is not None and exchange.world > 1 else None
+    with torch.cuda.device(b.device):
+        _lib.check(lib.exl3_linear_prerotated(_ptr(b), K, codebook, _ptr(svh_cat), _lib.int_array(shard_ends), shards, rows, k, n_total,
+                                              _ptr(out), _dtype_code(out, True), _ptr(ws), ws.numel(),
+                                              ex.peer_regions if ex else None, ex.rank if ex else 0, ex.world if ex else 1,
+                                              ex.max_elems if ex else 0, _ptr(ex.state) if ex else None, _stream(b.device)),
+                   "exl3_linear_prerotated")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # Building blocks (caller-owned buffers, rotated-basis product for reading decoded weights out, single matrices)
 
 def reconstruct(trellis: torch.Tensor, codebook: int) -> torch.Tensor:

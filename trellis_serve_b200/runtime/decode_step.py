@@ -1,0 +1,190 @@
+"""One decoded token through a dense transformer of EXL3 linears: the step either side of the kernels.
+
+    per layer:  residual += h;  a = RMSNorm(residual)          -> fused with the input rotation of q|k|v   (rmsnorm_rotate)
+                q|k|v = EXL3(a);  RoPE(q, k);  KV cache append;  attention over the cache
+                o = EXL3(attention)                             -> rotation launch, then the GEMV
+                residual += o;  a = RMSNorm(residual)           -> fused with the input rotation of gate|up
+                g|u = EXL3(a);  act = SiLU(g) * u               -> fused with the input rotation of down    (silu_mul_rotate)
+                h = EXL3(act)
+
+Every linear is ONE decode-GEMV launch whose activations were rotated by the kernel ahead of it; rotary embedding, cache
+append and attention are stock torch (`scaled_dot_product_attention`): they are not part of the quantized-linear path and
+their bytes (the KV read) are reported separately.  The whole step is captured in one CUDA graph, as an engine captures
+it (cuda/src/sglang_exl3/sglang_glue/moe.py:202-213 warms for that purpose; cuda/src/sglang_exl3/tools/decode_microbench.py
+:27-41 times launches the same way).
+
+Tensor parallelism: query and KV heads are split over the ranks (with more ranks than KV heads every head is held by
+several ranks: format/geometry.py `kv_shard_index`), q|k|v and gate|up by columns, o and down by rows with the exchange
+fused into their GEMV (or NCCL).  Weights are random (uniform trellis bits, +-1 sign vectors scaled so that activations
+stay in range); the step exists to be timed and to be checked against a float64 restatement, not to produce language.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..format import kv_shard_index
+from ..kernels import linear as lin
+from .layerset import random_packed, random_signs
+
+
+@dataclass(frozen=True)
+class ModelShape:
+    hidden: int = 5120
+    q_heads: int = 40
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 17408
+    layers: int = 64
+    rope_theta: float = 1.0e6
+    eps: float = 1.0e-6
+
+    @property
+    def q_out(self) -> int:
+        return self.q_heads * self.head_dim
+
+    @property
+    def kv_out(self) -> int:
+        return self.kv_heads * self.head_dim
+
+    def packed_bytes_per_layer(self, K: int) -> int:
+        weights = self.hidden * (self.q_out + 2 * self.kv_out) + self.q_out * self.hidden + 3 * self.hidden * self.ffn
+        return weights * K // 8
+
+    def kv_bytes_per_token(self, context: int, dtype_bytes: int = 2) -> int:
+        """Bytes of keys and values one decoded token reads (all layers, all KV heads)."""
+        return self.layers * 2 * self.kv_heads * self.head_dim * context * dtype_bytes
+
+
+@dataclass
+class _Lin:
+    packed: torch.Tensor
+    suh: torch.Tensor
+    svh: torch.Tensor
+    ends: list
+
+
+class DecodeStep:
+    """Random-initialised dense transformer of `shape` at `K` bits, one tensor-parallel rank of `tp_size`."""
+
+    def __init__(self, shape: ModelShape, K: int, codebook: int, context: int, rows: int = 1, tp_rank: int = 0, tp_size: int = 1,
+                 device="cuda:0", dtype: torch.dtype = torch.float16, seed: int = 400, exchange=None, group=None):
+        self.shape, self.K, self.codebook, self.context, self.rows = shape, K, codebook, context, rows
+        self.tp_rank, self.tp_size, self.exchange, self.group = tp_rank, tp_size, exchange, group
+        self.device, self.dtype = torch.device(device), dtype
+        s, dev, tp = shape, self.device, tp_size
+        if s.q_heads % tp or s.ffn % tp or (s.ffn // tp) % 128 or (s.q_out // tp) % 128:
+            raise ValueError(f"{s.q_heads} query heads / ffn {s.ffn} cannot be split over {tp} ranks at 128-aligned boundaries")
+        kv_index, kv_parts = kv_shard_index(tp, tp_rank, s.kv_heads)
+        self.q_heads, self.kv_heads = s.q_heads // tp, s.kv_heads // kv_parts
+        q, kv, f, h = self.q_heads * s.head_dim, self.kv_heads * s.head_dim, s.ffn // tp, s.hidden
+        gen = torch.Generator(device=dev)
+        scale = lambda n, k: (random_signs(n, gen, dev).view(-1).float() * (1.0 / (1.2437 * math.sqrt(k)))).half()
+        self.layers = []
+        for layer in range(s.layers):
+            gen.manual_seed(seed + layer * 1000 + tp_rank)
+            qkv = _Lin(torch.cat([random_packed(h, w, K, gen, dev) for w in (q, kv, kv)]), random_signs(h, gen, dev, 3),
+                       scale(q + 2 * kv, h), [q, q + kv])
+            o = _Lin(random_packed(q, h, K, gen, dev), random_signs(q, gen, dev, 1), scale(h, s.q_out), [])
+            gu = _Lin(torch.cat([random_packed(h, f, K, gen, dev) for _ in range(2)]), random_signs(h, gen, dev, 2), scale(2 * f, h), [f])
+            down = _Lin(random_packed(f, h, K, gen, dev), random_signs(f, gen, dev, 1), scale(h, s.ffn), [])
+            norms = (1.0 + 0.1 * torch.randn((2, h), device=dev, generator=gen)).to(dtype)
+            self.layers.append((qkv, o, gu, down, norms))
+        self.final_norm = torch.ones(h, dtype=dtype, device=dev)
+        self.workspace = torch.zeros(max(lin.workspace_bytes(rows, k_, n_, sh) for k_, n_, sh in
+                                         ((h, q + 2 * kv, 3), (q, h, 1), (h, 2 * f, 2), (f, h, 1))), dtype=torch.uint8, device=dev)
+        # KV cache [layer][2][rows, kv heads, context + 1, head_dim]: `context` past positions (random) and one new slot
+        self.kv = (torch.randn((s.layers, 2, rows, self.kv_heads, context + 1, s.head_dim), device=dev, generator=gen) * 0.5).to(dtype)
+        pos = torch.tensor([float(context)], device=dev)
+        inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, device=dev).float() / s.head_dim))
+        ang = pos[:, None] * inv[None, :]
+        self.cos, self.sin = torch.cos(ang).to(dtype), torch.sin(ang).to(dtype)          # [1, head_dim / 2]
+        # activations of the chain (static: the captured graph sees fixed addresses)
+        mk = lambda w: torch.empty((rows, w), dtype=dtype, device=dev)
+        self.h_in = torch.zeros((rows, h), dtype=dtype, device=dev)          # the step's input: the token's embedding
+        self.h, self.residual = mk(h), mk(h)
+        self.qkv, self.attn, self.o_out, self.gu, self.out = mk(q + 2 * kv), mk(q), mk(h), mk(2 * f), mk(h)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.linear_launches = s.layers * 4
+        self.fused_launches = s.layers * 4            # rmsnorm_rotate x2, rotation ahead of o, silu_mul_rotate
+
+    # ---- bytes
+    @property
+    def packed_bytes(self) -> int:
+        return sum(l.packed.numel() * 4 for layer in self.layers for l in layer[:4])
+
+    @property
+    def kv_bytes(self) -> int:
+        """Key and value bytes this rank reads per step."""
+        return self.shape.layers * 2 * self.rows * self.kv_heads * self.context * self.shape.head_dim * self.kv.element_size()
+
+    # ---- the step
+    def _rope(self, t: torch.Tensor, heads: int) -> torch.Tensor:
+        x = t.view(self.rows, heads, self.shape.head_dim)
+        x1, x2 = x[..., : self.shape.head_dim // 2], x[..., self.shape.head_dim // 2:]
+        return torch.cat([x1 * self.cos - x2 * self.sin, x2 * self.cos + x1 * self.sin], dim=-1)
+
+    def _attention(self, layer: int) -> None:
+        s, q, kv = self.shape, self.q_heads * self.shape.head_dim, self.kv_heads * self.shape.head_dim
+        qh = self._rope(self.qkv[:, :q], self.q_heads).unsqueeze(2)                        # [rows, q heads, 1, d]
+        kh = self._rope(self.qkv[:, q:q + kv], self.kv_heads)
+        vh = self.qkv[:, q + kv:].view(self.rows, self.kv_heads, s.head_dim)
+        cache = self.kv[layer]
+        cache[0][:, :, self.context] = kh
+        cache[1][:, :, self.context] = vh
+        y = torch.nn.functional.scaled_dot_product_attention(qh, cache[0], cache[1], enable_gqa=self.q_heads != self.kv_heads)
+        self.attn.copy_(y.reshape(self.rows, q))
+
+    def _reduce(self, t: torch.Tensor) -> None:
+        if self.tp_size > 1 and self.exchange is None:
+            torch.distributed.all_reduce(t, group=self.group)
+
+    def step(self) -> torch.Tensor:
+        """One token through all layers on the current stream; returns the final normalised hidden state."""
+        cb, ws, ex, rows = self.codebook, self.workspace, self.exchange, self.rows
+        self.residual.zero_()
+        h = self.h_in
+        for i, (qkv, o, gu, down, norms) in enumerate(self.layers):
+            lin.rmsnorm_rotate(h, self.residual, norms[0], self.shape.eps, qkv.suh, cb, ws)
+            lin.run_prerotated(rows, qkv.packed, qkv.svh, qkv.ends, cb, self.qkv, ws)
+            self._attention(i)
+            lin.rotate_fragments(self.attn, o.suh, cb, ws)
+            lin.run_prerotated(rows, o.packed, o.svh, o.ends, cb, self.o_out, ws, exchange=ex)
+            self._reduce(self.o_out)
+            lin.rmsnorm_rotate(self.o_out, self.residual, norms[1], self.shape.eps, gu.suh, cb, ws)
+            lin.run_prerotated(rows, gu.packed, gu.svh, gu.ends, cb, self.gu, ws)
+            lin.silu_mul_rotate(self.gu, down.suh, cb, ws)
+            lin.run_prerotated(rows, down.packed, down.svh, down.ends, cb, self.h, ws, exchange=ex)
+            self._reduce(self.h)
+            h = self.h
+        self.out.copy_(torch.nn.functional.rms_norm((self.residual + h).float(), (self.shape.hidden,), self.final_norm.float(),
+                                                    self.shape.eps).to(self.dtype))
+        return self.out
+
+    def capture(self, warmup: int = 2) -> None:
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.step()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step()
+
+    def replay(self) -> torch.Tensor:
+        if self.graph is None:
+            self.capture()
+        self.graph.replay()
+        return self.out
+
+    def forward_host(self, embedding: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """End to end with host buffers: the token's embedding (pinned) in, the final hidden state (pinned) out."""
+        self.h_in.copy_(embedding, non_blocking=True)
+        y = self.replay()
+        out.copy_(y, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out
