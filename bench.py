@@ -380,6 +380,87 @@ def decode_sweep(dev, args) -> dict:
     return out
 
 
+def decode_step_rate(dev, args, rank: int, world: int, reducer, dist, layers: int | None = None, context: int = 2048) -> dict:
+    """The whole decode step of the 27B-shape transformer (64 layers, 40 query / 8 KV heads of 128, FFN 17408, K bits,
+    `context` cached tokens in fp16, batch 1): RMSNorm, q|k|v, RoPE, attention over the cache, o, residual, RMSNorm,
+    gate|up, SiLU * up, down, captured in one CUDA graph.  tok/s of the step, the share of the EXL3 linears (the same
+    graph without the attention part is not separable, so the linears are timed as their own captured chain) and the
+    key / value bytes a token reads."""
+    import torch
+    from trellis_serve_b200.runtime.decode_step import DecodeStep, ModelShape
+    shape = ModelShape(layers=layers or args.layers)
+    step = DecodeStep(shape, args.bits, 0, context, rows=1, tp_rank=rank, tp_size=world, device=dev, exchange=reducer)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    step.h_in.copy_(torch.randn(step.h_in.shape, device=dev, generator=gen).to(step.dtype))
+    step.capture(warmup=2)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    ms = timed(step.replay, 20)
+    hin = torch.randn(step.h_in.shape).to(step.dtype).pin_memory()
+    hout = torch.empty(step.out.shape, dtype=step.dtype).pin_memory()
+    ms_e2e = timed(lambda: step.forward_host(hin, hout), 20)
+    finite = bool(torch.isfinite(step.out).all().item())
+    peak, kind = measured_peak_hbm()
+    res = {"workload": f"27B-shape transformer decode, {shape.layers} layers, K={args.bits} 3INST, {context}-token fp16 KV, batch 1, tp{world}",
+           "ms_per_token": ms, "tok_s": 1e3 / ms, "e2e_ms_per_token": ms_e2e, "e2e_tok_s": 1e3 / ms_e2e,
+           "packed_weight_bytes_per_rank": step.packed_bytes, "kv_bytes_per_rank": step.kv_bytes,
+           "hbm_gbs_weights_plus_kv_per_rank": (step.packed_bytes + step.kv_bytes) / ms / 1e6,
+           "frac_of_hbm_per_rank": (step.packed_bytes + step.kv_bytes) / ms / 1e6 / peak, "peak_source": f"of {kind}",
+           "launches_per_token": {"exl3_linears": step.linear_launches, "fused_producers": step.fused_launches,
+                                  "attention_and_rope": step.attention_launches or "stock torch"},
+           "outputs_finite": finite}
+    del step
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_step(args) -> None:
+    """Secondary workload (single GPU or under torchrun): the full decode step; one step = one token."""
+    import torch
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist, reducer = None, None
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        if args.allreduce in ("peer", "fused"):
+            from trellis_serve_b200.runtime.allreduce import PeerAllReduce
+            reducer = PeerAllReduce(dev, 16 * 5120)
+    with ClockSampler(local) as clocks:
+        r = decode_step_rate(dev, args, rank, world, reducer if args.allreduce == "fused" else None, dist)
+    if rank == 0:
+        print(json.dumps({"metric": "exl3_decode_tok_s_27b_k3_ctx2048_batch1", "value": r["tok_s"], "unit": "tok/s", "n_gpus": world,
+                          "steps": 20, "warmup": 3, "ms_per_step": r["ms_per_token"], "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": {"workload": r["workload"]},
+                          "e2e": {"value": r["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 10240, "d2h_bytes_per_step": 10240},
+                          "decode_step": r, "gpu_launches": 20 * (r["launches_per_token"]["exl3_linears"] + r["launches_per_token"]["fused_producers"]),
+                          "clocks": clocks.summary()}))
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def tp_check(dev, rank: int, world: int, reducer, dist) -> dict:
     """Outside the timed region, N > 1: one row-parallel linear (17408 -> 5120, K = 3, every rank slices ITS rows out of the
     same seeded matrix) summed three ways -- exchange fused into the kernel, the library's stand-alone all-reduce, NCCL --
@@ -440,8 +521,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "peer", "nccl"],
                     help="exchange step of row-parallel layers at N > 1: the library's one-shot peer-memory kernel, or NCCL")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe", "c1"],
-                    help="decode = the headline 27B-shape layer set (default); prefill / moe / c1 = secondary single-GPU workloads")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe", "c1", "step"],
+                    help="decode = the headline 27B-shape layer set (default); prefill / moe / c1 = secondary single-GPU workloads; "
+                         "step = the whole transformer decode step (attention and KV cache included), any N")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch and bit-rate sweep appended to the default line")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -457,6 +539,9 @@ def main() -> None:
         return
     if args.workload == "c1":
         run_c1(args)
+        return
+    if args.workload == "step":
+        run_step(args)
         return
 
     import torch
@@ -540,15 +625,21 @@ def main() -> None:
     block_ms, e2e_ms = t[:BLOCKS], t[BLOCKS:]
     ms_total, ms_e2e = statistics.median(block_ms), statistics.median(e2e_ms)
     total_bytes = nbytes.item()
+    ls_packed_bytes, ls_launches = ls.packed_bytes, ls.launches_per_step
     check = tp_check(dev, rank, world, reducer, dist) if dist is not None else None
     sweep = decode_sweep(dev, args) if (world == 1 and not args.no_sweep) else None
+    full_step = None
+    if not args.no_sweep:
+        del ls                                            # its weights make room for the full step's
+        torch.cuda.empty_cache()
+        full_step = decode_step_rate(dev, args, rank, world, reducer if args.allreduce == "fused" else None, dist)
     if rank == 0:
         ms_step = ms_total / args.steps
         value = total_bytes / (ms_step * 1e-3) / 1e9
         e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
         peak, peak_kind = measured_peak_hbm()
         gemv_launches = args.layers * 4
-        per_rank_bytes = ls.packed_bytes
+        per_rank_bytes = ls_packed_bytes
         # Roofline of the dominant kernel (the decode GEMV): algorithmic bytes = packed-weight bytes of a launch.
         # Its average duration is bounded from above by the whole step time divided by the number of GEMV launches
         # (the step also contains the small activation-rotation kernels), so `achieved` is a lower bound.
@@ -574,12 +665,14 @@ def main() -> None:
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": sum(h.numel() * h.element_size() for h in hx),
                         "d2h_bytes_per_step": hy.numel() * hy.element_size(), "tok_s": 1e3 / (ms_e2e / args.steps)},
-                "gpu_launches": ls.launches_per_step * args.steps,
+                "gpu_launches": ls_launches * args.steps,
                 "clocks": clocks.summary()}
         if check is not None:
             line["tp_check"] = check
         if sweep is not None:
             line["sweep"] = sweep
+        if full_step is not None:
+            line["decode_step"] = full_step
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = {k: v for k, v in cpu_sample(K, cb).items() if k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))

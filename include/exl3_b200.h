@@ -132,6 +132,27 @@ exl3_status exl3_linear_prerotated(const uint32_t *packed, int K, int codebook, 
                                    size_t workspace_bytes, void *const *peer_regions, int rank, int world, size_t max_elems,
                                    int *state, void *stream);
 
+/* The attention side of the same step (not quantized arithmetic; here so that a step is a handful of launches per layer):
+ *   exl3_rope_append       qkv [rows, (q_heads + 2 kv_heads) * 128] holds q | k | v of one new token per row.  Rotary
+ *                          embedding ("rotate half": pairs (i, i + 64)) with cos_table / sin_table [positions, 64] fp32 at
+ *                          `*position` (device int, so a captured graph can move on): q in place, k into slot `*position` of
+ *                          k_cache [rows, kv_heads, t_max, 128], v copied into v_cache.
+ *   exl3_decode_attention  softmax(q k^T * scale) v over cache positions 0..*position for every query head (q_heads a
+ *                          multiple of kv_heads, ratio 1, 2, 4, 5 or 8), split over the cache in chunks of 128 positions
+ *                          and merged in a fixed order; out [rows, q_heads * 128] in `dtype` (may be NULL).  scratch:
+ *                          exl3_attention_scratch_bytes().  suh_next != NULL: a head is one rotation block of the o
+ *                          projection's input, so the merge also writes that linear's rotated fragments into `workspace`
+ *                          (as exl3_rotate_fragments would from `out`) and exl3_linear_prerotated can follow directly.
+ * The reference leaves attention to its engine; no counterpart there. */
+size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);
+exl3_status exl3_rope_append(void *qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float *cos_table,
+                             const float *sin_table, void *k_cache, void *v_cache, int t_max, const int *position,
+                             void *stream);
+exl3_status exl3_decode_attention(const void *qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim,
+                                  const void *k_cache, const void *v_cache, int t_max, const int *position, float scale,
+                                  void *scratch, size_t scratch_bytes, void *out, const uint16_t *suh_next, int codebook,
+                                  void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- fused linear for many rows (prefill) on the tcgen05 tensor cores -----------------------------------
  * Same contract as exl3_linear (fused group, dtypes, shard ends); built for hundreds to thousands of rows: the
  * weights are decoded once per 512 rows straight into the shared-memory operand of tcgen05.mma, accumulators live in

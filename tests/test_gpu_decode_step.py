@@ -78,10 +78,33 @@ def _ref_linear(x64, packed, suh, svh, K, cb, col0, n):
                                  np.float64, reconstruct=orc.c_reconstruct)
 
 
-def test_two_layer_decode_step_against_a_float64_restatement():
+def test_library_attention_equals_the_stock_path():
+    """RoPE + cache append + split-KV attention + merge against torch's rotary arithmetic and scaled_dot_product_attention on
+    the same q|k|v and cache: grouped queries (5 per KV head), a context that spans several 128-position chunks and ends
+    inside one, fp16 and bf16."""
+    for dtype, ctx in ((torch.float16, 300), (torch.bfloat16, 127)):
+        shape = ModelShape(hidden=256, q_heads=10, kv_heads=2, head_dim=128, ffn=512, layers=1)
+        a = DecodeStep(shape, 3, 0, ctx, rows=2, device=DEV, seed=5, dtype=dtype, attention="library")
+        b = DecodeStep(shape, 3, 0, ctx, rows=2, device=DEV, seed=5, dtype=dtype, attention="torch")
+        gen = torch.Generator(device=DEV)
+        gen.manual_seed(9)
+        qkv = torch.randn(a.qkv.shape, device=DEV, generator=gen).to(dtype)
+        b.kv.copy_(a.kv)
+        a.qkv.copy_(qkv)
+        b.qkv.copy_(qkv)
+        a._attention(0)
+        b._attention(0)
+        torch.cuda.synchronize()
+        tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+        assert float((a.attn.float() - b.attn.float()).abs().max()) <= tol
+        assert float((a.kv[0].float() - b.kv[0].float()).abs().max()) <= tol          # the appended key (rotated) and value
+
+
+@pytest.mark.parametrize("attention", ["library", "torch"])
+def test_two_layer_decode_step_against_a_float64_restatement(attention):
     shape = ModelShape(hidden=256, q_heads=2, kv_heads=1, head_dim=128, ffn=512, layers=2)
     K, cb, ctx = 4, 1, 24
-    step = DecodeStep(shape, K, cb, ctx, rows=1, device=DEV, seed=77)
+    step = DecodeStep(shape, K, cb, ctx, rows=1, device=DEV, seed=77, attention=attention)
     gen = torch.Generator(device=DEV)
     gen.manual_seed(5)
     step.h_in.copy_(torch.randn((1, shape.hidden), device=DEV, generator=gen).half())

@@ -405,6 +405,43 @@ exl3_status exl3_linear_prerotated(const uint32_t* packed, int K, int codebook, 
                          y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, true);
 }
 
+size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)
+{
+    if (rows < 0 || q_heads < 1 || kv_heads < 1 || t_max < 1) return 0;
+    return attention_scratch_bytes(rows, q_heads, kv_heads, t_max);
+}
+
+exl3_status exl3_rope_append(void* qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float* cos_table,
+                             const float* sin_table, void* k_cache, void* v_cache, int t_max, const int* position, void* stream)
+{
+    if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows < 0 || q_heads < 1 || kv_heads < 1 || head_dim != 128 || t_max < 1) return EXL3_ERR_BAD_SHAPE;
+    if (!aligned(qkv, 2) || !aligned(cos_table, 4) || !aligned(sin_table, 4) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(position, 4))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_rope_append(qkv, dtype == EXL3_BF16, rows, q_heads, kv_heads, cos_table, sin_table, k_cache, v_cache, t_max, position,
+                              (cudaStream_t)stream);
+}
+
+exl3_status exl3_decode_attention(const void* qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const void* k_cache,
+                                  const void* v_cache, int t_max, const int* position, float scale, void* scratch, size_t scratch_bytes,
+                                  void* out, const uint16_t* suh_next, int codebook, void* workspace, size_t workspace_bytes, void* stream)
+{
+    uint32_t* xf = nullptr;
+    if (suh_next) {
+        if (codebook < 0 || codebook > 2) return EXL3_ERR_UNSUPPORTED_CODEBOOK;
+        if (!aligned(suh_next, 8)) return EXL3_ERR_BAD_POINTER;
+        if (int rc = fragment_region(rows, q_heads * 128, 1, workspace, workspace_bytes, &xf)) return rc;
+    }
+    if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows < 0 || q_heads < 1 || kv_heads < 1 || head_dim != 128 || t_max < 1 || q_heads % kv_heads) return EXL3_ERR_BAD_SHAPE;
+    if (!aligned(qkv, 2) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(position, 4) || (out && !aligned(out, 8)) || (!out && !suh_next))
+        return EXL3_ERR_BAD_POINTER;
+    if (!aligned(scratch, 16) || scratch_bytes < attention_scratch_bytes(rows, q_heads, kv_heads, t_max)) return EXL3_ERR_WORKSPACE;
+    return launch_decode_attention(qkv, dtype == EXL3_BF16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, position, scale,
+                                   reinterpret_cast<float*>(scratch), out, reinterpret_cast<const __half*>(suh_next), xf,
+                                   suh_next ? fragment_mode(codebook) : 0, (cudaStream_t)stream);
+}
+
 /* ---- many-row (prefill) fused GEMM on tcgen05 ------------------------------------------------------------- */
 
 static size_t tc_up(size_t v) { return (v + 255) & ~(size_t)255; }

@@ -175,3 +175,243 @@ int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows
 }
 
 }  // namespace exl3
+
+// ------------------------------------------------------------------------------------------------ attention side of the step
+//
+// Between q|k|v and o a decode step applies the rotary embedding to q and k, appends k and v to the cache and attends over
+// the cache.  None of it is quantized arithmetic; it is written here so that the step does not pay a dozen framework
+// launches per layer.  Head dimension 128, grouped queries (q_heads a multiple of kv_heads), one new token per sequence.
+
+namespace exl3 {
+
+constexpr int ATT_D = 128;
+constexpr int ATT_MAX_GROUP = 8;          // query heads per KV head
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_CHUNK = ATT_WARPS * 32; // cache positions per CTA
+constexpr int ATT_PART = ATT_D + 4;       // floats of one partial result: 128 weighted sums, maximum, normaliser (16-byte rows)
+
+// One thread per (row, head, pair i < 64): x1' = x1 cos - x2 sin, x2' = x2 cos + x1 sin with x1 = x[i], x2 = x[i + 64]
+// (the "rotate half" convention).  Query heads are rotated in place in qkv; key heads are rotated into the cache slot
+// `pos`, value heads copied there.  cache layout [rows, kv_heads, t_max, 128].
+__global__ void rope_append_kernel(void* __restrict__ qkv, int bf16, int rows, int q_heads, int kv_heads, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, void* __restrict__ k_cache, void* __restrict__ v_cache, int t_max,
+                                   const int* __restrict__ pos_ptr)
+{
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const int heads = q_heads + 2 * kv_heads;
+    const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (idx >= (long long)rows * heads * 64) return;
+    const int i = (int)(idx & 63), head = (int)((idx >> 6) % heads), row = (int)((idx >> 6) / heads);
+    const int pos = *pos_ptr;
+    const long long base = ((long long)row * heads + head) * ATT_D;
+    const bool b = bf16 != 0;
+    const float x1 = to_f32(qkv, base + i, b), x2 = to_f32(qkv, base + i + 64, b);
+    auto put = [&](void* dst, long long at, float v) {
+        if (b) reinterpret_cast<__nv_bfloat16*>(dst)[at] = __float2bfloat16_rn(v);
+        else reinterpret_cast<__half*>(dst)[at] = __float2half_rn(v);
+    };
+    if (head < q_heads + kv_heads) {
+        const float c = cos_t[(long long)pos * 64 + i], s = sin_t[(long long)pos * 64 + i];
+        const float y1 = x1 * c - x2 * s, y2 = x2 * c + x1 * s;
+        if (head < q_heads) {
+            put(qkv, base + i, y1);
+            put(qkv, base + i + 64, y2);
+        } else {
+            const long long at = (((long long)row * kv_heads + (head - q_heads)) * t_max + pos) * ATT_D;
+            put(k_cache, at + i, y1);
+            put(k_cache, at + i + 64, y2);
+        }
+    } else {
+        const long long at = (((long long)row * kv_heads + (head - q_heads - kv_heads)) * t_max + pos) * ATT_D;
+        put(v_cache, at + i, x1);
+        put(v_cache, at + i + 64, x2);
+    }
+}
+
+// Split-KV decode attention.  grid = (splits, kv_heads, rows); a CTA attends positions [split * ATT_CHUNK ...) of one KV
+// head for its G query heads: every lane owns ONE position (reads its key row, G dot products against the queries held in
+// shared memory, no shuffles), the warp then walks its 32 positions for the values (each lane four of the 128 columns).
+// Partial results (running maximum, normaliser, G x 128 weighted sums per warp) are merged by attention_merge_kernel.
+template <int G>
+__global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const void* __restrict__ qkv, int bf16, int q_heads, int kv_heads,
+                                                                           const void* __restrict__ k_cache, const void* __restrict__ v_cache,
+                                                                           int t_max, const int* __restrict__ pos_ptr, float scale,
+                                                                           float* __restrict__ part)
+{
+    __shared__ float qs[G][ATT_D];
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int T = *pos_ptr + 1;                                   // valid cache positions
+    const int heads = q_heads + 2 * kv_heads;
+    const bool b = bf16 != 0;
+    for (int e = threadIdx.x; e < G * ATT_D; e += ATT_WARPS * 32)
+        qs[e / ATT_D][e % ATT_D] = to_f32(qkv, ((long long)row * heads + kvh * G + e / ATT_D) * ATT_D + e % ATT_D, b) * scale;
+    __syncthreads();
+    const int splits = gridDim.x;
+    float* out = part + ((((long long)row * kv_heads + kvh) * splits + split) * ATT_WARPS + warp) * (G * ATT_PART);
+    const int t = split * ATT_CHUNK + warp * 32 + lane;
+    const long long rowbase = (((long long)row * kv_heads + kvh) * t_max) * ATT_D;
+    float sc[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) sc[g] = 0.f;
+    if (t < T) {
+        const uint4* kr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(k_cache) + (rowbase + (long long)t * ATT_D) * 2);
+#pragma unroll 8
+        for (int j = 0; j < 16; j++) {                             // 16 x 8 halves, eight loads in flight
+            const uint4 w = kr[j];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int h2 = 0; h2 < 4; h2++) {
+                float k0, k1;
+                if (b) {
+                    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&ww[h2]);
+                    k0 = __low2float(v);
+                    k1 = __high2float(v);
+                } else {
+                    const __half2 v = *reinterpret_cast<const __half2*>(&ww[h2]);
+                    k0 = __low2float(v);
+                    k1 = __high2float(v);
+                }
+#pragma unroll
+                for (int g = 0; g < G; g++) sc[g] += k0 * qs[g][j * 8 + h2 * 2] + k1 * qs[g][j * 8 + h2 * 2 + 1];
+            }
+        }
+    }
+    float m[G], l[G], p[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        float v = t < T ? sc[g] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+        m[g] = v;
+        p[g] = (t < T) ? __expf(sc[g] - v) : 0.f;
+        float s = p[g];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        l[g] = s;
+    }
+    float acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[g][e] = 0.f;
+    const int t0 = split * ATT_CHUNK + warp * 32;
+    const int n = T - t0 < 32 ? T - t0 : 32;                      // warp-uniform
+    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(v_cache) + (rowbase + (long long)t0 * ATT_D + 4 * lane) * 2;
+    for (int j0 = 0; j0 < n; j0 += 8) {                           // eight value rows in flight per warp
+        uint2 w[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) w[u] = (j0 + u < n) ? *reinterpret_cast<const uint2*>(vbase + (long long)(j0 + u) * ATT_D * 2) : make_uint2(0u, 0u);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            float v[4];
+            if (b) {
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w[u].x), c = *reinterpret_cast<const __nv_bfloat162*>(&w[u].y);
+                v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
+            } else {
+                const __half2 a = *reinterpret_cast<const __half2*>(&w[u].x), c = *reinterpret_cast<const __half2*>(&w[u].y);
+                v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float pj = __shfl_sync(0xFFFFFFFFu, p[g], (j0 + u) & 31);      // zero for positions past the end
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[g][e] += pj * v[e];
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        float* o = out + g * ATT_PART;
+        *reinterpret_cast<float4*>(o + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        if (lane == 0) {
+            o[ATT_D] = n > 0 ? m[g] : -INFINITY;
+            o[ATT_D + 1] = n > 0 ? l[g] : 0.f;
+        }
+    }
+}
+
+// One warp per (row, query head): lane l merges columns 4l..4l+3 of every partial of its head (fixed order: the same bits
+// every time), writes the output and -- a head is exactly one 128-wide rotation block of the o projection's input --
+// optionally the rotated fragments of that block for the linear that follows (suh != null).
+__global__ void attention_merge_kernel(const float* __restrict__ part, int rows, int q_heads, int kv_heads, int G, int parts,
+                                       void* __restrict__ out, int bf16, const __half* __restrict__ suh, uint32_t* __restrict__ xf, int mode)
+{
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= rows * q_heads) return;
+    const int qh = item % q_heads, row = item / q_heads;
+    const int kvh = qh / G, g = qh % G;
+    const float* base = part + (((long long)row * kv_heads + kvh) * parts) * (G * ATT_PART) + g * ATT_PART;
+    const long long stride = (long long)G * ATT_PART;
+    float mx = -INFINITY;
+    for (int s = 0; s < parts; s++) mx = fmaxf(mx, base[s * stride + ATT_D]);
+    float num[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
+    for (int s = 0; s < parts; s++) {
+        const float ms = base[s * stride + ATT_D];
+        const float w = ms == -INFINITY ? 0.f : __expf(ms - mx);
+        const float4 a = *reinterpret_cast<const float4*>(base + s * stride + 4 * lane);
+        num[0] += w * a.x;
+        num[1] += w * a.y;
+        num[2] += w * a.z;
+        num[3] += w * a.w;
+        den += w * base[s * stride + ATT_D + 1];
+    }
+    float y[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) y[e] = round_act(num[e] / den, bf16 != 0);
+    if (out) store_act4(out, ((long long)row * q_heads + qh) * ATT_D + 4 * lane, y, bf16 != 0);
+    if (suh) rotate_store(y, suh + qh * ATT_D, xf, mode, 0, (q_heads * ATT_D) >> 4, rows, row, qh, lane);
+}
+
+size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)
+{
+    const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
+    const int G = q_heads / (kv_heads > 0 ? kv_heads : 1);
+    return (size_t)rows * kv_heads * splits * ATT_WARPS * G * ATT_PART * sizeof(float);
+}
+
+int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads, const float* cos_t, const float* sin_t, void* k_cache,
+                       void* v_cache, int t_max, const int* pos, cudaStream_t st)
+{
+    const long long items = (long long)rows * (q_heads + 2 * kv_heads) * 64;
+    if (items == 0) return EXL3_OK;
+    return launch_chained(rope_append_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, st, qkv, bf16, rows, q_heads, kv_heads, cos_t,
+                          sin_t, k_cache, v_cache, t_max, pos);
+}
+
+template <int G>
+static int launch_attention_g(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, const void* k_cache, const void* v_cache,
+                              int t_max, const int* pos, float scale, float* part, void* out, const __half* suh, uint32_t* xf, int mode,
+                              cudaStream_t st)
+{
+    const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
+    int rc = launch_chained(decode_attention_kernel<G>, dim3(splits, kv_heads, rows), dim3(ATT_WARPS * 32), 0, st, qkv, bf16, q_heads, kv_heads,
+                            k_cache, v_cache, t_max, pos, scale, part);
+    if (rc) return rc;
+    return launch_chained(attention_merge_kernel, dim3((unsigned)((rows * q_heads + 3) / 4)), dim3(128), 0, st, static_cast<const float*>(part), rows,
+                          q_heads, kv_heads, G, splits * ATT_WARPS, out, bf16, suh, xf, mode);
+}
+
+int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, const void* k_cache, const void* v_cache,
+                            int t_max, const int* pos, float scale, float* part, void* out, const __half* suh, uint32_t* xf, int mode,
+                            cudaStream_t st)
+{
+    if (rows == 0) return EXL3_OK;
+    if (kv_heads < 1 || q_heads % kv_heads) return EXL3_ERR_BAD_SHAPE;
+    switch (q_heads / kv_heads) {
+        case 1: return launch_attention_g<1>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
+        case 2: return launch_attention_g<2>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
+        case 4: return launch_attention_g<4>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
+        case 5: return launch_attention_g<5>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
+        case 8: return launch_attention_g<8>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
+    }
+    return EXL3_ERR_BAD_SHAPE;
+}
+
+}  // namespace exl3

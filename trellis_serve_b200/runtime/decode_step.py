@@ -9,7 +9,8 @@
 
 Every linear is ONE decode-GEMV launch whose activations were rotated by the kernel ahead of it; rotary embedding, cache
 append and attention are stock torch (`scaled_dot_product_attention`): they are not part of the quantized-linear path and
-their bytes (the KV read) are reported separately.  The whole step is captured in one CUDA graph, as an engine captures
+their bytes (the KV read) are reported separately.  `attention="library"` (default) runs the library's own three small
+kernels for that part (RoPE + cache append, split-KV attention, merge); `attention="torch"` keeps the stock torch ops.  The whole step is captured in one CUDA graph, as an engine captures
 it (cuda/src/sglang_exl3/sglang_glue/moe.py:202-213 warms for that purpose; cuda/src/sglang_exl3/tools/decode_microbench.py
 :27-41 times launches the same way).
 
@@ -70,10 +71,11 @@ class DecodeStep:
     """Random-initialised dense transformer of `shape` at `K` bits, one tensor-parallel rank of `tp_size`."""
 
     def __init__(self, shape: ModelShape, K: int, codebook: int, context: int, rows: int = 1, tp_rank: int = 0, tp_size: int = 1,
-                 device="cuda:0", dtype: torch.dtype = torch.float16, seed: int = 400, exchange=None, group=None):
+                 device="cuda:0", dtype: torch.dtype = torch.float16, seed: int = 400, exchange=None, group=None,
+                 attention: str = "library"):
         self.shape, self.K, self.codebook, self.context, self.rows = shape, K, codebook, context, rows
         self.tp_rank, self.tp_size, self.exchange, self.group = tp_rank, tp_size, exchange, group
-        self.device, self.dtype = torch.device(device), dtype
+        self.device, self.dtype, self.attention = torch.device(device), dtype, attention
         s, dev, tp = shape, self.device, tp_size
         if s.q_heads % tp or s.ffn % tp or (s.ffn // tp) % 128 or (s.q_out // tp) % 128:
             raise ValueError(f"{s.q_heads} query heads / ffn {s.ffn} cannot be split over {tp} ranks at 128-aligned boundaries")
@@ -101,6 +103,14 @@ class DecodeStep:
         inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, device=dev).float() / s.head_dim))
         ang = pos[:, None] * inv[None, :]
         self.cos, self.sin = torch.cos(ang).to(dtype), torch.sin(ang).to(dtype)          # [1, head_dim / 2]
+        # the library's attention kernels: tables by position (the values of the torch path, as fp32), position on the device
+        self.cos_table = torch.zeros((context + 1, s.head_dim // 2), dtype=torch.float32, device=dev)
+        self.sin_table = torch.zeros_like(self.cos_table)
+        self.cos_table[context], self.sin_table[context] = self.cos[0].float(), self.sin[0].float()
+        self.position = torch.tensor([context], dtype=torch.int32, device=dev)
+        from .. import _lib
+        self.att_scratch = torch.empty(int(_lib.load().exl3_attention_scratch_bytes(rows, self.q_heads, self.kv_heads, context + 1)),
+                                       dtype=torch.uint8, device=dev)
         # activations of the chain (static: the captured graph sees fixed addresses)
         mk = lambda w: torch.empty((rows, w), dtype=dtype, device=dev)
         self.h_in = torch.zeros((rows, h), dtype=dtype, device=dev)          # the step's input: the token's embedding
@@ -108,7 +118,8 @@ class DecodeStep:
         self.qkv, self.attn, self.o_out, self.gu, self.out = mk(q + 2 * kv), mk(q), mk(h), mk(2 * f), mk(h)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.linear_launches = s.layers * 4
-        self.fused_launches = s.layers * 4            # rmsnorm_rotate x2, rotation ahead of o, silu_mul_rotate
+        self.fused_launches = s.layers * (3 if attention == "library" else 4)   # rmsnorm_rotate x2, silu_mul_rotate (+ rotation ahead of o)
+        self.attention_launches = s.layers * 3 if attention == "library" else None
 
     # ---- bytes
     @property
@@ -126,8 +137,24 @@ class DecodeStep:
         x1, x2 = x[..., : self.shape.head_dim // 2], x[..., self.shape.head_dim // 2:]
         return torch.cat([x1 * self.cos - x2 * self.sin, x2 * self.cos + x1 * self.sin], dim=-1)
 
-    def _attention(self, layer: int) -> None:
+    def _attention(self, layer: int, suh_next: torch.Tensor | None = None) -> bool:
+        """RoPE, cache append and attention of one layer into `self.attn`.  True when the rotated input of the o projection
+        was written as well (the library's merge kernel does that when handed the projection's sign vector)."""
         s, q, kv = self.shape, self.q_heads * self.shape.head_dim, self.kv_heads * self.shape.head_dim
+        if self.attention == "library":
+            from .. import _lib
+            lib, p, st = _lib.load(), lin._ptr, lin._stream(self.device)
+            cache, code = self.kv[layer], lin._dtype_code(self.qkv)
+            with torch.cuda.device(self.device):
+                _lib.check(lib.exl3_rope_append(p(self.qkv), code, self.rows, self.q_heads, self.kv_heads, s.head_dim, p(self.cos_table),
+                                                p(self.sin_table), p(cache[0]), p(cache[1]), self.context + 1, p(self.position), st),
+                           "exl3_rope_append")
+                _lib.check(lib.exl3_decode_attention(p(self.qkv), code, self.rows, self.q_heads, self.kv_heads, s.head_dim, p(cache[0]),
+                                                     p(cache[1]), self.context + 1, p(self.position), 1.0 / math.sqrt(s.head_dim),
+                                                     p(self.att_scratch), self.att_scratch.numel(), p(self.attn), p(suh_next),
+                                                     self.codebook, p(self.workspace), self.workspace.numel(), st),
+                           "exl3_decode_attention")
+            return suh_next is not None
         qh = self._rope(self.qkv[:, :q], self.q_heads).unsqueeze(2)                        # [rows, q heads, 1, d]
         kh = self._rope(self.qkv[:, q:q + kv], self.kv_heads)
         vh = self.qkv[:, q + kv:].view(self.rows, self.kv_heads, s.head_dim)
@@ -136,6 +163,7 @@ class DecodeStep:
         cache[1][:, :, self.context] = vh
         y = torch.nn.functional.scaled_dot_product_attention(qh, cache[0], cache[1], enable_gqa=self.q_heads != self.kv_heads)
         self.attn.copy_(y.reshape(self.rows, q))
+        return False
 
     def _reduce(self, t: torch.Tensor) -> None:
         if self.tp_size > 1 and self.exchange is None:
@@ -149,8 +177,8 @@ class DecodeStep:
         for i, (qkv, o, gu, down, norms) in enumerate(self.layers):
             lin.rmsnorm_rotate(h, self.residual, norms[0], self.shape.eps, qkv.suh, cb, ws)
             lin.run_prerotated(rows, qkv.packed, qkv.svh, qkv.ends, cb, self.qkv, ws)
-            self._attention(i)
-            lin.rotate_fragments(self.attn, o.suh, cb, ws)
+            if not self._attention(i, o.suh):
+                lin.rotate_fragments(self.attn, o.suh, cb, ws)
             lin.run_prerotated(rows, o.packed, o.svh, o.ends, cb, self.o_out, ws, exchange=ex)
             self._reduce(self.o_out)
             lin.rmsnorm_rotate(self.o_out, self.residual, norms[1], self.shape.eps, gu.suh, cb, ws)
