@@ -254,12 +254,22 @@ def run_moe(args) -> None:
     wts, ids = (wts / wts.sum(-1, keepdim=True)).float(), ids.int()
     x = torch.randn((T, H), device=dev, generator=gen).half()
     out = torch.empty_like(x)
+    if args.moe_path != "auto":           # measurement knob: force one path to find the crossover
+        moe.TC_ROWS_PER_EXPERT = 0 if args.moe_path == "tc" else 1 << 30
+    tensor_core = moe.moe_block_size(T, top_k, E) == 128
+    if tensor_core:
+        # many rows per expert: the allocation-free layer entry, which sends the class through the grouped tcgen05 GEMM
+        mixed = moe.MixedPack([pack], [torch.arange(E, dtype=torch.int32, device=dev)], E, H, I, cb)
+        ws = torch.zeros(moe.layer_workspace_bytes([E], H, I, cb, T, top_k), dtype=torch.uint8, device=dev)
+        layer = lambda: moe.run_layer(x, wts, ids, mixed, out, ws)
+    else:
+        layer = lambda: moe.forward(x, wts, ids, pack, out=out)
     for _ in range(args.warmup):
-        moe.forward(x, wts, ids, pack, out=out)
+        layer()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
-        moe.forward(x, wts, ids, pack, out=out)
+        layer()
     g.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -279,10 +289,12 @@ def run_moe(args) -> None:
                       "dtype": "f16", "data": "synthetic",
                       "config": {"workload": f"MoE layer hidden 2048, 256 experts, intermediate 512, top-8, K=3 3INST, {T} tokens",
                                  "tokens": T, "distinct_experts": distinct, "touched_bytes": nbytes,
+                                 "path": "grouped tcgen05 GEMM, 128-row moe blocks" if tensor_core else "grouped GEMV, 8-row moe blocks",
+                                 "tflops": 2.0 * T * top_k * 3 * H * I / ms / 1e9,
                                  "l2": "the layer's working set is L2-resident on replay (302 MB of experts, touched subset smaller)"},
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
-                                   "peak_source": f"of {kind}", "kernel": "moe_gemm_kernel"},
-                      "gpu_launches": 6 * args.steps, "clocks": clocks.summary()}))
+                                   "peak_source": f"of {kind}", "kernel": "gemm_tc_kernel (grouped)" if tensor_core else "moe_gemm_kernel"},
+                      "gpu_launches": (11 if tensor_core else 6) * args.steps, "clocks": clocks.summary()}))
 
 
 def _graph_ring_time(run_one, ring: int, reps: int = 5) -> float:
@@ -524,6 +536,7 @@ def main() -> None:
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe", "c1", "step"],
                     help="decode = the headline 27B-shape layer set (default); prefill / moe / c1 = secondary single-GPU workloads; "
                          "step = the whole transformer decode step (attention and KV cache included), any N")
+    ap.add_argument("--moe-path", choices=["auto", "gemv", "tc"], default="auto", help="--workload moe: force the grouped GEMV or the grouped tensor-core path")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch and bit-rate sweep appended to the default line")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -267,6 +267,24 @@ exl3_status exl3_moe_gemm(const uint32_t *xf, const uint32_t *packed, int K, int
 exl3_status exl3_moe_combine(const uint16_t *yd, const float *topk_weights, const int32_t *topk_ids, int tokens, int top_k,
                              int hidden, int num_experts, void *y, int y_dtype, void *stream);
 
+/* Routed experts with many rows per expert (prefill-sized batches) on the tensor cores.  The reference serves such batches
+ * with the same grouped kernel and larger moe blocks (moe_block_size picks 8..64 rows from T * top_k / E,
+ * cuda/src/sglang_exl3/kernels/marlin_moe.py:52-57; launch at cuda/csrc/exl3_marlin_moe.cu:376-408); here the routing is
+ * aligned to blocks of exl3_moe_tc_block_rows() = 128 rows and up to two blocks of one expert (four when hidden or inter is
+ * not a multiple of 256) share every decoded weight block in a grouped tcgen05 GEMM.  x and the sign vectors must be 8-byte
+ * aligned.  One call runs one bitrate class from the routing to the per-slot outputs:
+ *   align (expert_map as in exl3_moe_align_mapped, or NULL with num_local == num_experts) -> gate|up -> SiLU(gate) * up
+ *   -> down -> yd[slot, :] (fp16 [tokens * top_k, hidden]; slots of experts outside the class are not written).
+ * exl3_moe_combine then closes the layer.  w13 / suh13 / svh13 / w2 / suh2 / svh2 are the resident expert stacks of
+ * exl3_moe_gemm ([E][2I/128][H/128]..., [E][2][H], [E][2I], [E][H/128][I/128]..., [E][I], [E][H]).  The workspace holds
+ * exl3_moe_tc_workspace_bytes(tokens * top_k, num_local, hidden, inter) bytes, 256-byte aligned, first 256 bytes zero. */
+int exl3_moe_tc_block_rows(void);
+size_t exl3_moe_tc_workspace_bytes(int slots, int num_local, int hidden, int inter);
+exl3_status exl3_moe_tc_experts(const void *x, int x_dtype, int tokens, int top_k, int hidden, int inter, const int32_t *topk_ids,
+                                int num_experts, const int32_t *expert_map, int num_local, const uint32_t *w13, const uint16_t *suh13,
+                                const uint16_t *svh13, const uint32_t *w2, const uint16_t *suh2, const uint16_t *svh2, int K,
+                                int codebook, uint16_t *yd, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Reads and clears the device-side error word kept in a workspace (set when a bounded wait in a kernel gave up).
  * workspace == NULL with workspace_bytes == 0 means the built-in scratch of exl3_linear_static on the current device.
  * Synchronises `stream`.  Returns EXL3_OK or EXL3_ERR_DEVICE_WAIT. */

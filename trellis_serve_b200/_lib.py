@@ -61,6 +61,9 @@ SIGNATURES = {
     "exl3_moe_workspace_bytes": (_sz, [_i, _i]),
     "exl3_moe_gemm": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "exl3_moe_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
+    "exl3_moe_tc_block_rows": (_i, []),
+    "exl3_moe_tc_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "exl3_moe_tc_experts": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "exl3_device_error": (_i, [_vp, _sz, _vp]),
     "exl3_set_gemv_mode": (None, [_i]),
     "exl3_set_tc_tiling": (None, [_i]),

@@ -23,7 +23,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", 
          "--expt-relaxed-constexpr", "-Xptxas", "-v", *os.environ.get("EXL3_B200_NVCC_FLAGS", "").split()]
 
-PLAIN = ["exl3_api.cu", "exl3_kernels.cu", "exl3_gemv.cu", "exl3_moe.cu", "exl3_gemm_tc.cu", "exl3_allreduce.cu", "exl3_step.cu"]
+PLAIN = ["exl3_api.cu", "exl3_kernels.cu", "exl3_gemv.cu", "exl3_moe.cu", "exl3_moe_tc.cu", "exl3_gemm_tc.cu", "exl3_allreduce.cu", "exl3_step.cu"]
 PER_K = [("exl3_gemv_inst.cu", "EXL3_GEMV_K", range(2, 9)), ("exl3_moe_inst.cu", "EXL3_MOE_K", range(2, 9))]
 
 

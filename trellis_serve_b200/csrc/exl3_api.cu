@@ -637,6 +637,38 @@ exl3_status exl3_moe_combine(const uint16_t* yd, const float* topk_weights, cons
                               y_dtype == EXL3_BF16, (cudaStream_t)stream);
 }
 
+int exl3_moe_tc_block_rows(void) { return MOE_TC_BLOCK_ROWS; }
+
+size_t exl3_moe_tc_workspace_bytes(int slots, int num_local, int hidden, int inter)
+{
+    if (slots < 0 || num_local < 1 || hidden <= 0 || inter <= 0 || hidden % 128 || inter % 128) return 0;
+    return moe_tc_workspace_bytes(slots, num_local, hidden, inter);
+}
+
+exl3_status exl3_moe_tc_experts(const void* x, int x_dtype, int tokens, int top_k, int hidden, int inter, const int32_t* topk_ids,
+                                int num_experts, const int32_t* expert_map, int num_local, const uint32_t* w13, const uint16_t* suh13,
+                                const uint16_t* svh13, const uint32_t* w2, const uint16_t* suh2, const uint16_t* svh2, int K, int codebook,
+                                uint16_t* yd, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (int rc = check_matrix(hidden, 2 * inter, K, codebook)) return rc;
+    if (int rc = check_matrix(inter, hidden, K, codebook)) return rc;
+    if (tokens < 0 || top_k < 1 || num_experts < 1 || num_local < 1 || num_local > MOE_MAX_EXPERTS) return EXL3_ERR_BAD_SHAPE;
+    if (!expert_map && num_local != num_experts) return EXL3_ERR_BAD_SHAPE;
+    if ((long long)tokens * top_k > (1 << 24)) return EXL3_ERR_BAD_SHAPE;
+    if (x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (tokens == 0) return EXL3_OK;
+    if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
+    if (!aligned(x, 8) || !aligned(topk_ids, 4) || !aligned(w13, 16) || !aligned(w2, 16) || !aligned(suh13, 8) || !aligned(svh13, 8) ||
+        !aligned(suh2, 8) || !aligned(svh2, 8) || !aligned(yd, 8))
+        return EXL3_ERR_BAD_POINTER;
+    const int slots = tokens * top_k;
+    if (!aligned(workspace, 256) || workspace_bytes < moe_tc_workspace_bytes(slots, num_local, hidden, inter)) return EXL3_ERR_WORKSPACE;
+    return launch_moe_tc_experts(x, x_dtype == EXL3_BF16, top_k, hidden, inter, topk_ids, slots, num_experts, expert_map, num_local, w13,
+                                 reinterpret_cast<const __half*>(suh13), reinterpret_cast<const __half*>(svh13), w2,
+                                 reinterpret_cast<const __half*>(suh2), reinterpret_cast<const __half*>(svh2), K, codebook,
+                                 reinterpret_cast<__half*>(yd), reinterpret_cast<unsigned char*>(workspace), (cudaStream_t)stream);
+}
+
 /* ---- exl3_linear_static: the fused linear for callers that cannot bring a workspace ---------------------------
  * Scratch (activation fragments, split-k partial sums, block counters, error word) lives in this file-scope device
  * array instead of a caller buffer.  Every GPU that loads the library holds the array until the process exits. */

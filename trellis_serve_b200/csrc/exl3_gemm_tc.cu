@@ -18,13 +18,13 @@
 // Each weight block is decoded once per 512 rows and reused by 16 MMAs, so the kernel is bound by the tensor pipe,
 // not by the decode.  Every wait is bounded (exl3_ptx.cuh); on a time-out the error word is set and the control flow
 // continues unchanged to the common exit, where tensor memory is released.
+#include <cstring>
+
 #include "exl3_internal.h"
 #include "exl3_ptx.cuh"
 
 namespace exl3 {
 
-constexpr int TC_ROWS = 512;                  // rows of one super tile of the A-operand layout in global memory
-constexpr int TC_KB = 64;                     // reduction block
 constexpr uint32_t TC_A_TILE_BYTES = 128 * TC_KB * 2;                 // 16 KB: one 128-row A tile of a reduction block
 
 // Tilings of the output.  Narrow: MT x 128 rows by 128 columns (MT = 4 or 3 accumulators), 8 decode warps, 2 stages.  Wide:
@@ -65,6 +65,12 @@ struct GemmTcLaunch {
     int ksplit;                  // > 1: the reduction of every tile is cut into this many parts, each on its own CTA
     float* part;                 //      which stores its fp32 accumulators into slab [part index][rows][n_total]
     long long part_slab;         //      floats per slab
+    // Grouped (routed experts): work items come from a device-side list built after the routing alignment.  Item i =
+    // (expert, first 128-row block, blocks of that expert in the item (1..TC_GROUPED_MT), unused); the weights of expert e start
+    // expert_stride words after `packed`, rows are positions of the alignment (blocks of 128 rows of one expert).
+    const int4* items;
+    const int* n_items;
+    long long expert_stride;
     Pow2 pw;
 };
 
@@ -115,9 +121,10 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
 
 // SPLIT: the reduction of a tile may be cut into p.ksplit parts (work items); without it the part count is the constant 1
 // and the index arithmetic of the unsplit kernel folds away.
-template <int K, int FAM, int MT_, bool WIDE, bool SPLIT>
+template <int K, int FAM, int MT_, bool WIDE, bool SPLIT, bool GROUPED = false>
 __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
 {
+    static_assert(!GROUPED || !SPLIT, "grouped work items carry whole reductions");
     using TT = TcTile<MT_, WIDE>;
     constexpr int DW = TT::DECODE_WARPS, STAGES = TT::STAGES;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -149,11 +156,13 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if constexpr (GROUPED) ptx::grid_dependency_wait();      // the item list comes from the kernels ahead in the stream
     const int KB = p.KG * 2;                           // reduction blocks of 64
-    const int MT = (p.rows + TT::ROWS - 1) / TT::ROWS; // row tiles
+    const int MT = GROUPED ? 1 : (p.rows + TT::ROWS - 1) / TT::ROWS;   // row tiles
     const int NT = p.NB / TT::NBLK;                    // column tiles
     const int KS = SPLIT ? p.ksplit : 1;
-    const long long n_tiles = (long long)MT * NT * KS;       // work items: (tile, part of its reduction), part fastest
+    // work items: (tile, part of its reduction), part fastest; grouped: (item of the list, column tile), column fastest
+    const long long n_tiles = GROUPED ? (long long)(*p.n_items) * NT : (long long)MT * NT * KS;
     auto kb_begin = [&](long long t) { return (int)((long long)KB * (t % KS) / KS); };
     auto kb_end = [&](long long t) { return (int)((long long)KB * (t % KS + 1) / KS); };
     bool failed = false;
@@ -172,20 +181,36 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
         // The warp's words of the next reduction block are requested one block ahead, so their L2 latency hides
         // behind the decode of the current block.
         // column block of a work item (64-bit divisions: once per work item, not per reduction block)
-        auto block_of = [&](long long tile) { return (int)((tile / KS) / MT) * TT::NBLK + nbh; };
-        auto words_ptr = [&](int nb_, int kb) {
-            return p.packed + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
+        auto block_of = [&](long long tile) { return (GROUPED ? (int)(tile % NT) : (int)((tile / KS) / MT)) * TT::NBLK + nbh; };
+        auto base_of = [&](long long tile) {               // start of the tile's weight matrix
+            if constexpr (GROUPED) return p.packed + (long long)p.items[tile / NT].x * p.expert_stride;
+            else return p.packed;
+        };
+        auto words_ptr = [&](const uint32_t* base, int nb_, int kb) {
+            return base + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
         };
         uint32_t Lnext[K];
         if ((long long)blockIdx.x < n_tiles) {
-            const uint32_t* src = words_ptr(block_of(blockIdx.x), kb_begin(blockIdx.x));
+            const uint32_t* src = words_ptr(base_of(blockIdx.x), block_of(blockIdx.x), kb_begin(blockIdx.x));
 #pragma unroll
             for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
         }
         for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-            const int ms = (int)((t / KS) % MT), ct = (int)((t / KS) / MT), sp = (int)(t % KS);
+            int ms = (int)((t / KS) % MT), ct = (int)((t / KS) / MT), row0, present = TT::M_TILES;
+            const int sp = (int)(t % KS);
+            if constexpr (GROUPED) {
+                const int4 item = p.items[t / NT];
+                ms = 0;
+                ct = (int)(t % NT);
+                row0 = item.y * 128;
+                present = item.z;
+            } else {
+                row0 = ms * TT::ROWS;
+            }
             const int kb0 = kb_begin(t), kb1 = kb_end(t);
             const long long t_next = t + gridDim.x;
+            const uint32_t* base_cur = base_of(t);
+            const uint32_t* base_next = t_next < n_tiles ? base_of(t_next) : p.packed;
             const int nb_cur = block_of(t), nb_next = t_next < n_tiles ? block_of(t_next) : 0;
             const int kb_next = t_next < n_tiles ? kb_begin(t_next) : 0;
             for (int kb = kb0; kb < kb1; kb++, it++) {
@@ -197,7 +222,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                 {
                     const bool last = kb + 1 == kb1;
                     if (!last || t_next < n_tiles) {
-                        const uint32_t* src = last ? words_ptr(nb_next, kb_next) : words_ptr(nb_cur, kb + 1);
+                        const uint32_t* src = last ? words_ptr(base_next, nb_next, kb_next) : words_ptr(base_cur, nb_cur, kb + 1);
 #pragma unroll
                         for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
                     }
@@ -239,8 +264,8 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
             tc_fence_after();
             const int quarter = warp & 3, cgroup = warp >> 2;
 #pragma unroll 1
-            for (int mt = 0; mt < TT::M_TILES; mt++) {
-                const int row = ms * TT::ROWS + mt * 128 + quarter * 32 + lane;
+            for (int mt = 0; mt < present; mt++) {
+                const int row = row0 + mt * 128 + quarter * 32 + lane;
 #pragma unroll 1
                 for (int cc = 0; cc < 2; cc++) {
                     const int col = cgroup * 64 + cc * 32;
@@ -252,7 +277,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
 #pragma unroll
                         for (int v = 0; v < 32; v += 4)
                             *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
-                    } else if (row < p.rows) {
+                    } else if (GROUPED || row < p.rows) {
                         __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
 #pragma unroll
                         for (int v = 0; v < 32; v += 8) {
@@ -280,16 +305,21 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
         if (lane == 0) {
             uint32_t it = 0;
             for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-                const int ms = (int)((t / KS) % MT), nb = (int)((t / KS) / MT) * TT::NBLK;
+                const int ms = (int)((t / KS) % MT), nb = (GROUPED ? (int)(t % NT) : (int)((t / KS) / MT)) * TT::NBLK;
                 const int kb0 = kb_begin(t), kb1 = kb_end(t);
                 int shard = 0;
                 while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
                 // The A layout in global memory is in super tiles of 512 rows = four 128-row tiles of 16 KB per reduction
                 // block; the tile's 128-row tiles are fetched one by one (a 384-row tile may straddle two super tiles, and
                 // its last 128-row tiles may lie beyond the padded rows: those are not fetched, their products are never stored).
-                const int t128 = ms * TT::M_TILES;
+                int t128 = ms * TT::M_TILES;
                 int present = p.MS * 4 - t128;
                 if (present > TT::M_TILES) present = TT::M_TILES;
+                if constexpr (GROUPED) {
+                    const int4 item = p.items[t / NT];
+                    t128 = item.y;
+                    present = item.z;
+                }
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -311,6 +341,8 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                 if (acc_round > 0 && !failed && !ptx::mbar_wait(acc_empty, (acc_round - 1) & 1)) fail();
                 tc_fence_after();
                 const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                int present = TT::M_TILES;
+                if constexpr (GROUPED) present = p.items[t / NT].z;
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -323,7 +355,8 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                     for (int mt = 0; mt < TT::M_TILES; mt++)
 #pragma unroll
                         for (int ks = 0; ks < TC_KB / 16; ks++)
-                            tc_mma(tmem_base + (uint32_t)(mt * TT::NCOLS), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096, 2048),
+                            if (!GROUPED || mt < present)
+                                tc_mma(tmem_base + (uint32_t)(mt * TT::NCOLS), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096, 2048),
                                    tc_smem_desc(b_addr + ks * 2 * TT::B_LBO, TT::B_LBO), TT::IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
                     tc_commit(&empty[s]);               // stage reusable once these MMAs have read it
                 }
@@ -365,12 +398,7 @@ __global__ void had_in_tc_kernel(const void* __restrict__ x, int x_bf16, const _
     __half h[4];
 #pragma unroll
     for (int e = 0; e < 4; e++) h[e] = __float2half_rn(v[e] * HAD_SCALE);
-    const int kk = 4 * lane;                               // column inside the 128 block
-    const int kb = kg * 2 + (kk >> 6), c = (kk & 63) >> 3, e0 = kk & 7;
-    const int ms = row / TC_ROWS, mt = (row % TC_ROWS) >> 7, j = (row & 127) >> 3, rr = row & 7;
-    const long long KB = (long long)kgs * 2;
-    const long long off = ((((((long long)ms * KB + kb) * 4 + mt) * 8 + c) * 16 + j) * 8 + rr) * 8 + e0;
-    *reinterpret_cast<uint2*>(xa + s * shard_stride + off) = *reinterpret_cast<uint2*>(h);
+    *reinterpret_cast<uint2*>(xa + s * shard_stride + tc_a_offset(row, kg * 128 + 4 * lane, kgs * 2)) = *reinterpret_cast<uint2*>(h);
 }
 
 template <int K, int FAM, int MT, bool WIDE, bool SPLIT>
@@ -426,6 +454,16 @@ static int tc_set_attr_k()
     if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_MUL1, 2, true>();
     if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_MUL1, 3, false>();
     if (rc == EXL3_OK) rc = tc_set_attr_tile<K, FAM_MUL1, 4, false>();
+    using TN = TcTile<4, false>;
+    if (rc == EXL3_OK)
+        rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_HASH, 4, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TN::SMEM_BYTES));
+    if (rc == EXL3_OK)
+        rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_MUL1, 4, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TN::SMEM_BYTES));
+    using TG = TcTile<TC_GROUPED_MT, true>;
+    if (rc == EXL3_OK)
+        rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_HASH, TC_GROUPED_MT, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TG::SMEM_BYTES));
+    if (rc == EXL3_OK)
+        rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_MUL1, TC_GROUPED_MT, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TG::SMEM_BYTES));
     return rc;
 }
 
@@ -530,6 +568,67 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
         case 6: return launch_tc_k<6>(l, fam, tiling, d->sm_count, st);
         case 7: return launch_tc_k<7>(l, fam, tiling, d->sm_count, st);
         case 8: return launch_tc_k<8>(l, fam, tiling, d->sm_count, st);
+    }
+    return EXL3_ERR_UNSUPPORTED_K;
+}
+
+template <int K>
+static int launch_tc_grouped_k(const GemmTcLaunch& l, int fam, bool wide, int sm_count, cudaStream_t st)
+{
+    if (!wide) {
+        using TN = TcTile<4, false>;
+        if (fam == FAM_HASH) gemm_tc_kernel<K, FAM_HASH, 4, false, false, true><<<sm_count, TN::THREADS, TN::SMEM_BYTES, st>>>(l);
+        else gemm_tc_kernel<K, FAM_MUL1, 4, false, false, true><<<sm_count, TN::THREADS, TN::SMEM_BYTES, st>>>(l);
+        return cuda_status(cudaGetLastError());
+    }
+    using TT = TcTile<TC_GROUPED_MT, true>;
+    if (fam == FAM_HASH) gemm_tc_kernel<K, FAM_HASH, TC_GROUPED_MT, true, false, true><<<sm_count, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
+    else gemm_tc_kernel<K, FAM_MUL1, TC_GROUPED_MT, true, false, true><<<sm_count, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
+    return cuda_status(cudaGetLastError());
+}
+
+// Routed experts with many rows each: out[position, :] = xa[position, :] @ W_inner[expert of the position's block], for
+// the work items of `items` (see GemmTcLaunch).  xa is in the A-operand layout over positions (blocks of 128 rows of one
+// expert, padding rows zero), `cap512` positions per shard; out is [cap][n_total] fp16 in the rotated basis.  wide: the
+// 256-column tiling with 16 decode warps and items of at most TC_GROUPED_MT blocks (column blocks must pair up inside every
+// shard); otherwise 128-column tiles and items of at most 4 blocks.
+int launch_gemm_tc_grouped(const uint32_t* packed, long long expert_stride, int K, int codebook, const int* shard_end_blocks, int n_shards,
+                           int k, int n_total, const __half* xa, int cap512, __half* out, const int4* items, const int* n_items, bool wide,
+                           int* err, cudaStream_t st)
+{
+    const DeviceInfo* d = current_device_info();
+    if (!d) return EXL3_ERR_NOT_INITIALISED;
+    GemmTcLaunch l;
+    memset(&l, 0, sizeof(l));
+    l.packed = packed;
+    l.expert_stride = expert_stride;
+    l.xa = xa;
+    l.out = out;
+    l.err = err;
+    l.rows = cap512;
+    l.KG = k / 128;
+    l.NB = n_total / 128;
+    l.MS = cap512 / TC_ROWS;
+    l.n_total = n_total;
+    l.n_shards = n_shards;
+    for (int s = 0; s < GEMV_MAX_SHARDS; s++) l.shard_end_block[s] = shard_end_blocks[s];
+    l.xa_shard_stride = (long long)cap512 * k;
+    const CodebookConst c = codebook_const(codebook);
+    l.mul = c.mul;
+    l.add = c.add;
+    l.pw = make_pow2();
+    l.ksplit = 1;
+    l.items = items;
+    l.n_items = n_items;
+    const int fam = codebook_family(codebook);
+    switch (K) {
+        case 2: return launch_tc_grouped_k<2>(l, fam, wide, d->sm_count, st);
+        case 3: return launch_tc_grouped_k<3>(l, fam, wide, d->sm_count, st);
+        case 4: return launch_tc_grouped_k<4>(l, fam, wide, d->sm_count, st);
+        case 5: return launch_tc_grouped_k<5>(l, fam, wide, d->sm_count, st);
+        case 6: return launch_tc_grouped_k<6>(l, fam, wide, d->sm_count, st);
+        case 7: return launch_tc_grouped_k<7>(l, fam, wide, d->sm_count, st);
+        case 8: return launch_tc_grouped_k<8>(l, fam, wide, d->sm_count, st);
     }
     return EXL3_ERR_UNSUPPORTED_K;
 }

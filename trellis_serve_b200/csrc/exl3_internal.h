@@ -114,6 +114,32 @@ int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, in
                             cudaStream_t st);
 
 // exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
+// A-operand layout of the tensor-core GEMM in global memory: super tiles of TC_ROWS rows; per reduction block of TC_KB
+// columns four 128-row tiles of 16 KB, each in 8 x 8 fp16 core matrices (k chunk of 8 outermost, then row group of 8).
+constexpr int TC_ROWS = 512;
+constexpr int TC_KB = 64;
+// Element offset of (row, col) for a matrix of KB reduction blocks; col is a multiple of 4, the 4 halves are contiguous.
+__host__ __device__ inline long long tc_a_offset(int row, int col, int KB)
+{
+    const int kb = col >> 6, c = (col & 63) >> 3, e0 = col & 7;
+    const int ms = row / TC_ROWS, mt = (row % TC_ROWS) >> 7, j = (row & 127) >> 3, rr = row & 7;
+    return ((((((long long)ms * KB + kb) * 4 + mt) * 8 + c) * 16 + j) * 8 + rr) * 8 + e0;
+}
+// The grouped instances: the wide tiling where column blocks pair up inside every shard -- 16 decode warps on a 64 x 256 weight
+// block per step (routed experts have few rows each, so the decode bounds the kernel and needs the warps), items of up to
+// TC_GROUPED_MT blocks of 128 rows of one expert -- else 128-column tiles with 8 decode warps and items of up to 4 blocks.
+constexpr int TC_GROUPED_MT = 2;
+int launch_gemm_tc_grouped(const uint32_t* packed, long long expert_stride, int K, int codebook, const int* shard_end_blocks, int n_shards,
+                           int k, int n_total, const __half* xa, int cap512, __half* out, const int4* items, const int* n_items, bool wide,
+                           int* err, cudaStream_t st);
+// exl3_moe_tc.cu: routed experts through the grouped tensor-core GEMM (many rows per expert)
+constexpr int MOE_TC_BLOCK_ROWS = 128;
+size_t moe_tc_capacity(int slots, int num_local);
+size_t moe_tc_workspace_bytes(int slots, int num_local, int hidden, int inter);
+int launch_moe_tc_experts(const void* x, int x_bf16, int top_k, int hidden, int inter, const int* topk_ids, int slots, int num_experts,
+                          const int* expert_map, int num_local, const uint32_t* w13, const __half* suh13, const __half* svh13,
+                          const uint32_t* w2, const __half* suh2, const __half* svh2, int K, int codebook, __half* yd, unsigned char* ws,
+                          cudaStream_t st);
 int gemm_tc_init_device();
 size_t gemm_tc_activation_bytes(int rows, int k, int shards);
 void gemm_tc_set_tiling(int t);             // -1 = choose; 0 = 512 x 128 tiles; 1 = 256 x 256 tiles where the shape allows; 2 = 384 x 128 tiles

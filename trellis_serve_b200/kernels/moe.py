@@ -23,7 +23,10 @@ from .. import _lib
 from .base import BackendStatus
 from .linear import _dtype_code, _ptr, _require_cuda, _stream, prepare_matrix
 
-BLOCK_SIZES = (8,)
+BLOCK_SIZES = (8, 128)
+# Average routed rows per expert from which a class goes through the grouped tensor-core GEMM (128-row blocks, every
+# expert decoded once per up to 512 rows) instead of the grouped GEMV (8-row blocks, decoded once per block).
+TC_ROWS_PER_EXPERT = 16
 _workspace: dict[int, torch.Tensor] = {}
 
 
@@ -36,9 +39,10 @@ def probe() -> BackendStatus:
 
 
 def moe_block_size(tokens: int, top_k: int, num_experts: int) -> int:
-    """Rows per moe block.  The reference picks from a ladder 8..64 by shape (marlin_moe.py:52-57); the grouped GEMV
-    here always works on 8-row blocks, larger groups simply span several blocks."""
-    return BLOCK_SIZES[0]
+    """Rows per moe block.  The reference picks from a ladder 8..64 by T * top_k / E (marlin_moe.py:52-57); here decode-sized
+    batches use the grouped GEMV on 8-row blocks and batches with many rows per expert the grouped tensor-core GEMM on
+    128-row blocks (`run_layer` switches by this value)."""
+    return BLOCK_SIZES[1] if tokens * top_k >= TC_ROWS_PER_EXPERT * num_experts else BLOCK_SIZES[0]
 
 
 def sorted_ids_capacity(tokens: int, top_k: int, num_experts: int, block: int = 8) -> int:
@@ -333,6 +337,8 @@ def _layer_regions(num_experts_per_class: list[int], hidden: int, inter: int, co
                     (f"xf13_{c}", int(lib.exl3_moe_fragment_bytes(cap, hidden, 2, codebook))),
                     (f"xf2_{c}", int(lib.exl3_moe_fragment_bytes(cap, inter, 1, codebook)))]
         gemv = max(gemv, int(lib.exl3_moe_workspace_bytes(cap, 2 * inter)), int(lib.exl3_moe_workspace_bytes(cap, hidden)))
+        if moe_block_size(tokens, top_k, e) == BLOCK_SIZES[1]:
+            regions.append((f"tc{c}", int(lib.exl3_moe_tc_workspace_bytes(slots, e, hidden, inter))))
     return [("gemv", gemv)] + regions       # the GEMV workspace first: its header and counters must stay zero
 
 
@@ -345,7 +351,8 @@ def run_layer(x, topk_weights, topk_ids, pack: MixedPack, out: torch.Tensor, wor
               expert_maps: list[torch.Tensor] | None = None) -> torch.Tensor:
     """One MoE layer (alignment included) that allocates nothing: `workspace` is a zero-filled uint8 tensor of at least
     `layer_workspace_bytes(...)`; `expert_maps` replaces the pack's per-class maps (expert parallelism with an engine's
-    global -> local map composed in).  Same kernels and the same bits as `forward_mixed`."""
+    global -> local map composed in).  Same kernels and the same bits as `forward_mixed` for decode-sized batches; a class
+    whose experts see `TC_ROWS_PER_EXPERT` rows or more on average goes through the grouped tensor-core GEMM."""
     _require_cuda(x, "x")
     lib = _lib.load()
     tokens, hidden = x.shape
@@ -373,6 +380,13 @@ def run_layer(x, topk_weights, topk_ids, pack: MixedPack, out: torch.Tensor, wor
             xf13, xf2 = views[f"xf13_{c}"], views[f"xf2_{c}"]
             cap = sorted_ids.numel() // 4
             K = pk.bits
+            if moe_block_size(tokens, top_k, pk.num_experts) == BLOCK_SIZES[1]:
+                tc = views[f"tc{c}"]
+                tc[:256].zero_()          # this region moves with the token count: its error word starts clean
+                _lib.check(lib.exl3_moe_tc_experts(_ptr(x), _dtype_code(x), tokens, top_k, hidden, inter, _ptr(ids32), emap.numel(), _ptr(emap),
+                                                   pk.num_experts, _ptr(pk.w13), _ptr(pk.suh13), _ptr(pk.svh13), _ptr(pk.w2), _ptr(pk.suh2),
+                                                   _ptr(pk.svh2), K, pk.codebook, _ptr(yd), _ptr(tc), tc.numel(), st), "exl3_moe_tc_experts")
+                continue
             _lib.check(lib.exl3_moe_align_mapped(_ptr(ids32), slots, emap.numel(), _ptr(emap), pk.num_experts, _ptr(sorted_ids), cap,
                                                  _ptr(expert_ids), _ptr(num_post), st), "exl3_moe_align_mapped")
             _lib.check(lib.exl3_moe_had_in(_ptr(x), _dtype_code(x), _ptr(pk.suh13), 2, hidden, top_k, slots, _ptr(sorted_ids), cap,
