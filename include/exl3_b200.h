@@ -143,6 +143,10 @@ exl3_status exl3_linear_prerotated(const uint32_t *packed, int K, int codebook, 
  *                          exl3_attention_scratch_bytes().  suh_next != NULL: a head is one rotation block of the o
  *                          projection's input, so the merge also writes that linear's rotated fragments into `workspace`
  *                          (as exl3_rotate_fragments would from `out`) and exl3_linear_prerotated can follow directly.
+ *   exl3_rope_decode_attention  the two above in one call and two launches instead of three: the attention kernel rotates
+ *                          the queries as it loads them (qkv is left unrotated) and the warp that owns cache slot `*position`
+ *                          rotates the new key into k_cache and copies the new value into v_cache before it reads them; same
+ *                          roundings, same bits.  qkv must be 8-byte aligned.
  * The reference leaves attention to its engine; no counterpart there. */
 size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);
 exl3_status exl3_rope_append(void *qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float *cos_table,
@@ -152,6 +156,11 @@ exl3_status exl3_decode_attention(const void *qkv, int dtype, int rows, int q_he
                                   const void *k_cache, const void *v_cache, int t_max, const int *position, float scale,
                                   void *scratch, size_t scratch_bytes, void *out, const uint16_t *suh_next, int codebook,
                                   void *workspace, size_t workspace_bytes, void *stream);
+exl3_status exl3_rope_decode_attention(const void *qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim,
+                                       const float *cos_table, const float *sin_table, void *k_cache, void *v_cache, int t_max,
+                                       const int *position, float scale, void *scratch, size_t scratch_bytes, void *out,
+                                       const uint16_t *suh_next, int codebook, void *workspace, size_t workspace_bytes,
+                                       void *stream);
 
 /* ---- fused linear for many rows (prefill) on the tcgen05 tensor cores -----------------------------------
  * Same contract as exl3_linear (fused group, dtypes, shard ends); built for hundreds to thousands of rows: the

@@ -152,3 +152,50 @@ def test_two_layer_decode_step_against_a_float64_restatement(attention):
     got = eager.double().cpu().numpy()
     assert np.isfinite(got).all()
     assert orc.rel_norm(got, want) <= 1.5e-2, orc.rel_norm(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("q_heads,kv_heads,pos", [(10, 2, 300), (8, 8, 127), (16, 2, 128), (4, 1, 0)])
+def test_rope_inside_the_attention_kernel_gives_the_bits_of_the_separate_launch(dtype, q_heads, kv_heads, pos):
+    """exl3_rope_decode_attention == exl3_rope_append followed by exl3_decode_attention: output, appended cache slot and the o
+    projection's rotated fragments, bit for bit; positions at the start, at the end of a 128-position chunk and at the start of
+    the next one."""
+    import ctypes
+    import math
+    from trellis_serve_b200 import _lib
+    from trellis_serve_b200.kernels import linear as lin
+    lib, rows, t_max = _lib.load(), 2, 384
+    _lib.init_device(0)
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(pos + q_heads)
+    heads = q_heads + 2 * kv_heads
+    qkv = torch.randn((rows, heads * 128), device=DEV, generator=gen).to(dtype)
+    cache = torch.randn((2, rows, kv_heads, t_max, 128), device=DEV, generator=gen).to(dtype)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, device=DEV, dtype=torch.float32) / 64))
+    ang = torch.arange(t_max, device=DEV, dtype=torch.float32)[:, None] * inv[None]
+    cos_t, sin_t = ang.cos().contiguous(), ang.sin().contiguous()
+    position = torch.tensor([pos], dtype=torch.int32, device=DEV)
+    suh = (torch.randint(0, 2, (q_heads * 128,), device=DEV, generator=gen) * 2 - 1).half()
+    scratch = torch.empty(int(lib.exl3_attention_scratch_bytes(rows, q_heads, kv_heads, t_max)), dtype=torch.uint8, device=DEV)
+    need = int(lib.exl3_linear_workspace_bytes(rows, q_heads * 128, 256, 1))
+    p, st, code, scale = lin._ptr, lin._stream(torch.device(DEV)), lin._dtype_code(qkv), 1.0 / math.sqrt(128)
+    results = []
+    for fused in (False, True):
+        q2, c2 = qkv.clone(), cache.clone()
+        out = torch.empty((rows, q_heads * 128), dtype=dtype, device=DEV)
+        ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
+        if fused:
+            _lib.check(lib.exl3_rope_decode_attention(p(q2), code, rows, q_heads, kv_heads, 128, p(cos_t), p(sin_t), p(c2[0]), p(c2[1]), t_max,
+                                                      p(position), scale, p(scratch), scratch.numel(), p(out), p(suh), 0, p(ws), ws.numel(), st),
+                       "exl3_rope_decode_attention")
+        else:
+            _lib.check(lib.exl3_rope_append(p(q2), code, rows, q_heads, kv_heads, 128, p(cos_t), p(sin_t), p(c2[0]), p(c2[1]), t_max,
+                                            p(position), st), "exl3_rope_append")
+            _lib.check(lib.exl3_decode_attention(p(q2), code, rows, q_heads, kv_heads, 128, p(c2[0]), p(c2[1]), t_max, p(position), scale,
+                                                 p(scratch), scratch.numel(), p(out), p(suh), 0, p(ws), ws.numel(), st), "exl3_decode_attention")
+        torch.cuda.synchronize()
+        results.append((out, c2, ws))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+    assert torch.equal(results[0][2], results[1][2])
+    assert torch.isfinite(results[1][0].float()).all()

@@ -42,6 +42,8 @@ SIGNATURES = {
     "exl3_attention_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_rope_append": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "exl3_decode_attention": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, ctypes.c_float, _vp, _sz, _vp, _vp, _i, _vp, _sz, _vp]),
+    "exl3_rope_decode_attention": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, ctypes.c_float, _vp, _sz, _vp, _vp, _i, _vp, _sz,
+                                        _vp]),
     "exl3_gemm_tc_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_linear_tc": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "exl3_linear_static": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp]),

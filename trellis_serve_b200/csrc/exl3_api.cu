@@ -359,7 +359,7 @@ exl3_status exl3_rmsnorm_rotate(const void* x, void* residual, const void* weigh
     uint32_t* xf = nullptr;
     if (int rc = fragment_region(rows, k, n_shards, workspace, workspace_bytes, &xf)) return rc;
     if (rows == 0 || k == 0) return EXL3_OK;
-    if (!aligned(x, 8) || !aligned(weight, 2) || !aligned(suh_cat, 8) || (residual && !aligned(residual, 8)) || (normed && !aligned(normed, 8)))
+    if (!aligned(x, 8) || !aligned(weight, 8) || !aligned(suh_cat, 8) || (residual && !aligned(residual, 8)) || (normed && !aligned(normed, 8)))
         return EXL3_ERR_BAD_POINTER;
     return launch_rmsnorm_rotate(x, residual, weight, eps, dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, rows, k,
                                  normed, xf, fragment_mode(codebook), (cudaStream_t)stream);
@@ -373,7 +373,7 @@ exl3_status exl3_silu_mul_rotate(const void* gate_up, int dtype, const uint16_t*
     uint32_t* xf = nullptr;
     if (int rc = fragment_region(rows, inter, 1, workspace, workspace_bytes, &xf)) return rc;
     if (rows == 0 || inter == 0) return EXL3_OK;
-    if (!aligned(gate_up, 2) || !aligned(suh, 8) || (act && !aligned(act, 8))) return EXL3_ERR_BAD_POINTER;
+    if (!aligned(gate_up, 8) || !aligned(suh, 8) || (act && !aligned(act, 8))) return EXL3_ERR_BAD_POINTER;
     return launch_silu_mul_rotate(gate_up, dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh), rows, inter, act, xf,
                                   fragment_mode(codebook), (cudaStream_t)stream);
 }
@@ -422,9 +422,10 @@ exl3_status exl3_rope_append(void* qkv, int dtype, int rows, int q_heads, int kv
                               (cudaStream_t)stream);
 }
 
-exl3_status exl3_decode_attention(const void* qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const void* k_cache,
-                                  const void* v_cache, int t_max, const int* position, float scale, void* scratch, size_t scratch_bytes,
-                                  void* out, const uint16_t* suh_next, int codebook, void* workspace, size_t workspace_bytes, void* stream)
+static int attention_common(const void* qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float* cos_table,
+                            const float* sin_table, void* k_cache, void* v_cache, int t_max, const int* position, float scale, void* scratch,
+                            size_t scratch_bytes, void* out, const uint16_t* suh_next, int codebook, void* workspace, size_t workspace_bytes,
+                            void* stream)
 {
     uint32_t* xf = nullptr;
     if (suh_next) {
@@ -434,12 +435,31 @@ exl3_status exl3_decode_attention(const void* qkv, int dtype, int rows, int q_he
     }
     if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (rows < 0 || q_heads < 1 || kv_heads < 1 || head_dim != 128 || t_max < 1 || q_heads % kv_heads) return EXL3_ERR_BAD_SHAPE;
-    if (!aligned(qkv, 2) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(position, 4) || (out && !aligned(out, 8)) || (!out && !suh_next))
+    if (!aligned(qkv, 8) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(position, 4) || (out && !aligned(out, 8)) || (!out && !suh_next))
         return EXL3_ERR_BAD_POINTER;
     if (!aligned(scratch, 16) || scratch_bytes < attention_scratch_bytes(rows, q_heads, kv_heads, t_max)) return EXL3_ERR_WORKSPACE;
-    return launch_decode_attention(qkv, dtype == EXL3_BF16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, position, scale,
-                                   reinterpret_cast<float*>(scratch), out, reinterpret_cast<const __half*>(suh_next), xf,
+    return launch_decode_attention(qkv, dtype == EXL3_BF16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, position, scale, cos_table,
+                                   sin_table, reinterpret_cast<float*>(scratch), out, reinterpret_cast<const __half*>(suh_next), xf,
                                    suh_next ? fragment_mode(codebook) : 0, (cudaStream_t)stream);
+}
+
+exl3_status exl3_decode_attention(const void* qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const void* k_cache,
+                                  const void* v_cache, int t_max, const int* position, float scale, void* scratch, size_t scratch_bytes,
+                                  void* out, const uint16_t* suh_next, int codebook, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return attention_common(qkv, dtype, rows, q_heads, kv_heads, head_dim, nullptr, nullptr, const_cast<void*>(k_cache),
+                            const_cast<void*>(v_cache), t_max, position, scale, scratch, scratch_bytes, out, suh_next, codebook, workspace,
+                            workspace_bytes, stream);
+}
+
+exl3_status exl3_rope_decode_attention(const void* qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float* cos_table,
+                                       const float* sin_table, void* k_cache, void* v_cache, int t_max, const int* position, float scale,
+                                       void* scratch, size_t scratch_bytes, void* out, const uint16_t* suh_next, int codebook,
+                                       void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (!aligned(cos_table, 4) || !aligned(sin_table, 4)) return EXL3_ERR_BAD_POINTER;
+    return attention_common(qkv, dtype, rows, q_heads, kv_heads, head_dim, cos_table, sin_table, k_cache, v_cache, t_max, position, scale,
+                            scratch, scratch_bytes, out, suh_next, codebook, workspace, workspace_bytes, stream);
 }
 
 /* ---- many-row (prefill) fused GEMM on tcgen05 ------------------------------------------------------------- */

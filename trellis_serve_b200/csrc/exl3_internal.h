@@ -109,9 +109,9 @@ int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows
 size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);
 int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads, const float* cos_t, const float* sin_t, void* k_cache,
                        void* v_cache, int t_max, const int* pos, cudaStream_t st);
-int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, const void* k_cache, const void* v_cache,
-                            int t_max, const int* pos, float scale, float* part, void* out, const __half* suh, uint32_t* xf, int mode,
-                            cudaStream_t st);
+int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, void* k_cache, void* v_cache, int t_max,
+                            const int* pos, float scale, const float* cos_t, const float* sin_t, float* part, void* out, const __half* suh,
+                            uint32_t* xf, int mode, cudaStream_t st);
 
 // exl3_gemm_tc.cu ---------------------------------------------------------------------------------------
 // A-operand layout of the tensor-core GEMM in global memory: super tiles of TC_ROWS rows; per reduction block of TC_KB

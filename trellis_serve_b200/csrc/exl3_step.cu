@@ -39,6 +39,20 @@ __device__ __forceinline__ void store_act4(void* p, long long i, const float (&v
     }
 }
 
+// Four consecutive activations (8-byte aligned) as floats.
+__device__ __forceinline__ void load_act4(const void* p, long long i, bool bf16, float (&v)[4])
+{
+    if (bf16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p) + i);
+        const __half2 a = *reinterpret_cast<const __half2*>(&raw.x), c = *reinterpret_cast<const __half2*>(&raw.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
+    }
+}
+
 // One warp, one (shard, row, 128 block): a[e] are activation values already rounded to the activation type.  They are
 // converted to fp16 as the rotation kernel does, scaled by suh, rotated and stored as fragments.
 // mode 1: split-pair fragments (4 words per lane q), mode 2: paired (2 words); layouts of had_in_kernel.
@@ -84,11 +98,18 @@ __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void
 {
     __shared__ float part[STEP_THREADS / 32];
     __shared__ float rstd_s;
-    ptx::grid_launch_dependents();
-    ptx::grid_dependency_wait();
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kgs = k >> 7;
     const bool b = bf16 != 0;
+    // The norm weights are constants: they are fetched while the kernel ahead is still finishing.
+    float wv[STEP_MAX_BLOCKS_PER_WARP][4];
+#pragma unroll
+    for (int j = 0; j < STEP_MAX_BLOCKS_PER_WARP; j++) {
+        const int kg = warp + j * (STEP_THREADS / 32);
+        if (kg < kgs) load_act4(weight, kg * 128 + 4 * lane, b, wv[j]);
+    }
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     float h[STEP_MAX_BLOCKS_PER_WARP][4];
     float ss = 0.f;
 #pragma unroll
@@ -96,15 +117,19 @@ __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void
         const int kg = warp + j * (STEP_THREADS / 32);
         if (kg < kgs) {
             const long long i0 = (long long)row * k + kg * 128 + 4 * lane;
-            float z[4];
+            float z[4], r[4];
+            load_act4(x, i0, b, z);
+            if (residual) {
+                load_act4(residual, i0, b, r);
+#pragma unroll
+                for (int e = 0; e < 4; e++) z[e] = round_act(z[e] + r[e], b);
+                store_act4(residual, i0, z, b);
+            }
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                z[e] = to_f32(x, i0 + e, b);
-                if (residual) z[e] = round_act(z[e] + to_f32(residual, i0 + e, b), b);
                 h[j][e] = z[e];
                 ss += z[e] * z[e];
             }
-            if (residual) store_act4(residual, i0, z, b);
         }
     }
 #pragma unroll
@@ -126,7 +151,7 @@ __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void
             const long long i0 = (long long)row * k + kg * 128 + 4 * lane;
             float a[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) a[e] = round_act(h[j][e] * rstd * to_f32(weight, kg * 128 + 4 * lane + e, b), b);
+            for (int e = 0; e < 4; e++) a[e] = round_act(h[j][e] * rstd * wv[j][e], b);
             if (normed) store_act4(normed, i0, a, b);
             for (int s = 0; s < shards; s++) rotate_store(a, suh + (long long)s * k + kg * 128, xf, mode, s, k >> 4, rows, row, kg, lane);
         }
@@ -145,13 +170,11 @@ __global__ void silu_mul_rotate_kernel(const void* __restrict__ gu, int bf16, co
     if (item >= (long long)rows * kgs) return;
     const int kg = (int)(item % kgs), row = (int)(item / kgs);
     const bool b = bf16 != 0;
-    float a[4];
+    float a[4], gv[4], uv[4];
+    load_act4(gu, (long long)row * 2 * inter + kg * 128 + 4 * lane, b, gv);
+    load_act4(gu, (long long)row * 2 * inter + inter + kg * 128 + 4 * lane, b, uv);
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        const int col = kg * 128 + 4 * lane + e;
-        const float g = to_f32(gu, (long long)row * 2 * inter + col, b), u = to_f32(gu, (long long)row * 2 * inter + inter + col, b);
-        a[e] = round_act(g / (1.0f + __expf(-g)) * u, b);
-    }
+    for (int e = 0; e < 4; e++) a[e] = round_act(gv[e] / (1.0f + __expf(-gv[e])) * uv[e], b);
     if (act) store_act4(act, (long long)row * inter + kg * 128 + 4 * lane, a, b);
     rotate_store(a, suh + kg * 128, xf, mode, 0, inter >> 4, rows, row, kg, lane);
 }
@@ -232,11 +255,15 @@ __global__ void rope_append_kernel(void* __restrict__ qkv, int bf16, int rows, i
 // Split-KV decode attention.  grid = (splits, kv_heads, rows); a CTA attends positions [split * ATT_CHUNK ...) of one KV
 // head for its G query heads: every lane owns ONE position (reads its key row, G dot products against the queries held in
 // shared memory, no shuffles), the warp then walks its 32 positions for the values (each lane four of the 128 columns).
-// Partial results (running maximum, normaliser, G x 128 weighted sums per warp) are merged by attention_merge_kernel.
+// Partial results (running maximum, normaliser, G x 128 weighted sums per split) are merged by attention_merge_kernel.
+// With cos_t / sin_t the kernel also does what rope_append_kernel does, with the same roundings: the queries are rotated as
+// they are loaded (qkv itself is left as it is), and the warp that owns cache position `pos` rotates the new key into the
+// cache and copies the new value there before it reads them back like any other position.
 template <int G>
 __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const void* __restrict__ qkv, int bf16, int q_heads, int kv_heads,
-                                                                           const void* __restrict__ k_cache, const void* __restrict__ v_cache,
-                                                                           int t_max, const int* __restrict__ pos_ptr, float scale,
+                                                                           void* k_cache, void* v_cache, int t_max,
+                                                                           const int* __restrict__ pos_ptr, float scale,
+                                                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                                            float* __restrict__ part)
 {
     __shared__ float qs[G][ATT_D];
@@ -244,14 +271,45 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     ptx::grid_dependency_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int T = *pos_ptr + 1;                                   // valid cache positions
+    const int pos = *pos_ptr;
+    const int T = pos + 1;                                        // valid cache positions
     const int heads = q_heads + 2 * kv_heads;
     const bool b = bf16 != 0;
-    for (int e = threadIdx.x; e < G * ATT_D; e += ATT_WARPS * 32)
-        qs[e / ATT_D][e % ATT_D] = to_f32(qkv, ((long long)row * heads + kvh * G + e / ATT_D) * ATT_D + e % ATT_D, b) * scale;
+    if (cos_t) {
+        for (int e = threadIdx.x; e < G * (ATT_D / 2); e += ATT_WARPS * 32) {
+            const int g = e / (ATT_D / 2), i = e % (ATT_D / 2);
+            const long long at = ((long long)row * heads + kvh * G + g) * ATT_D;
+            const float x1 = to_f32(qkv, at + i, b), x2 = to_f32(qkv, at + i + 64, b);
+            const float c = cos_t[(long long)pos * 64 + i], sn = sin_t[(long long)pos * 64 + i];
+            qs[g][i] = round_act(x1 * c - x2 * sn, b) * scale;
+            qs[g][i + 64] = round_act(x2 * c + x1 * sn, b) * scale;
+        }
+        if (split == pos / ATT_CHUNK && warp == (pos % ATT_CHUNK) / 32) {
+            const long long kat = ((long long)row * heads + q_heads + kvh) * ATT_D, vat = kat + (long long)kv_heads * ATT_D;
+            const long long cat = (((long long)row * kv_heads + kvh) * t_max + pos) * ATT_D;
+            for (int i = lane; i < 64; i += 32) {
+                const float x1 = to_f32(qkv, kat + i, b), x2 = to_f32(qkv, kat + i + 64, b);
+                const float c = cos_t[(long long)pos * 64 + i], sn = sin_t[(long long)pos * 64 + i];
+                const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+                if (b) {
+                    reinterpret_cast<__nv_bfloat16*>(k_cache)[cat + i] = __float2bfloat16_rn(y1);
+                    reinterpret_cast<__nv_bfloat16*>(k_cache)[cat + i + 64] = __float2bfloat16_rn(y2);
+                } else {
+                    reinterpret_cast<__half*>(k_cache)[cat + i] = __float2half_rn(y1);
+                    reinterpret_cast<__half*>(k_cache)[cat + i + 64] = __float2half_rn(y2);
+                }
+            }
+            reinterpret_cast<uint2*>(reinterpret_cast<unsigned char*>(v_cache) + cat * 2)[lane] =
+                reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(qkv) + vat * 2)[lane];
+            __syncwarp();                                         // the warp's own stores are visible to its loads below
+        }
+    } else {
+        for (int e = threadIdx.x; e < G * ATT_D; e += ATT_WARPS * 32)
+            qs[e / ATT_D][e % ATT_D] = to_f32(qkv, ((long long)row * heads + kvh * G + e / ATT_D) * ATT_D + e % ATT_D, b) * scale;
+    }
     __syncthreads();
     const int splits = gridDim.x;
-    float* out = part + ((((long long)row * kv_heads + kvh) * splits + split) * ATT_WARPS + warp) * (G * ATT_PART);
+    float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
     const int t = split * ATT_CHUNK + warp * 32 + lane;
     const long long rowbase = (((long long)row * kv_heads + kvh) * t_max) * ATT_D;
     float sc[G];
@@ -259,9 +317,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     for (int g = 0; g < G; g++) sc[g] = 0.f;
     if (t < T) {
         const uint4* kr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(k_cache) + (rowbase + (long long)t * ATT_D) * 2);
-#pragma unroll 8
-        for (int j = 0; j < 16; j++) {                             // 16 x 8 halves, eight loads in flight
-            const uint4 w = kr[j];
+        uint4 kw[16];                                             // the whole key row in flight at once
+#pragma unroll
+        for (int j = 0; j < 16; j++) kw[j] = kr[j];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const uint4 w = kw[j];
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
             for (int h2 = 0; h2 < 4; h2++) {
@@ -301,12 +362,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     const int t0 = split * ATT_CHUNK + warp * 32;
     const int n = T - t0 < 32 ? T - t0 : 32;                      // warp-uniform
     const unsigned char* vbase = reinterpret_cast<const unsigned char*>(v_cache) + (rowbase + (long long)t0 * ATT_D + 4 * lane) * 2;
-    for (int j0 = 0; j0 < n; j0 += 8) {                           // eight value rows in flight per warp
-        uint2 w[8];
+    for (int j0 = 0; j0 < n; j0 += 16) {                          // sixteen value rows in flight per warp
+        uint2 w[16];
 #pragma unroll
-        for (int u = 0; u < 8; u++) w[u] = (j0 + u < n) ? *reinterpret_cast<const uint2*>(vbase + (long long)(j0 + u) * ATT_D * 2) : make_uint2(0u, 0u);
+        for (int u = 0; u < 16; u++) w[u] = (j0 + u < n) ? *reinterpret_cast<const uint2*>(vbase + (long long)(j0 + u) * ATT_D * 2) : make_uint2(0u, 0u);
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < 16; u++) {
             float v[4];
             if (b) {
                 const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w[u].x), c = *reinterpret_cast<const __nv_bfloat162*>(&w[u].y);
@@ -323,14 +384,48 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
             }
         }
     }
+    // The four warps' partial results are merged inside the CTA (fixed warp order), so one partial per split goes out.
+    __shared__ __align__(16) float red[ATT_WARPS][G][ATT_PART];
+    __shared__ float wgt[G][ATT_WARPS];
 #pragma unroll
     for (int g = 0; g < G; g++) {
-        float* o = out + g * ATT_PART;
-        *reinterpret_cast<float4*>(o + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        *reinterpret_cast<float4*>(&red[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
         if (lane == 0) {
-            o[ATT_D] = n > 0 ? m[g] : -INFINITY;
-            o[ATT_D + 1] = n > 0 ? l[g] : 0.f;
+            red[warp][g][ATT_D] = n > 0 ? m[g] : -INFINITY;
+            red[warp][g][ATT_D + 1] = n > 0 ? l[g] : 0.f;
         }
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) mx = fmaxf(mx, red[w][g][ATT_D]);
+        float den = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float mw = red[w][g][ATT_D];
+            const float f = mw == -INFINITY ? 0.f : __expf(mw - mx);
+            wgt[g][w] = f;
+            den += f * red[w][g][ATT_D + 1];
+        }
+        out[g * ATT_PART + ATT_D] = mx;
+        out[g * ATT_PART + ATT_D + 1] = den;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * (ATT_D / 4); e += ATT_WARPS * 32) {
+        const int g = e / (ATT_D / 4), c = (e % (ATT_D / 4)) * 4;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float f = wgt[g][w];
+            const float4 a = *reinterpret_cast<const float4*>(&red[w][g][c]);
+            sum.x += f * a.x;
+            sum.y += f * a.y;
+            sum.z += f * a.z;
+            sum.w += f * a.w;
+        }
+        *reinterpret_cast<float4*>(out + g * ATT_PART + c) = sum;
     }
 }
 
@@ -349,18 +444,37 @@ __global__ void attention_merge_kernel(const float* __restrict__ part, int rows,
     const int kvh = qh / G, g = qh % G;
     const float* base = part + (((long long)row * kv_heads + kvh) * parts) * (G * ATT_PART) + g * ATT_PART;
     const long long stride = (long long)G * ATT_PART;
-    float mx = -INFINITY;
-    for (int s = 0; s < parts; s++) mx = fmaxf(mx, base[s * stride + ATT_D]);
-    float num[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
-    for (int s = 0; s < parts; s++) {
-        const float ms = base[s * stride + ATT_D];
-        const float w = ms == -INFINITY ? 0.f : __expf(ms - mx);
-        const float4 a = *reinterpret_cast<const float4*>(base + s * stride + 4 * lane);
-        num[0] += w * a.x;
-        num[1] += w * a.y;
-        num[2] += w * a.z;
-        num[3] += w * a.w;
-        den += w * base[s * stride + ATT_D + 1];
+    // Sixteen partials per round of loads (one round up to 2048 cache positions), added in split order under a running
+    // maximum: the same bits every time.
+    float mx = -INFINITY, num[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
+    for (int s0 = 0; s0 < parts; s0 += 16) {
+        float4 a[16];
+        float ms[16], ls[16];
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            const bool in = s0 + u < parts;
+            const float* ps = base + (long long)(in ? s0 + u : s0) * stride;
+            a[u] = *reinterpret_cast<const float4*>(ps + 4 * lane);
+            ms[u] = in ? ps[ATT_D] : -INFINITY;
+            ls[u] = ps[ATT_D + 1];
+        }
+        float bm = mx;
+#pragma unroll
+        for (int u = 0; u < 16; u++) bm = fmaxf(bm, ms[u]);
+        const float keep = mx == -INFINITY ? 0.f : __expf(mx - bm);   // rescale what earlier rounds added
+        mx = bm;
+        den *= keep;
+#pragma unroll
+        for (int e = 0; e < 4; e++) num[e] *= keep;
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            const float w = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - mx);
+            num[0] += w * a[u].x;
+            num[1] += w * a[u].y;
+            num[2] += w * a[u].z;
+            num[3] += w * a[u].w;
+            den += w * ls[u];
+        }
     }
     float y[4];
 #pragma unroll
@@ -373,7 +487,7 @@ size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)
 {
     const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
     const int G = q_heads / (kv_heads > 0 ? kv_heads : 1);
-    return (size_t)rows * kv_heads * splits * ATT_WARPS * G * ATT_PART * sizeof(float);
+    return (size_t)rows * kv_heads * splits * G * ATT_PART * sizeof(float);
 }
 
 int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads, const float* cos_t, const float* sin_t, void* k_cache,
@@ -386,30 +500,30 @@ int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads,
 }
 
 template <int G>
-static int launch_attention_g(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, const void* k_cache, const void* v_cache,
-                              int t_max, const int* pos, float scale, float* part, void* out, const __half* suh, uint32_t* xf, int mode,
-                              cudaStream_t st)
+static int launch_attention_g(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, void* k_cache, void* v_cache, int t_max,
+                              const int* pos, float scale, const float* cos_t, const float* sin_t, float* part, void* out, const __half* suh,
+                              uint32_t* xf, int mode, cudaStream_t st)
 {
     const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
     int rc = launch_chained(decode_attention_kernel<G>, dim3(splits, kv_heads, rows), dim3(ATT_WARPS * 32), 0, st, qkv, bf16, q_heads, kv_heads,
-                            k_cache, v_cache, t_max, pos, scale, part);
+                            k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part);
     if (rc) return rc;
     return launch_chained(attention_merge_kernel, dim3((unsigned)((rows * q_heads + 3) / 4)), dim3(128), 0, st, static_cast<const float*>(part), rows,
-                          q_heads, kv_heads, G, splits * ATT_WARPS, out, bf16, suh, xf, mode);
+                          q_heads, kv_heads, G, splits, out, bf16, suh, xf, mode);
 }
 
-int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, const void* k_cache, const void* v_cache,
-                            int t_max, const int* pos, float scale, float* part, void* out, const __half* suh, uint32_t* xf, int mode,
-                            cudaStream_t st)
+int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, void* k_cache, void* v_cache, int t_max,
+                            const int* pos, float scale, const float* cos_t, const float* sin_t, float* part, void* out, const __half* suh,
+                            uint32_t* xf, int mode, cudaStream_t st)
 {
     if (rows == 0) return EXL3_OK;
     if (kv_heads < 1 || q_heads % kv_heads) return EXL3_ERR_BAD_SHAPE;
     switch (q_heads / kv_heads) {
-        case 1: return launch_attention_g<1>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
-        case 2: return launch_attention_g<2>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
-        case 4: return launch_attention_g<4>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
-        case 5: return launch_attention_g<5>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
-        case 8: return launch_attention_g<8>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, part, out, suh, xf, mode, st);
+        case 1: return launch_attention_g<1>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part, out, suh, xf, mode, st);
+        case 2: return launch_attention_g<2>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part, out, suh, xf, mode, st);
+        case 4: return launch_attention_g<4>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part, out, suh, xf, mode, st);
+        case 5: return launch_attention_g<5>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part, out, suh, xf, mode, st);
+        case 8: return launch_attention_g<8>(qkv, bf16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part, out, suh, xf, mode, st);
     }
     return EXL3_ERR_BAD_SHAPE;
 }

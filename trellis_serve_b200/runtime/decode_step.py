@@ -119,7 +119,7 @@ class DecodeStep:
         self.graph: torch.cuda.CUDAGraph | None = None
         self.linear_launches = s.layers * 4
         self.fused_launches = s.layers * (3 if attention == "library" else 4)   # rmsnorm_rotate x2, silu_mul_rotate (+ rotation ahead of o)
-        self.attention_launches = s.layers * 3 if attention == "library" else None
+        self.attention_launches = s.layers * 2 if attention == "library" else None   # rope + attention, merge
 
     # ---- bytes
     @property
@@ -146,14 +146,11 @@ class DecodeStep:
             lib, p, st = _lib.load(), lin._ptr, lin._stream(self.device)
             cache, code = self.kv[layer], lin._dtype_code(self.qkv)
             with torch.cuda.device(self.device):
-                _lib.check(lib.exl3_rope_append(p(self.qkv), code, self.rows, self.q_heads, self.kv_heads, s.head_dim, p(self.cos_table),
-                                                p(self.sin_table), p(cache[0]), p(cache[1]), self.context + 1, p(self.position), st),
-                           "exl3_rope_append")
-                _lib.check(lib.exl3_decode_attention(p(self.qkv), code, self.rows, self.q_heads, self.kv_heads, s.head_dim, p(cache[0]),
-                                                     p(cache[1]), self.context + 1, p(self.position), 1.0 / math.sqrt(s.head_dim),
-                                                     p(self.att_scratch), self.att_scratch.numel(), p(self.attn), p(suh_next),
-                                                     self.codebook, p(self.workspace), self.workspace.numel(), st),
-                           "exl3_decode_attention")
+                _lib.check(lib.exl3_rope_decode_attention(p(self.qkv), code, self.rows, self.q_heads, self.kv_heads, s.head_dim,
+                                                          p(self.cos_table), p(self.sin_table), p(cache[0]), p(cache[1]), self.context + 1,
+                                                          p(self.position), 1.0 / math.sqrt(s.head_dim), p(self.att_scratch),
+                                                          self.att_scratch.numel(), p(self.attn), p(suh_next), self.codebook,
+                                                          p(self.workspace), self.workspace.numel(), st), "exl3_rope_decode_attention")
             return suh_next is not None
         qh = self._rope(self.qkv[:, :q], self.q_heads).unsqueeze(2)                        # [rows, q heads, 1, d]
         kh = self._rope(self.qkv[:, q:q + kv], self.kv_heads)
