@@ -132,6 +132,16 @@ exl3_status exl3_linear_prerotated(const uint32_t *packed, int K, int codebook, 
                                    size_t workspace_bytes, void *const *peer_regions, int rank, int world, size_t max_elems,
                                    int *state, void *stream);
 
+/* A down projection fed straight from the gate | up output: y = linear(fp16(silu(gate) * up)) with gate_up [rows, 2k] in
+ * x_dtype, suh [k], n_shards = 1.  Up to two rows the activation is computed inside the GEMV's own input rotation (one launch,
+ * no activation buffer); above that the library runs the activation kernel ahead of it.  Same bits as exl3_silu_mul_rotate
+ * followed by exl3_linear_prerotated.  The exchange arguments are those of exl3_linear_prerotated (world <= 1: none).
+ * The reference's engine runs its activation kernel between the two launches; no counterpart there. */
+exl3_status exl3_glu_linear(const void *gate_up, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh,
+                            const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
+                            int y_dtype, void *workspace, size_t workspace_bytes, void *const *peer_regions, int rank, int world,
+                            size_t max_elems, int *state, void *stream);
+
 /* The attention side of the same step (not quantized arithmetic; here so that a step is a handful of launches per layer):
  *   exl3_rope_append       qkv [rows, (q_heads + 2 kv_heads) * 128] holds q | k | v of one new token per row.  Rotary
  *                          embedding ("rotate half": pairs (i, i + 64)) with cos_table / sin_table [positions, 64] fp32 at

@@ -69,6 +69,12 @@ def test_silu_mul_rotation_feeds_the_down_projection(rows, dtype):
     want = torch.nn.functional.silu(gu[:, :inter].float()) * gu[:, inter:].float()
     assert float((act.float() - want).abs().max()) <= (3e-2 if dtype == torch.bfloat16 else 4e-3)
     assert torch.equal(out.view(torch.int16), lin.run(act, packed, suh, svh, ends, cb).view(torch.int16))
+    # the same projection fed straight from gate | up: the activation inside the GEMV's own rotation (up to two rows) or the
+    # activation kernel ahead of it (more rows) -- the same bits either way
+    out2 = torch.full_like(out, float("nan"))
+    lin.run_glu(gu, packed, suh.view(-1), svh, cb, out2, ws)
+    assert torch.equal(out2.view(torch.int16), out.view(torch.int16))
+    lin.device_error(DEV)
 
 
 def _ref_linear(x64, packed, suh, svh, K, cb, col0, n):

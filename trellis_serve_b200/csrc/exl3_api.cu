@@ -178,7 +178,7 @@ size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards)
 static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor, const uint32_t* packed, int K, int codebook,
                          const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k,
                          int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated,
-                         const TpExchange* tp = nullptr, bool prerotated = false)
+                         const TpExchange* tp = nullptr, bool prerotated = false, bool glu = false)
 {
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (rows < 0) return EXL3_ERR_BAD_SHAPE;
@@ -235,14 +235,18 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
             }
         } else {
             // Up to two rows: the GEMV rotates its own input (one launch); otherwise the rotation kernel runs ahead of it.
-            const unsigned char* xr = reinterpret_cast<const unsigned char*>(x) + (size_t)r0 * k * esz;
+            // glu: x is gate | up with rows of 2k values and the input proper is silu(gate) * up.
+            const unsigned char* xr = reinterpret_cast<const unsigned char*>(x) + (size_t)r0 * (glu ? 2 * k : k) * esz;
             a.x = xr;
             a.suh = reinterpret_cast<const __half*>(suh_cat);
             a.x_bf16 = x_dtype == EXL3_BF16;
+            a.x_glu = glu ? 1 : 0;
             if (!gemv_rotates_input(a)) {
                 a.x = nullptr;
-                rc = launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
-                                   const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
+                rc = glu ? launch_silu_mul_rotate(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), r, k, nullptr,
+                                                  const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st)
+                         : launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
+                                         const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
                 if (rc) return rc;
             }
         }
@@ -378,20 +382,14 @@ exl3_status exl3_silu_mul_rotate(const void* gate_up, int dtype, const uint16_t*
                                   fragment_mode(codebook), (cudaStream_t)stream);
 }
 
-exl3_status exl3_linear_prerotated(const uint32_t* packed, int K, int codebook, const uint16_t* svh_cat, const int* shard_ends,
-                                   int n_shards, int rows, int k, int n_total, void* y, int y_dtype, void* workspace,
-                                   size_t workspace_bytes, void* const* peer_regions, int rank, int world, size_t max_elems, int* state,
-                                   void* stream)
+static int make_exchange(TpExchange& tp, void* const* peer_regions, int rank, int world, size_t max_elems, int* state, int rows, int n_total,
+                         int y_dtype)
 {
-    if (world <= 1)
-        return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
-                             y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, true);
     if (world > TP_MAX_WORLD || rank < 0 || rank >= world) return EXL3_ERR_BAD_SHAPE;
     if (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
     const size_t slot_bytes = (max_elems * 4 + 255) & ~(size_t)255;
     if ((size_t)(rows < 0 ? 0 : rows) * (size_t)(n_total < 0 ? 0 : n_total) > max_elems || slot_bytes > 0xFFFFFFFFu) return EXL3_ERR_BAD_SHAPE;
     if (!peer_regions || !state || !aligned(state, 4)) return EXL3_ERR_BAD_POINTER;
-    TpExchange tp;
     memset(&tp, 0, sizeof(tp));
     for (int r = 0; r < world; r++) {
         if (!aligned(peer_regions[r], 256)) return EXL3_ERR_BAD_POINTER;
@@ -401,8 +399,37 @@ exl3_status exl3_linear_prerotated(const uint32_t* packed, int K, int codebook, 
     tp.world = world;
     tp.slot_bytes = (unsigned int)slot_bytes;
     tp.state = state;
+    return EXL3_OK;
+}
+
+exl3_status exl3_linear_prerotated(const uint32_t* packed, int K, int codebook, const uint16_t* svh_cat, const int* shard_ends,
+                                   int n_shards, int rows, int k, int n_total, void* y, int y_dtype, void* workspace,
+                                   size_t workspace_bytes, void* const* peer_regions, int rank, int world, size_t max_elems, int* state,
+                                   void* stream)
+{
+    if (world <= 1)
+        return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
+                             y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, true);
+    TpExchange tp;
+    if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
     return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
                          y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, true);
+}
+
+exl3_status exl3_glu_linear(const void* gate_up, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh,
+                            const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y, int y_dtype,
+                            void* workspace, size_t workspace_bytes, void* const* peer_regions, int rank, int world, size_t max_elems,
+                            int* state, void* stream)
+{
+    if (n_shards != 1) return EXL3_ERR_BAD_SHAPE;               // one input, one sign vector: a down projection is not a fused group
+    if (rows > 0 && !aligned(gate_up, 8)) return EXL3_ERR_BAD_POINTER;
+    if (world <= 1)
+        return linear_common(gate_up, x_dtype, nullptr, packed, K, codebook, suh, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
+                             workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, false, true);
+    TpExchange tp;
+    if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
+    return linear_common(gate_up, x_dtype, nullptr, packed, K, codebook, suh, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
+                         workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, false, true);
 }
 
 size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)

@@ -64,6 +64,22 @@ __device__ __forceinline__ float gemv_load_x(const void* p, long long idx, bool 
     return __half2float(reinterpret_cast<const __half*>(p)[idx]);
 }
 
+// The same for a down projection fed straight from gate | up (row stride 2k): the activation silu(gate) * up, rounded to the
+// activation type as the stand-alone activation kernel stores it, then taken as fp16.
+__device__ __forceinline__ float gemv_load_glu(const void* p, long long idx, int k, bool bf16)
+{
+    float g, u;
+    if (bf16) {
+        g = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
+        u = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx + k]);
+    } else {
+        g = __half2float(reinterpret_cast<const __half*>(p)[idx]);
+        u = __half2float(reinterpret_cast<const __half*>(p)[idx + k]);
+    }
+    const float act = g / (1.0f + __expf(-g)) * u;
+    return __half2float(__float2half_rn(bf16 ? __bfloat162float(__float2bfloat16_rn(act)) : act));
+}
+
 // Row-parallel shard: 4 consecutive columns (index o) of one output row are a partial sum.  They go, rounded to the
 // output type and tagged with the call number, into this rank's slot at every peer (single 64-bit peer stores); then
 // the same words of all ranks are awaited here (bounded), added in rank order in fp32 and rounded once: the bits a

@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                     int s = 0;
                     while (s < p.a.n_shards - 1 && unb >= p.a.shard_end_blocks[s]) s++;
                     const long long col = (long long)ukg * 128 + 4 * lane;
-                    xi[b] = (long long)row * p.a.k + col;
+                    xi[b] = (long long)row * (p.a.x_glu ? 2 * p.a.k : p.a.k) + col;
 #pragma unroll
                     for (int e = 0; e < 4; e++) v[b][e] = __half2float(p.a.suh[(long long)s * p.a.k + col + e]);
                 }
@@ -318,7 +318,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             for (int b = 0; b < BATCH; b++) {
                 if (it0 + GEMV_CONSUMER_WARPS * b < items) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) v[b][e] *= gemv_load_x(p.a.x, xi[b] + e, bf16);
+                    for (int e = 0; e < 4; e++)
+                        v[b][e] *= p.a.x_glu ? gemv_load_glu(p.a.x, xi[b] + e, p.a.k, bf16) : gemv_load_x(p.a.x, xi[b] + e, bf16);
                 }
             }
 #pragma unroll

@@ -64,6 +64,7 @@ struct GemvArgs {
     const void* x;              // in-kernel rotation (rows <= 2): raw activations [rows, k], else nullptr
     const __half* suh;          //   and the input sign vectors [n_shards][k]
     int x_bf16;
+    int x_glu;                  // x is gate | up [rows, 2k]: the input is silu(gate) * up (a down projection's activation)
     int xf_staged;              // rows <= 2 without x: the fragments in xf are copied to shared memory once (bulk copies)
                                 //   instead of being read from global memory tile by tile
     const __half* svh;          // [n_total]; unused when rotated

@@ -297,6 +297,27 @@ def run_prerotated(rows: int, b: torch.Tensor, svh_cat: torch.Tensor, shard_ends
     return out
 
 
+def run_glu(gate_up: torch.Tensor, b: torch.Tensor, suh: torch.Tensor, svh_cat: torch.Tensor, codebook: int, out: torch.Tensor,
+            workspace: torch.Tensor | None = None, exchange=None) -> torch.Tensor:
+    """Down projection of silu(gate) * up straight from `gate_up` [rows, 2k]: up to two rows the activation is computed inside
+    the GEMV's own input rotation (one launch, no activation buffer).  `exchange` as in `run_prerotated`."""
+    _require_cuda(gate_up, "gate_up")
+    lib = _lib.load()
+    _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
+    k, n_total, K = _geometry(b)
+    rows = gate_up.shape[0]
+    if gate_up.shape[1] != 2 * k:
+        raise ValueError(f"gate_up has {gate_up.shape[1]} columns, the matrix wants 2 x {k}")
+    ws = _own_or_given(workspace, b.device, workspace_bytes(rows, k, n_total, 1), _workspace)
+    ex = exchange if exchange is not None and exchange.world > 1 else None
+    with torch.cuda.device(b.device):
+        _lib.check(lib.exl3_glu_linear(_ptr(gate_up), _dtype_code(gate_up), _ptr(b), K, codebook, _ptr(suh), _ptr(svh_cat), _lib.int_array([]), 1,
+                                       rows, k, n_total, _ptr(out), _dtype_code(out, True), _ptr(ws), ws.numel(),
+                                       ex.peer_regions if ex else None, ex.rank if ex else 0, ex.world if ex else 1,
+                                       ex.max_elems if ex else 0, _ptr(ex.state) if ex else None, _stream(b.device)), "exl3_glu_linear")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # Building blocks (caller-owned buffers, rotated-basis product for reading decoded weights out, single matrices)
 

@@ -4,13 +4,13 @@
                 q|k|v = EXL3(a);  RoPE(q, k);  KV cache append;  attention over the cache
                 o = EXL3(attention)                             -> rotation launch, then the GEMV
                 residual += o;  a = RMSNorm(residual)           -> fused with the input rotation of gate|up
-                g|u = EXL3(a);  act = SiLU(g) * u               -> fused with the input rotation of down    (silu_mul_rotate)
-                h = EXL3(act)
+                g|u = EXL3(a);  act = SiLU(g) * u               -> computed inside down's own input rotation (glu linear; from three
+                h = EXL3(act)                                      rows up: silu_mul_rotate ahead of the GEMV)
 
 Every linear is ONE decode-GEMV launch whose activations were rotated by the kernel ahead of it; rotary embedding, cache
 append and attention are stock torch (`scaled_dot_product_attention`): they are not part of the quantized-linear path and
-their bytes (the KV read) are reported separately.  `attention="library"` (default) runs the library's own three small
-kernels for that part (RoPE + cache append, split-KV attention, merge); `attention="torch"` keeps the stock torch ops.  The whole step is captured in one CUDA graph, as an engine captures
+their bytes (the KV read) are reported separately.  `attention="library"` (default) runs the library's own two small
+kernels for that part (RoPE + cache append + split-KV attention, merge); `attention="torch"` keeps the stock torch ops.  The whole step is captured in one CUDA graph, as an engine captures
 it (cuda/src/sglang_exl3/sglang_glue/moe.py:202-213 warms for that purpose; cuda/src/sglang_exl3/tools/decode_microbench.py
 :27-41 times launches the same way).
 
@@ -118,7 +118,8 @@ class DecodeStep:
         self.qkv, self.attn, self.o_out, self.gu, self.out = mk(q + 2 * kv), mk(q), mk(h), mk(2 * f), mk(h)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.linear_launches = s.layers * 4
-        self.fused_launches = s.layers * (3 if attention == "library" else 4)   # rmsnorm_rotate x2, silu_mul_rotate (+ rotation ahead of o)
+        glu = 0 if rows <= 2 else 1                                   # the activation kernel runs only from three rows up
+        self.fused_launches = s.layers * ((2 if attention == "library" else 3) + glu)   # rmsnorm_rotate x2 (+ rotation ahead of o)
         self.attention_launches = s.layers * 2 if attention == "library" else None   # rope + attention, merge
 
     # ---- bytes
@@ -180,8 +181,7 @@ class DecodeStep:
             self._reduce(self.o_out)
             lin.rmsnorm_rotate(self.o_out, self.residual, norms[1], self.shape.eps, gu.suh, cb, ws)
             lin.run_prerotated(rows, gu.packed, gu.svh, gu.ends, cb, self.gu, ws)
-            lin.silu_mul_rotate(self.gu, down.suh, cb, ws)
-            lin.run_prerotated(rows, down.packed, down.svh, down.ends, cb, self.h, ws, exchange=ex)
+            lin.run_glu(self.gu, down.packed, down.suh, down.svh, cb, self.h, ws, exchange=ex)
             self._reduce(self.h)
             h = self.h
         self.out.copy_(torch.nn.functional.rms_norm((self.residual + h).float(), (self.shape.hidden,), self.final_norm.float(),
