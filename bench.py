@@ -476,7 +476,9 @@ def run_step(args) -> None:
 def tp_check(dev, rank: int, world: int, reducer, dist) -> dict:
     """Outside the timed region, N > 1: one row-parallel linear (17408 -> 5120, K = 3, every rank slices ITS rows out of the
     same seeded matrix) summed three ways -- exchange fused into the kernel, the library's stand-alone all-reduce, NCCL --
-    and compared with each other and with the unsharded linear computed on every rank."""
+    and compared with each other, with the ranks' rounded partial results added on the host side of the check in rank order
+    in fp32 and rounded once (what the exchange promises, bit for bit) and with the unsharded linear computed on every rank.
+    NCCL adds in its own order with fp16 intermediates, so beyond two ranks it may differ from that sum by an ulp."""
     import torch
     from trellis_serve_b200.kernels import linear as lin
     from trellis_serve_b200.runtime.layerset import random_packed, random_signs
@@ -495,15 +497,22 @@ def tp_check(dev, rank: int, world: int, reducer, dist) -> dict:
     y_fused = lin.run(xs, shard, suhs, svh, [], cb, exchange=reducer) if reducer is not None else None
     y_peer = lin.run(xs, shard, suhs, svh, [], cb)
     y_nccl = y_peer.clone()
+    parts = [torch.empty_like(y_peer) for _ in range(world)]
+    dist.all_gather(parts, y_peer)
+    expected = parts[0].float()
+    for part in parts[1:]:
+        expected = expected + part.float()
+    expected = expected.half()
     if reducer is not None:
         reducer(y_peer)
     dist.all_reduce(y_nccl)
     torch.cuda.synchronize(dev)
     rms = float(whole.pow(2).mean().sqrt())
     res = {"shape": f"{k}x{n} K={K}", "max_rel_nccl_vs_unsharded": float((y_nccl.float() - whole).abs().max()) / rms}
-    flags = torch.ones(2, dtype=torch.int32, device=dev)
+    flags = torch.ones(3, dtype=torch.int32, device=dev)
     if reducer is not None:
         flags[0] = int(torch.equal(y_fused.view(torch.int16), y_peer.view(torch.int16)))
+        flags[2] = int(torch.equal(y_fused.view(torch.int16), expected.view(torch.int16)))
         res["max_rel_vs_nccl"] = float((y_fused.float() - y_nccl.float()).abs().max()) / rms
         gathered = [torch.empty_like(y_fused) for _ in range(world)]
         dist.all_gather(gathered, y_fused)
@@ -516,6 +525,7 @@ def tp_check(dev, rank: int, world: int, reducer, dist) -> dict:
         res["max_rel_vs_nccl"] = worst_nccl
         res["fused_eq_peer"] = bool(flags[0].item())
         res["same_bits_on_every_rank"] = bool(flags[1].item())
+        res["fused_eq_rank_order_fp32_sum"] = bool(flags[2].item())
     del full, shard
     torch.cuda.empty_cache()
     return res
