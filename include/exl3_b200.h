@@ -149,11 +149,12 @@ exl3_status exl3_glu_linear(const void *gate_up, int x_dtype, const uint32_t *pa
  *                          k_cache [rows, kv_heads, t_max, 128], v copied into v_cache.
  *   exl3_decode_attention  softmax(q k^T * scale) v over cache positions 0..*position for every query head (q_heads a
  *                          multiple of kv_heads, ratio 1, 2, 4, 5 or 8), split over the cache in chunks of 128 positions
- *                          and merged in a fixed order; out [rows, q_heads * 128] in `dtype` (may be NULL).  scratch:
- *                          exl3_attention_scratch_bytes().  suh_next != NULL: a head is one rotation block of the o
+ *                          and merged in a fixed order by the last CTA of each (row, KV head) to finish (one launch);
+ *                          out [rows, q_heads * 128] in `dtype` (may be NULL).  scratch: exl3_attention_scratch_bytes(),
+ *                          zero-filled once before its first use (arrival counters; every call leaves them zero).  suh_next != NULL: a head is one rotation block of the o
  *                          projection's input, so the merge also writes that linear's rotated fragments into `workspace`
  *                          (as exl3_rotate_fragments would from `out`) and exl3_linear_prerotated can follow directly.
- *   exl3_rope_decode_attention  the two above in one call and two launches instead of three: the attention kernel rotates
+ *   exl3_rope_decode_attention  the two above in one call and one launch: the attention kernel rotates
  *                          the queries as it loads them (qkv is left unrotated) and the warp that owns cache slot `*position`
  *                          rotates the new key into k_cache and copies the new value into v_cache before it reads them; same
  *                          roundings, same bits.  qkv must be 8-byte aligned.

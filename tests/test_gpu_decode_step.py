@@ -182,7 +182,7 @@ def test_rope_inside_the_attention_kernel_gives_the_bits_of_the_separate_launch(
     cos_t, sin_t = ang.cos().contiguous(), ang.sin().contiguous()
     position = torch.tensor([pos], dtype=torch.int32, device=DEV)
     suh = (torch.randint(0, 2, (q_heads * 128,), device=DEV, generator=gen) * 2 - 1).half()
-    scratch = torch.empty(int(lib.exl3_attention_scratch_bytes(rows, q_heads, kv_heads, t_max)), dtype=torch.uint8, device=DEV)
+    scratch = torch.zeros(int(lib.exl3_attention_scratch_bytes(rows, q_heads, kv_heads, t_max)), dtype=torch.uint8, device=DEV)
     need = int(lib.exl3_linear_workspace_bytes(rows, q_heads * 128, 256, 1))
     p, st, code, scale = lin._ptr, lin._stream(torch.device(DEV)), lin._dtype_code(qkv), 1.0 / math.sqrt(128)
     results = []

@@ -90,7 +90,8 @@ __device__ __forceinline__ void rotate_store(const float (&a)[4], const __half* 
 }
 
 // grid = rows, block = STEP_THREADS.  x [rows, k]; residual [rows, k] or null (in / out); weight [k]; suh [shards, k];
-// normed [rows, k] or null.
+// normed [rows, k] or null.  J = 128-column blocks a warp keeps in registers (k <= J * 4096).
+template <int J>
 __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void* __restrict__ x, void* __restrict__ residual,
                                                                        const void* __restrict__ weight, float eps, int bf16,
                                                                        const __half* __restrict__ suh, int shards, int rows, int k,
@@ -102,18 +103,18 @@ __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void
     const int kgs = k >> 7;
     const bool b = bf16 != 0;
     // The norm weights are constants: they are fetched while the kernel ahead is still finishing.
-    float wv[STEP_MAX_BLOCKS_PER_WARP][4];
+    float wv[J][4];
 #pragma unroll
-    for (int j = 0; j < STEP_MAX_BLOCKS_PER_WARP; j++) {
+    for (int j = 0; j < J; j++) {
         const int kg = warp + j * (STEP_THREADS / 32);
         if (kg < kgs) load_act4(weight, kg * 128 + 4 * lane, b, wv[j]);
     }
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
-    float h[STEP_MAX_BLOCKS_PER_WARP][4];
+    float h[J][4];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < STEP_MAX_BLOCKS_PER_WARP; j++) {
+    for (int j = 0; j < J; j++) {
         const int kg = warp + j * (STEP_THREADS / 32);
         if (kg < kgs) {
             const long long i0 = (long long)row * k + kg * 128 + 4 * lane;
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void
     __syncthreads();
     const float rstd = rstd_s;
 #pragma unroll
-    for (int j = 0; j < STEP_MAX_BLOCKS_PER_WARP; j++) {
+    for (int j = 0; j < J; j++) {
         const int kg = warp + j * (STEP_THREADS / 32);
         if (kg < kgs) {                                   // warp-uniform: all lanes take part in the rotation's shuffles
             const long long i0 = (long long)row * k + kg * 128 + 4 * lane;
@@ -184,8 +185,9 @@ int launch_rmsnorm_rotate(const void* x, void* residual, const void* weight, flo
 {
     if (rows == 0 || k == 0) return EXL3_OK;
     if ((k >> 7) > STEP_MAX_BLOCKS_PER_WARP * (STEP_THREADS / 32)) return EXL3_ERR_BAD_SHAPE;
-    return launch_chained(rmsnorm_rotate_kernel, dim3(rows), dim3(STEP_THREADS), 0, st, x, residual, weight, eps, bf16, suh, shards, rows, k,
-                          normed, xf, mode);
+    const int per_warp = ((k >> 7) + STEP_THREADS / 32 - 1) / (STEP_THREADS / 32);
+    auto kernel = per_warp <= 2 ? rmsnorm_rotate_kernel<2> : per_warp <= 4 ? rmsnorm_rotate_kernel<4> : rmsnorm_rotate_kernel<STEP_MAX_BLOCKS_PER_WARP>;
+    return launch_chained(kernel, dim3(rows), dim3(STEP_THREADS), 0, st, x, residual, weight, eps, bf16, suh, shards, rows, k, normed, xf, mode);
 }
 
 int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows, int inter, void* act, uint32_t* xf, int mode,
@@ -252,10 +254,57 @@ __global__ void rope_append_kernel(void* __restrict__ qkv, int bf16, int rows, i
     }
 }
 
+// One warp, one (row, query head): lane l merges columns 4l..4l+3 of every partial of the head (fixed order: the same bits
+// every time), writes the output and -- a head is exactly one 128-wide rotation block of the o projection's input --
+// optionally the rotated fragments of that block for the linear that follows (suh != null).  The partials were written by
+// other CTAs of the same launch, so they are read past the L1 cache.
+__device__ __forceinline__ void attention_merge_head(const float* base, long long stride, int parts, int rows, int q_heads, int row, int qh,
+                                                     int lane, void* out, bool bf16, const __half* suh, uint32_t* xf, int mode)
+{
+    // Sixteen partials per round of loads (one round up to 2048 cache positions), added in split order under a running
+    // maximum.
+    float mx = -INFINITY, num[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
+    for (int s0 = 0; s0 < parts; s0 += 16) {
+        float4 a[16];
+        float ms[16], ls[16];
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            const bool in = s0 + u < parts;
+            const float* ps = base + (long long)(in ? s0 + u : s0) * stride;
+            a[u] = __ldcg(reinterpret_cast<const float4*>(ps + 4 * lane));
+            ms[u] = in ? __ldcg(ps + ATT_D) : -INFINITY;
+            ls[u] = __ldcg(ps + ATT_D + 1);
+        }
+        float bm = mx;
+#pragma unroll
+        for (int u = 0; u < 16; u++) bm = fmaxf(bm, ms[u]);
+        const float keep = mx == -INFINITY ? 0.f : __expf(mx - bm);   // rescale what earlier rounds added
+        mx = bm;
+        den *= keep;
+#pragma unroll
+        for (int e = 0; e < 4; e++) num[e] *= keep;
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            const float w = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - mx);
+            num[0] += w * a[u].x;
+            num[1] += w * a[u].y;
+            num[2] += w * a[u].z;
+            num[3] += w * a[u].w;
+            den += w * ls[u];
+        }
+    }
+    float y[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) y[e] = round_act(num[e] / den, bf16);
+    if (out) store_act4(out, ((long long)row * q_heads + qh) * ATT_D + 4 * lane, y, bf16);
+    if (suh) rotate_store(y, suh + qh * ATT_D, xf, mode, 0, (q_heads * ATT_D) >> 4, rows, row, qh, lane);
+}
+
 // Split-KV decode attention.  grid = (splits, kv_heads, rows); a CTA attends positions [split * ATT_CHUNK ...) of one KV
 // head for its G query heads: every lane owns ONE position (reads its key row, G dot products against the queries held in
 // shared memory, no shuffles), the warp then walks its 32 positions for the values (each lane four of the 128 columns).
-// Partial results (running maximum, normaliser, G x 128 weighted sums per split) are merged by attention_merge_kernel.
+// Partial results (running maximum, normaliser, G x 128 weighted sums per split) go to scratch; the last CTA of a (row, KV
+// head) to arrive merges them.
 // With cos_t / sin_t the kernel also does what rope_append_kernel does, with the same roundings: the queries are rotated as
 // they are loaded (qkv itself is left as it is), and the warp that owns cache position `pos` rotates the new key into the
 // cache and copies the new value there before it reads them back like any other position.
@@ -264,7 +313,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
                                                                            void* k_cache, void* v_cache, int t_max,
                                                                            const int* __restrict__ pos_ptr, float scale,
                                                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                                                           float* __restrict__ part)
+                                                                           float* part, int* counters, int rows, void* __restrict__ y_out,
+                                                                           const __half* __restrict__ suh, uint32_t* __restrict__ xf, int mode)
 {
     __shared__ float qs[G][ATT_D];
     ptx::grid_launch_dependents();
@@ -275,6 +325,22 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     const int T = pos + 1;                                        // valid cache positions
     const int heads = q_heads + 2 * kv_heads;
     const bool b = bf16 != 0;
+    // Cache rows below `pos` are requested first and all at once -- the key row of the lane's position whole and all of the
+    // warp's 32 value rows -- so one round of memory latency covers them; row `pos` itself may come from this kernel's own
+    // append and is fetched after it.
+    const int t0 = split * ATT_CHUNK + warp * 32;
+    const int t = t0 + lane;
+    const long long rowbase = (((long long)row * kv_heads + kvh) * t_max) * ATT_D;
+    const uint4* kr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(k_cache) + (rowbase + (long long)t * ATT_D) * 2);
+    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(v_cache) + (rowbase + (long long)t0 * ATT_D + 4 * lane) * 2;
+    uint4 kw[16];
+    uint2 vw[32];
+    if (t < pos) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) kw[j] = kr[j];
+    }
+#pragma unroll
+    for (int u = 0; u < 32; u++) vw[u] = (t0 + u < pos) ? *reinterpret_cast<const uint2*>(vbase + (long long)u * ATT_D * 2) : make_uint2(0u, 0u);
     if (cos_t) {
         for (int e = threadIdx.x; e < G * (ATT_D / 2); e += ATT_WARPS * 32) {
             const int g = e / (ATT_D / 2), i = e % (ATT_D / 2);
@@ -310,16 +376,19 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     __syncthreads();
     const int splits = gridDim.x;
     float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
-    const int t = split * ATT_CHUNK + warp * 32 + lane;
-    const long long rowbase = (((long long)row * kv_heads + kvh) * t_max) * ATT_D;
+    if (t == pos) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) kw[j] = kr[j];
+    }
+    if (pos >= t0 && pos < t0 + 32) {                             // warp-uniform
+#pragma unroll
+        for (int u = 0; u < 32; u++)
+            if (t0 + u == pos) vw[u] = *reinterpret_cast<const uint2*>(vbase + (long long)u * ATT_D * 2);
+    }
     float sc[G];
 #pragma unroll
     for (int g = 0; g < G; g++) sc[g] = 0.f;
     if (t < T) {
-        const uint4* kr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(k_cache) + (rowbase + (long long)t * ATT_D) * 2);
-        uint4 kw[16];                                             // the whole key row in flight at once
-#pragma unroll
-        for (int j = 0; j < 16; j++) kw[j] = kr[j];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             const uint4 w = kw[j];
@@ -359,29 +428,22 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     for (int g = 0; g < G; g++)
 #pragma unroll
         for (int e = 0; e < 4; e++) acc[g][e] = 0.f;
-    const int t0 = split * ATT_CHUNK + warp * 32;
-    const int n = T - t0 < 32 ? T - t0 : 32;                      // warp-uniform
-    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(v_cache) + (rowbase + (long long)t0 * ATT_D + 4 * lane) * 2;
-    for (int j0 = 0; j0 < n; j0 += 16) {                          // sixteen value rows in flight per warp
-        uint2 w[16];
+    const int n = T - t0 < 32 ? T - t0 : 32;                      // warp-uniform; rows past the end hold zeros and weigh zero
 #pragma unroll
-        for (int u = 0; u < 16; u++) w[u] = (j0 + u < n) ? *reinterpret_cast<const uint2*>(vbase + (long long)(j0 + u) * ATT_D * 2) : make_uint2(0u, 0u);
+    for (int u = 0; u < 32; u++) {
+        float v[4];
+        if (b) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&vw[u].x), c = *reinterpret_cast<const __nv_bfloat162*>(&vw[u].y);
+            v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
+        } else {
+            const __half2 a = *reinterpret_cast<const __half2*>(&vw[u].x), c = *reinterpret_cast<const __half2*>(&vw[u].y);
+            v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
+        }
 #pragma unroll
-        for (int u = 0; u < 16; u++) {
-            float v[4];
-            if (b) {
-                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w[u].x), c = *reinterpret_cast<const __nv_bfloat162*>(&w[u].y);
-                v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
-            } else {
-                const __half2 a = *reinterpret_cast<const __half2*>(&w[u].x), c = *reinterpret_cast<const __half2*>(&w[u].y);
-                v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
-            }
+        for (int g = 0; g < G; g++) {
+            const float pj = __shfl_sync(0xFFFFFFFFu, p[g], u);
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float pj = __shfl_sync(0xFFFFFFFFu, p[g], (j0 + u) & 31);      // zero for positions past the end
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[g][e] += pj * v[e];
-            }
+            for (int e = 0; e < 4; e++) acc[g][e] += pj * v[e];
         }
     }
     // The four warps' partial results are merged inside the CTA (fixed warp order), so one partial per split goes out.
@@ -427,67 +489,33 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
         }
         *reinterpret_cast<float4*>(out + g * ATT_PART + c) = sum;
     }
+    // The CTA that is last to deliver its split for this (row, KV head) merges all of them: no second launch.  Its partial
+    // stores are fenced before the count, the others' are read after it.
+    __shared__ int last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* cnt = counters + row * kv_heads + kvh;
+        const int arrived = atomicAdd(cnt, 1);
+        last_s = arrived == splits - 1;
+        if (last_s) *cnt = 0;                                     // everyone has counted: zero again for the next launch
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    const float* base = part + ((long long)row * kv_heads + kvh) * splits * (G * ATT_PART);
+    for (int g = warp; g < G; g += ATT_WARPS)
+        attention_merge_head(base + g * ATT_PART, (long long)G * ATT_PART, splits, rows, q_heads, row, kvh * G + g, lane, y_out, b, suh, xf, mode);
 }
 
-// One warp per (row, query head): lane l merges columns 4l..4l+3 of every partial of its head (fixed order: the same bits
-// every time), writes the output and -- a head is exactly one 128-wide rotation block of the o projection's input --
-// optionally the rotated fragments of that block for the linear that follows (suh != null).
-__global__ void attention_merge_kernel(const float* __restrict__ part, int rows, int q_heads, int kv_heads, int G, int parts,
-                                       void* __restrict__ out, int bf16, const __half* __restrict__ suh, uint32_t* __restrict__ xf, int mode)
-{
-    ptx::grid_launch_dependents();
-    ptx::grid_dependency_wait();
-    const int lane = threadIdx.x & 31;
-    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= rows * q_heads) return;
-    const int qh = item % q_heads, row = item / q_heads;
-    const int kvh = qh / G, g = qh % G;
-    const float* base = part + (((long long)row * kv_heads + kvh) * parts) * (G * ATT_PART) + g * ATT_PART;
-    const long long stride = (long long)G * ATT_PART;
-    // Sixteen partials per round of loads (one round up to 2048 cache positions), added in split order under a running
-    // maximum: the same bits every time.
-    float mx = -INFINITY, num[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
-    for (int s0 = 0; s0 < parts; s0 += 16) {
-        float4 a[16];
-        float ms[16], ls[16];
-#pragma unroll
-        for (int u = 0; u < 16; u++) {
-            const bool in = s0 + u < parts;
-            const float* ps = base + (long long)(in ? s0 + u : s0) * stride;
-            a[u] = *reinterpret_cast<const float4*>(ps + 4 * lane);
-            ms[u] = in ? ps[ATT_D] : -INFINITY;
-            ls[u] = ps[ATT_D + 1];
-        }
-        float bm = mx;
-#pragma unroll
-        for (int u = 0; u < 16; u++) bm = fmaxf(bm, ms[u]);
-        const float keep = mx == -INFINITY ? 0.f : __expf(mx - bm);   // rescale what earlier rounds added
-        mx = bm;
-        den *= keep;
-#pragma unroll
-        for (int e = 0; e < 4; e++) num[e] *= keep;
-#pragma unroll
-        for (int u = 0; u < 16; u++) {
-            const float w = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - mx);
-            num[0] += w * a[u].x;
-            num[1] += w * a[u].y;
-            num[2] += w * a[u].z;
-            num[3] += w * a[u].w;
-            den += w * ls[u];
-        }
-    }
-    float y[4];
-#pragma unroll
-    for (int e = 0; e < 4; e++) y[e] = round_act(num[e] / den, bf16 != 0);
-    if (out) store_act4(out, ((long long)row * q_heads + qh) * ATT_D + 4 * lane, y, bf16 != 0);
-    if (suh) rotate_store(y, suh + qh * ATT_D, xf, mode, 0, (q_heads * ATT_D) >> 4, rows, row, qh, lane);
-}
+// Scratch: one arrival counter per (row, KV head) -- zero before the first launch, left zero by every launch -- then the partials.
+static size_t attention_counter_bytes(int rows, int kv_heads) { return ((size_t)rows * kv_heads * sizeof(int) + 255) & ~(size_t)255; }
 
 size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)
 {
     const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
     const int G = q_heads / (kv_heads > 0 ? kv_heads : 1);
-    return (size_t)rows * kv_heads * splits * G * ATT_PART * sizeof(float);
+    return attention_counter_bytes(rows, kv_heads) + (size_t)rows * kv_heads * splits * G * ATT_PART * sizeof(float);
 }
 
 int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads, const float* cos_t, const float* sin_t, void* k_cache,
@@ -505,11 +533,10 @@ static int launch_attention_g(const void* qkv, int bf16, int rows, int q_heads, 
                               uint32_t* xf, int mode, cudaStream_t st)
 {
     const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
-    int rc = launch_chained(decode_attention_kernel<G>, dim3(splits, kv_heads, rows), dim3(ATT_WARPS * 32), 0, st, qkv, bf16, q_heads, kv_heads,
-                            k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, part);
-    if (rc) return rc;
-    return launch_chained(attention_merge_kernel, dim3((unsigned)((rows * q_heads + 3) / 4)), dim3(128), 0, st, static_cast<const float*>(part), rows,
-                          q_heads, kv_heads, G, splits, out, bf16, suh, xf, mode);
+    int* counters = reinterpret_cast<int*>(part);
+    float* partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(part) + attention_counter_bytes(rows, kv_heads));
+    return launch_chained(decode_attention_kernel<G>, dim3(splits, kv_heads, rows), dim3(ATT_WARPS * 32), 0, st, qkv, bf16, q_heads, kv_heads,
+                          k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, partials, counters, rows, out, suh, xf, mode);
 }
 
 int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, void* k_cache, void* v_cache, int t_max,

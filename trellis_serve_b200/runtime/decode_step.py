@@ -9,8 +9,8 @@
 
 Every linear is ONE decode-GEMV launch whose activations were rotated by the kernel ahead of it; rotary embedding, cache
 append and attention are stock torch (`scaled_dot_product_attention`): they are not part of the quantized-linear path and
-their bytes (the KV read) are reported separately.  `attention="library"` (default) runs the library's own two small
-kernels for that part (RoPE + cache append + split-KV attention, merge); `attention="torch"` keeps the stock torch ops.  The whole step is captured in one CUDA graph, as an engine captures
+their bytes (the KV read) are reported separately.  `attention="library"` (default) runs the library's own kernel for that part (RoPE + cache append + split-KV attention, merged
+by the last CTA to arrive); `attention="torch"` keeps the stock torch ops.  The whole step is captured in one CUDA graph, as an engine captures
 it (cuda/src/sglang_exl3/sglang_glue/moe.py:202-213 warms for that purpose; cuda/src/sglang_exl3/tools/decode_microbench.py
 :27-41 times launches the same way).
 
@@ -109,7 +109,7 @@ class DecodeStep:
         self.cos_table[context], self.sin_table[context] = self.cos[0].float(), self.sin[0].float()
         self.position = torch.tensor([context], dtype=torch.int32, device=dev)
         from .. import _lib
-        self.att_scratch = torch.empty(int(_lib.load().exl3_attention_scratch_bytes(rows, self.q_heads, self.kv_heads, context + 1)),
+        self.att_scratch = torch.zeros(int(_lib.load().exl3_attention_scratch_bytes(rows, self.q_heads, self.kv_heads, context + 1)),
                                        dtype=torch.uint8, device=dev)
         # activations of the chain (static: the captured graph sees fixed addresses)
         mk = lambda w: torch.empty((rows, w), dtype=dtype, device=dev)
@@ -120,7 +120,7 @@ class DecodeStep:
         self.linear_launches = s.layers * 4
         glu = 0 if rows <= 2 else 1                                   # the activation kernel runs only from three rows up
         self.fused_launches = s.layers * ((2 if attention == "library" else 3) + glu)   # rmsnorm_rotate x2 (+ rotation ahead of o)
-        self.attention_launches = s.layers * 2 if attention == "library" else None   # rope + attention, merge
+        self.attention_launches = s.layers if attention == "library" else None   # RoPE, append, attention and merge in one
 
     # ---- bytes
     @property
