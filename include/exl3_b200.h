@@ -142,6 +142,18 @@ exl3_status exl3_glu_linear(const void *gate_up, int x_dtype, const uint32_t *pa
                             int y_dtype, void *workspace, size_t workspace_bytes, void *const *peer_regions, int rank, int world,
                             size_t max_elems, int *state, void *stream);
 
+/* A fused group whose input is the normalised residual stream: residual_out = x + residual_in (rounded to x_dtype),
+ * y = linear(rmsnorm(residual_out, eps) * norm_weight).  residual_in may be NULL (no residual: x itself is normalised and
+ * residual_out is ignored); otherwise residual_out is a second buffer (it must not alias residual_in: up to two rows every CTA
+ * of the GEMV forms the rows' mean square itself while one of them stores the sum, so the whole step is one launch).
+ * From three rows up the library runs its normalisation kernel ahead of the GEMV.  The mean square is added in a different
+ * order than in exl3_rmsnorm_rotate, so results may differ from that sequence in the last bit of the normalisation factor.
+ * The reference's engine runs residual add and RMSNorm as kernels of its own ahead of had_in; no counterpart there. */
+exl3_status exl3_rmsnorm_linear(const void *x, int x_dtype, const void *residual_in, void *residual_out, const void *norm_weight,
+                                float eps, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
+                                const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
+                                int y_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
 /* The attention side of the same step (not quantized arithmetic; here so that a step is a handful of launches per layer):
  *   exl3_rope_append       qkv [rows, (q_heads + 2 kv_heads) * 128] holds q | k | v of one new token per row.  Rotary
  *                          embedding ("rotate half": pairs (i, i + 64)) with cos_table / sin_table [positions, 64] fp32 at
@@ -158,6 +170,8 @@ exl3_status exl3_glu_linear(const void *gate_up, int x_dtype, const uint32_t *pa
  *                          the queries as it loads them (qkv is left unrotated) and the warp that owns cache slot `*position`
  *                          rotates the new key into k_cache and copies the new value into v_cache before it reads them; same
  *                          roundings, same bits.  qkv must be 8-byte aligned.
+ * Before it waits for the kernel ahead of it in the stream, an attention call walks through its merge code once on what the
+ * scratch buffer holds, storing nothing (instruction-cache warm-up): the scratch must be readable then, nothing else is touched.
  * The reference leaves attention to its engine; no counterpart there. */
 size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);
 exl3_status exl3_rope_append(void *qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float *cos_table,

@@ -58,6 +58,34 @@ def test_fused_producers_give_the_bits_of_the_stand_alone_linear(rows, dtype, K,
     lin.device_error(DEV)
 
 
+@pytest.mark.parametrize("rows,dtype,K,cb", [(1, torch.float16, 3, 0), (2, torch.bfloat16, 4, 1), (2, torch.float16, 3, 2), (5, torch.bfloat16, 3, 0)])
+def test_normalisation_inside_the_linear(rows, dtype, K, cb):
+    """exl3_rmsnorm_linear against exl3_rmsnorm_rotate + exl3_linear_prerotated: the new residual stream is the same bits; the
+    outputs agree to the last bit of the normalisation factor (the mean square is added in another order), i.e. to an ulp of a few
+    activations ahead of the rotation -- far inside the 2e-3 of the linear itself.  Five rows take the normalisation kernel."""
+    k, ns = 1024, [640, 384]
+    packed, suh, svh, ends, ws, gen = _group(k, ns, K, 7 * rows + K)
+    x = torch.randn((rows, k), device=DEV, generator=gen).to(dtype)
+    res0 = torch.randn((rows, k), device=DEV, generator=gen).to(dtype)
+    weight = (1.0 + 0.1 * torch.randn(k, device=DEV, generator=gen)).to(dtype)
+    want, got = torch.empty((rows, sum(ns)), dtype=dtype, device=DEV), torch.empty((rows, sum(ns)), dtype=dtype, device=DEV)
+    residual = res0.clone()
+    lin.rmsnorm_rotate(x, residual, weight, 1e-6, suh, cb, ws)
+    lin.run_prerotated(rows, packed, svh, ends, cb, want, ws)
+    res_out = torch.full_like(res0, float("nan"))
+    lin.run_rmsnorm(x, res0, res_out, weight, 1e-6, packed, suh, svh, ends, cb, got, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(res_out, residual)
+    scale = float(want.float().pow(2).mean().sqrt())
+    assert float((got.float() - want.float()).abs().max()) <= 2e-3 * scale
+    # no residual: x itself is normalised
+    lin.rmsnorm_rotate(x, None, weight, 1e-6, suh, cb, ws)
+    lin.run_prerotated(rows, packed, svh, ends, cb, want, ws)
+    lin.run_rmsnorm(x, None, None, weight, 1e-6, packed, suh, svh, ends, cb, got, ws)
+    assert float((got.float() - want.float()).abs().max()) <= 2e-3 * scale
+    lin.device_error(DEV)
+
+
 @pytest.mark.parametrize("rows,dtype", [(1, torch.float16), (2, torch.bfloat16), (7, torch.float16)])
 def test_silu_mul_rotation_feeds_the_down_projection(rows, dtype):
     inter, n, K, cb = 768, 512, 3, 0

@@ -175,10 +175,19 @@ size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards)
     return workspace_layout(rows, k, n_total, n_shards).total;
 }
 
+namespace {
+struct NormArgs {                // residual add + RMSNorm ahead of the group (exl3_rmsnorm_linear)
+    const void* weight;
+    const void* res_in;
+    void* res_out;
+    float eps;
+};
+}  // namespace
+
 static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor, const uint32_t* packed, int K, int codebook,
                          const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k,
                          int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated,
-                         const TpExchange* tp = nullptr, bool prerotated = false, bool glu = false)
+                         const TpExchange* tp = nullptr, bool prerotated = false, bool glu = false, const NormArgs* norm = nullptr)
 {
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (rows < 0) return EXL3_ERR_BAD_SHAPE;
@@ -241,8 +250,27 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
             a.suh = reinterpret_cast<const __half*>(suh_cat);
             a.x_bf16 = x_dtype == EXL3_BF16;
             a.x_glu = glu ? 1 : 0;
+            if (norm) {
+                a.norm_weight = norm->weight;
+                a.norm_res_in = norm->res_in ? reinterpret_cast<const unsigned char*>(norm->res_in) + (size_t)r0 * k * esz : nullptr;
+                a.norm_res_out = norm->res_out ? reinterpret_cast<unsigned char*>(norm->res_out) + (size_t)r0 * k * esz : nullptr;
+                a.norm_eps = norm->eps;
+            }
             if (!gemv_rotates_input(a)) {
                 a.x = nullptr;
+                if (norm) {
+                    // more rows than the kernel rotates itself: the normalisation kernel runs ahead of it
+                    const void* res_in = a.norm_res_in;
+                    void* res_out = a.norm_res_out;
+                    a.norm_weight = nullptr;
+                    rc = launch_rmsnorm_rotate(xr, const_cast<void*>(res_in), norm->weight, norm->eps, x_dtype == EXL3_BF16,
+                                               reinterpret_cast<const __half*>(suh_cat), n_shards, r, k, nullptr, const_cast<uint32_t*>(a.xf),
+                                               a.mode == GEMV_SPLIT ? 1 : 2, st, res_in ? res_out : nullptr);
+                    if (rc) return rc;
+                    rc = launch_gemv(a, st);
+                    if (rc) return rc;
+                    continue;
+                }
                 rc = glu ? launch_silu_mul_rotate(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), r, k, nullptr,
                                                   const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st)
                          : launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
@@ -430,6 +458,18 @@ exl3_status exl3_glu_linear(const void* gate_up, int x_dtype, const uint32_t* pa
     if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
     return linear_common(gate_up, x_dtype, nullptr, packed, K, codebook, suh, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
                          workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, false, true);
+}
+
+exl3_status exl3_rmsnorm_linear(const void* x, int x_dtype, const void* residual_in, void* residual_out, const void* norm_weight, float eps,
+                                const uint32_t* packed, int K, int codebook, const uint16_t* suh_cat, const uint16_t* svh_cat,
+                                const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y, int y_dtype, void* workspace,
+                                size_t workspace_bytes, void* stream)
+{
+    if (rows > 0 && (!aligned(x, 8) || !aligned(norm_weight, 8) || !aligned(suh_cat, 8))) return EXL3_ERR_BAD_POINTER;
+    if (residual_in && (!aligned(residual_in, 8) || !aligned(residual_out, 8) || residual_in == residual_out)) return EXL3_ERR_BAD_POINTER;
+    NormArgs norm = {norm_weight, residual_in, residual_in ? residual_out : nullptr, eps};
+    return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
+                         workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, false, false, &norm);
 }
 
 size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)

@@ -80,6 +80,102 @@ __device__ __forceinline__ float gemv_load_glu(const void* p, long long idx, int
     return __half2float(__float2half_rn(bf16 ? __bfloat162float(__float2bfloat16_rn(act)) : act));
 }
 
+__device__ __forceinline__ float gemv_raw(const void* p, long long idx, bool bf16)
+{
+    return bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]) : __half2float(reinterpret_cast<const __half*>(p)[idx]);
+}
+
+__device__ __forceinline__ float gemv_round_act(float v, bool bf16)
+{
+    return bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
+}
+
+// Residual stream element z = x (+ residual, rounded to the activation type), as the stand-alone normalisation kernel forms it.
+__device__ __forceinline__ float gemv_residual_sum(const void* x, const void* res, long long idx, bool bf16)
+{
+    const float xv = gemv_raw(x, idx, bf16);
+    return res ? gemv_round_act(xv + gemv_raw(res, idx, bf16), bf16) : xv;
+}
+
+// The normalised activation rmsnorm(z) * weight, rounded to the activation type and taken as fp16.
+__device__ __forceinline__ float gemv_load_norm(const void* x, const void* res, const void* weight, long long idx, long long col, float rstd,
+                                                bool bf16)
+{
+    const float a = gemv_round_act(gemv_residual_sum(x, res, idx, bf16) * rstd * gemv_raw(weight, col, bf16), bf16);
+    return __half2float(__float2half_rn(a));
+}
+
+// 1 / sqrt(mean square + eps) of row `row` of the residual stream x (+ residual), formed by the whole CTA (all consumer
+// warps call this): per-thread sums, warp sums by shuffle, the warps' sums added in warp order through `scratch`
+// (`warps` floats of shared memory, `warps` = warps of the CTA); `store` makes this CTA write the stream to norm_res_out.  Kept out of
+// line: it runs once per launch and must not weigh on the register allocation of the decode loop.
+static __device__ __noinline__ float gemv_row_rstd(const GemvArgs& a, int row, bool store, float* scratch, int warps)
+{
+    const bool bf16 = a.x_bf16 != 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float ss = 0.f;
+    // Four activations per 8-byte load (the rows are 8-byte aligned), all of a thread's loads issued before they are used:
+    // every CTA of the launch reads the same few KB at the same moment, so requests are kept few.
+    constexpr int MAXIT = 4;                                    // k <= MAXIT * warps * 128 is covered without a second round
+    for (int i0 = threadIdx.x * 4; i0 < a.k; i0 += MAXIT * warps * 128) {
+        uint2 xr[MAXIT], rr[MAXIT];
+#pragma unroll
+        for (int j = 0; j < MAXIT; j++) {
+            const int i = i0 + j * warps * 128;
+            if (i < a.k) {
+                const long long at = ((long long)row * a.k + i) * 2;
+                xr[j] = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(a.x) + at);
+                rr[j] = a.norm_res_in ? *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(a.norm_res_in) + at) : make_uint2(0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < MAXIT; j++) {
+            const int i = i0 + j * warps * 128;
+            if (i < a.k) {
+                float xv[4], rv[4], z[4];
+                if (bf16) {
+                    const __nv_bfloat162 x0 = *reinterpret_cast<const __nv_bfloat162*>(&xr[j].x), x1 = *reinterpret_cast<const __nv_bfloat162*>(&xr[j].y);
+                    const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr[j].x), r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr[j].y);
+                    xv[0] = __low2float(x0); xv[1] = __high2float(x0); xv[2] = __low2float(x1); xv[3] = __high2float(x1);
+                    rv[0] = __low2float(r0); rv[1] = __high2float(r0); rv[2] = __low2float(r1); rv[3] = __high2float(r1);
+                } else {
+                    const __half2 x0 = *reinterpret_cast<const __half2*>(&xr[j].x), x1 = *reinterpret_cast<const __half2*>(&xr[j].y);
+                    const __half2 r0 = *reinterpret_cast<const __half2*>(&rr[j].x), r1 = *reinterpret_cast<const __half2*>(&rr[j].y);
+                    xv[0] = __low2float(x0); xv[1] = __high2float(x0); xv[2] = __low2float(x1); xv[3] = __high2float(x1);
+                    rv[0] = __low2float(r0); rv[1] = __high2float(r0); rv[2] = __low2float(r1); rv[3] = __high2float(r1);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    z[e] = a.norm_res_in ? gemv_round_act(xv[e] + rv[e], bf16) : xv[e];
+                    ss += z[e] * z[e];
+                }
+                if (store && a.norm_res_out) {
+                    const long long at = (long long)row * a.k + i;
+                    if (bf16) {
+                        __nv_bfloat16 o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) o[e] = __float2bfloat16_rn(z[e]);
+                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.norm_res_out) + at) = *reinterpret_cast<uint2*>(o);
+                    } else {
+                        __half o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) o[e] = __float2half_rn(z[e]);
+                        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.norm_res_out) + at) = *reinterpret_cast<uint2*>(o);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
+    ptx::named_bar_sync(1, warps * 32);                      // scratch is free (an earlier row's sums have been read)
+    if (lane == 0) scratch[warp] = ss;
+    ptx::named_bar_sync(1, warps * 32);
+    float t = 0.f;
+    for (int w = 0; w < warps; w++) t += scratch[w];
+    return rsqrtf(t / (float)a.k + a.norm_eps);
+}
+
 // Row-parallel shard: 4 consecutive columns (index o) of one output row are a partial sum.  They go, rounded to the
 // output type and tagged with the call number, into this rank's slot at every peer (single 64-bit peer stores); then
 // the same words of all ranks are awaited here (bounded), added in rank order in fp32 and rounded once: the bits a

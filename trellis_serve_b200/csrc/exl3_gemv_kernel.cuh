@@ -56,7 +56,9 @@ __host__ __device__ constexpr uint32_t gemv_xs_slot_bytes(int mode, int rows) { 
 //     1, 2 = that many rows, and the kernel rotates the input itself: before the main loop every consumer warp turns
 //     x * suh of a few of the CTA's units into fragments in shared memory (one slot per unit, in unit order), so the
 //     linear is ONE launch and the main loop reads its activations with immediate-offset shared loads.
-template <int K, int MODE, int FAM, int MB, int XR>
+// XIN: what the in-kernel rotation (XR > 0) reads -- 0: x as it is (or gate | up, a run-time flag); 1: the residual stream, which
+// it normalises itself (an instance of its own: the statistics pass must not touch the code of the others).
+template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0>
 __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(const __grid_constant__ GemvLaunch p)
 {
     static_assert(XR == 0 || MB == 1, "in-kernel rotation serves one 8-row group");
@@ -289,6 +291,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         } else {
         const int items = (int)(u1 - u0) * XR;
         const bool bf16 = p.a.x_bf16 != 0;
+        // Normalised input: every CTA forms the rows' mean square itself (the rows are a few KB in L2), warps' sums added in
+        // warp order; CTA 0 also stores the new residual stream.
+        float rstd[XR];
+#pragma unroll
+        for (int r = 0; r < XR; r++) rstd[r] = 1.f;
+        if constexpr (XIN == 1) {
+            ptx::grid_dependency_wait();
+            waited = true;
+            EXL3_STAMP(1);
+#pragma unroll
+            for (int r = 0; r < XR; r++)
+                if (r < rows) rstd[r] = gemv_row_rstd(p.a, r, cta == 0, P, GEMV_CONSUMER_WARPS);
+        }
         constexpr int BATCH = 3;                      // rotations in flight per warp: their loads overlap
         for (int it0 = warp; it0 < items; it0 += GEMV_CONSUMER_WARPS * BATCH) {
             float v[BATCH][4];
@@ -318,8 +333,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             for (int b = 0; b < BATCH; b++) {
                 if (it0 + GEMV_CONSUMER_WARPS * b < items) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++)
-                        v[b][e] *= p.a.x_glu ? gemv_load_glu(p.a.x, xi[b] + e, p.a.k, bf16) : gemv_load_x(p.a.x, xi[b] + e, bf16);
+                    for (int e = 0; e < 4; e++) {
+                        if constexpr (XIN == 1) {
+                            const int row = (it0 + GEMV_CONSUMER_WARPS * b) % XR;
+                            v[b][e] *= gemv_load_norm(p.a.x, p.a.norm_res_in, p.a.norm_weight, xi[b] + e, xi[b] + e - (long long)row * p.a.k,
+                                                      XR > 1 && row == 1 ? rstd[XR - 1] : rstd[0], bf16);
+                        } else {
+                            v[b][e] *= p.a.x_glu ? gemv_load_glu(p.a.x, xi[b] + e, p.a.k, bf16) : gemv_load_x(p.a.x, xi[b] + e, bf16);
+                        }
+                    }
                 }
             }
 #pragma unroll

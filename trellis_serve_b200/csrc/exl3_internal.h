@@ -65,6 +65,10 @@ struct GemvArgs {
     const __half* suh;          //   and the input sign vectors [n_shards][k]
     int x_bf16;
     int x_glu;                  // x is gate | up [rows, 2k]: the input is silu(gate) * up (a down projection's activation)
+    const void* norm_weight;    // set: the input is rmsnorm(x + norm_res_in) * norm_weight (residual add and normalisation of the
+    const void* norm_res_in;    //   layer ahead of a q|k|v or gate|up group); norm_res_in may be null (no residual).  CTA 0 writes
+    void* norm_res_out;         //   x + norm_res_in to norm_res_out (null: not wanted), which must not alias norm_res_in
+    float norm_eps;
     int xf_staged;              // rows <= 2 without x: the fragments in xf are copied to shared memory once (bulk copies)
                                 //   instead of being read from global memory tile by tile
     const __half* svh;          // [n_total]; unused when rotated
@@ -104,7 +108,7 @@ int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, in
 
 // exl3_step.cu ------------------------------------------------------------------------------------------
 int launch_rmsnorm_rotate(const void* x, void* residual, const void* weight, float eps, int bf16, const __half* suh, int shards, int rows,
-                          int k, void* normed, uint32_t* xf, int mode, cudaStream_t st);
+                          int k, void* normed, uint32_t* xf, int mode, cudaStream_t st, void* residual_out = nullptr);
 int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows, int inter, void* act, uint32_t* xf, int mode,
                            cudaStream_t st);
 size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);

@@ -95,7 +95,8 @@ template <int J>
 __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void* __restrict__ x, void* __restrict__ residual,
                                                                        const void* __restrict__ weight, float eps, int bf16,
                                                                        const __half* __restrict__ suh, int shards, int rows, int k,
-                                                                       void* __restrict__ normed, uint32_t* __restrict__ xf, int mode)
+                                                                       void* __restrict__ normed, uint32_t* __restrict__ xf, int mode,
+                                                                       void* __restrict__ residual_out)
 {
     __shared__ float part[STEP_THREADS / 32];
     __shared__ float rstd_s;
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(STEP_THREADS) rmsnorm_rotate_kernel(const void
                 load_act4(residual, i0, b, r);
 #pragma unroll
                 for (int e = 0; e < 4; e++) z[e] = round_act(z[e] + r[e], b);
-                store_act4(residual, i0, z, b);
+                store_act4(residual_out ? residual_out : residual, i0, z, b);      // in place unless a second buffer is given
             }
 #pragma unroll
             for (int e = 0; e < 4; e++) {
@@ -181,13 +182,14 @@ __global__ void silu_mul_rotate_kernel(const void* __restrict__ gu, int bf16, co
 }
 
 int launch_rmsnorm_rotate(const void* x, void* residual, const void* weight, float eps, int bf16, const __half* suh, int shards, int rows,
-                          int k, void* normed, uint32_t* xf, int mode, cudaStream_t st)
+                          int k, void* normed, uint32_t* xf, int mode, cudaStream_t st, void* residual_out)
 {
     if (rows == 0 || k == 0) return EXL3_OK;
     if ((k >> 7) > STEP_MAX_BLOCKS_PER_WARP * (STEP_THREADS / 32)) return EXL3_ERR_BAD_SHAPE;
     const int per_warp = ((k >> 7) + STEP_THREADS / 32 - 1) / (STEP_THREADS / 32);
     auto kernel = per_warp <= 2 ? rmsnorm_rotate_kernel<2> : per_warp <= 4 ? rmsnorm_rotate_kernel<4> : rmsnorm_rotate_kernel<STEP_MAX_BLOCKS_PER_WARP>;
-    return launch_chained(kernel, dim3(rows), dim3(STEP_THREADS), 0, st, x, residual, weight, eps, bf16, suh, shards, rows, k, normed, xf, mode);
+    return launch_chained(kernel, dim3(rows), dim3(STEP_THREADS), 0, st, x, residual, weight, eps, bf16, suh, shards, rows, k, normed, xf, mode,
+                          residual_out);
 }
 
 int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows, int inter, void* act, uint32_t* xf, int mode,
@@ -254,6 +256,22 @@ __global__ void rope_append_kernel(void* __restrict__ qkv, int bf16, int rows, i
     }
 }
 
+#ifdef EXL3_TIMELINE
+// Measurement build only: thread 0 of every attention CTA stamps %globaltimer; the slot is derived from the cache address.
+__device__ unsigned long long g_att_timeline[64][256][8];
+extern "C" int exl3_debug_att_timeline(unsigned long long* host_out) { return (int)cudaMemcpyFromSymbol(host_out, g_att_timeline, sizeof(g_att_timeline)); }
+#define ATT_STAMP(i)                                                                                                          \
+    do {                                                                                                                      \
+        if (threadIdx.x == 0) {                                                                                               \
+            unsigned long long t_;                                                                                            \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                            \
+            g_att_timeline[(unsigned)(reinterpret_cast<unsigned long long>(k_cache) >> 22) & 63][blockIdx.x + gridDim.x * blockIdx.y][i] = t_; \
+        }                                                                                                                     \
+    } while (0)
+#else
+#define ATT_STAMP(i) do { } while (0)
+#endif
+
 // One warp, one (row, query head): lane l merges columns 4l..4l+3 of every partial of the head (fixed order: the same bits
 // every time), writes the output and -- a head is exactly one 128-wide rotation block of the o projection's input --
 // optionally the rotated fragments of that block for the linear that follows (suh != null).  The partials were written by
@@ -300,6 +318,100 @@ __device__ __forceinline__ void attention_merge_head(const float* base, long lon
     if (suh) rotate_store(y, suh + qh * ATT_D, xf, mode, 0, (q_heads * ATT_D) >> 4, rows, row, qh, lane);
 }
 
+// The merge of all splits of one (row, KV head) by a whole CTA (ATT_WARPS warps).  `dry`: same instructions, no stores -- run
+// once before the wait for the kernel ahead, while the CTA has nothing else to do, so that the real pass at the very end of
+// the launch finds its code in the instruction cache.
+template <int G>
+static __device__ __noinline__ void attention_merge_cta(const float* part, float (*red)[G][ATT_PART], int row, int kvh, int kv_heads, int q_heads,
+                                                        int splits, int rows, void* y_out, bool b, const __half* suh, uint32_t* xf, int mode,
+                                                        bool dry)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* base = part + ((long long)row * kv_heads + kvh) * splits * (G * ATT_PART);
+    const long long stride = (long long)G * ATT_PART;
+    if (splits > 32) {                                            // more than 4096 cache positions: one warp per head, split after split
+        if (!dry)
+            for (int g = warp; g < G; g += ATT_WARPS)
+                attention_merge_head(base + g * ATT_PART, stride, splits, rows, q_heads, row, kvh * G + g, lane, y_out, b, suh, xf, mode);
+        return;
+    }
+    // Up to 32 splits: the whole CTA merges all G heads together, in three short phases with one round of loads each, so the
+    // tail of the launch is a few dependent memory round trips instead of one per head and warp.  Every sum has a fixed order.
+    __shared__ float sm_ms[ATT_MAX_GROUP * 32], sm_ls[ATT_MAX_GROUP * 32], sm_w[ATT_MAX_GROUP * 32];
+    // (1) maxima and normalisers of every (head, split)
+    for (int i = threadIdx.x; i < G * splits; i += ATT_WARPS * 32) {
+        const int g = i / splits, sp = i - g * splits;
+        const float* ps = base + sp * stride + g * ATT_PART;
+        sm_ms[g * 32 + sp] = __ldcg(ps + ATT_D);
+        sm_ls[g * 32 + sp] = __ldcg(ps + ATT_D + 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * splits; i += ATT_WARPS * 32) {
+        const int g = i / splits, sp = i - g * splits;
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int t2 = 0; t2 < splits; t2++) mx = fmaxf(mx, sm_ms[g * 32 + t2]);
+        const float ms = sm_ms[g * 32 + sp];
+        sm_w[g * 32 + sp] = ms == -INFINITY ? 0.f : __expf(ms - mx);
+    }
+    __syncthreads();
+    // (2) warp w adds the splits w, w + 4, ... of every head
+    constexpr int JB = G <= 5 ? 5 : (G <= 6 ? 4 : 3);            // splits in flight per warp: JB x G 16-byte loads per lane
+    float sum[G][4];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) sum[g][e] = 0.f;
+    const int per_warp = (splits + ATT_WARPS - 1) / ATT_WARPS;
+#pragma unroll 1
+    for (int j0 = 0; j0 < per_warp; j0 += JB) {
+        float4 a[JB][G];
+#pragma unroll
+        for (int j = 0; j < JB; j++) {
+            const int sp = warp + ATT_WARPS * (j0 + j);
+#pragma unroll
+            for (int g = 0; g < G; g++)
+                a[j][g] = sp < splits ? __ldcg(reinterpret_cast<const float4*>(base + sp * stride + g * ATT_PART + 4 * lane)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < JB; j++) {
+            const int sp = warp + ATT_WARPS * (j0 + j);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float w = sp < splits ? sm_w[g * 32 + sp] : 0.f;
+                sum[g][0] += w * a[j][g].x;
+                sum[g][1] += w * a[j][g].y;
+                sum[g][2] += w * a[j][g].z;
+                sum[g][3] += w * a[j][g].w;
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) *reinterpret_cast<float4*>(&red[warp][g][4 * lane]) = make_float4(sum[g][0], sum[g][1], sum[g][2], sum[g][3]);
+    __syncthreads();
+    // (3) one warp per head: the warps' sums in warp order, the normaliser, the output and the next linear's fragments
+    for (int g = warp; g < G; g += ATT_WARPS) {
+        float num[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float4 v = *reinterpret_cast<const float4*>(&red[w][g][4 * lane]);
+            num[0] += v.x;
+            num[1] += v.y;
+            num[2] += v.z;
+            num[3] += v.w;
+        }
+        float den = lane < splits ? sm_w[g * 32 + lane] * sm_ls[g * 32 + lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, o);
+        const int qh = kvh * G + g;
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[e] = round_act(num[e] / den, b);
+        if (y_out && !dry) store_act4(y_out, ((long long)row * q_heads + qh) * ATT_D + 4 * lane, y, b);
+        if (suh && !dry) rotate_store(y, suh + qh * ATT_D, xf, mode, 0, (q_heads * ATT_D) >> 4, rows, row, qh, lane);
+    }
+}
+
 // Split-KV decode attention.  grid = (splits, kv_heads, rows); a CTA attends positions [split * ATT_CHUNK ...) of one KV
 // head for its G query heads: every lane owns ONE position (reads its key row, G dot products against the queries held in
 // shared memory, no shuffles), the warp then walks its 32 positions for the values (each lane four of the 128 columns).
@@ -317,8 +429,14 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
                                                                            const __half* __restrict__ suh, uint32_t* __restrict__ xf, int mode)
 {
     __shared__ float qs[G][ATT_D];
+    __shared__ __align__(16) float red[ATT_WARPS][G][ATT_PART];
+    ATT_STAMP(0);
     ptx::grid_launch_dependents();
+    // Nothing to do until the kernel ahead has finished: walk through the merge code once without storing anything, so that
+    // the CTA that ends up merging runs it from the instruction cache (it reads last step's partials; they are only looked at).
+    attention_merge_cta<G>(part, red, blockIdx.z, blockIdx.y, kv_heads, q_heads, gridDim.x, rows, y_out, bf16 != 0, suh, xf, mode, true);
     ptx::grid_dependency_wait();
+    ATT_STAMP(1);
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = *pos_ptr;
@@ -341,6 +459,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     }
 #pragma unroll
     for (int u = 0; u < 32; u++) vw[u] = (t0 + u < pos) ? *reinterpret_cast<const uint2*>(vbase + (long long)u * ATT_D * 2) : make_uint2(0u, 0u);
+    const int splits = gridDim.x;
+    float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
+    __shared__ float wgt[G][ATT_WARPS];
+    __shared__ int last_s;
     if (cos_t) {
         for (int e = threadIdx.x; e < G * (ATT_D / 2); e += ATT_WARPS * 32) {
             const int g = e / (ATT_D / 2), i = e % (ATT_D / 2);
@@ -374,8 +496,6 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
             qs[e / ATT_D][e % ATT_D] = to_f32(qkv, ((long long)row * heads + kvh * G + e / ATT_D) * ATT_D + e % ATT_D, b) * scale;
     }
     __syncthreads();
-    const int splits = gridDim.x;
-    float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
     if (t == pos) {
 #pragma unroll
         for (int j = 0; j < 16; j++) kw[j] = kr[j];
@@ -410,6 +530,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
             }
         }
     }
+    ATT_STAMP(2);
     float m[G], l[G], p[G];
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -446,9 +567,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
             for (int e = 0; e < 4; e++) acc[g][e] += pj * v[e];
         }
     }
+    ATT_STAMP(3);
     // The four warps' partial results are merged inside the CTA (fixed warp order), so one partial per split goes out.
-    __shared__ __align__(16) float red[ATT_WARPS][G][ATT_PART];
-    __shared__ float wgt[G][ATT_WARPS];
 #pragma unroll
     for (int g = 0; g < G; g++) {
         *reinterpret_cast<float4*>(&red[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
@@ -491,7 +611,6 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     }
     // The CTA that is last to deliver its split for this (row, KV head) merges all of them: no second launch.  Its partial
     // stores are fenced before the count, the others' are read after it.
-    __shared__ int last_s;
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -501,11 +620,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
         if (last_s) *cnt = 0;                                     // everyone has counted: zero again for the next launch
     }
     __syncthreads();
+    ATT_STAMP(4);
     if (!last_s) return;
     __threadfence();
-    const float* base = part + ((long long)row * kv_heads + kvh) * splits * (G * ATT_PART);
-    for (int g = warp; g < G; g += ATT_WARPS)
-        attention_merge_head(base + g * ATT_PART, (long long)G * ATT_PART, splits, rows, q_heads, row, kvh * G + g, lane, y_out, b, suh, xf, mode);
+    ATT_STAMP(5);
+    attention_merge_cta<G>(part, red, row, kvh, kv_heads, q_heads, splits, rows, y_out, b, suh, xf, mode, false);
+    ATT_STAMP(7);
 }
 
 // Scratch: one arrival counter per (row, KV head) -- zero before the first launch, left zero by every launch -- then the partials.

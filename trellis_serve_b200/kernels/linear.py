@@ -297,6 +297,24 @@ def run_prerotated(rows: int, b: torch.Tensor, svh_cat: torch.Tensor, shard_ends
     return out
 
 
+def run_rmsnorm(x: torch.Tensor, residual_in: torch.Tensor | None, residual_out: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int], codebook: int, out: torch.Tensor,
+                workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """The fused group on rmsnorm(x + residual_in) * weight, with residual_out = x + residual_in written to a second buffer: up
+    to two rows one launch (every CTA of the GEMV forms the mean square itself)."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
+    _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
+    k, n_total, K = _geometry(b)
+    rows, shards = x.shape[0], len(shard_ends) + 1
+    ws = _own_or_given(workspace, b.device, workspace_bytes(rows, k, n_total, shards), _workspace)
+    with torch.cuda.device(b.device):
+        _lib.check(lib.exl3_rmsnorm_linear(_ptr(x), _dtype_code(x), _ptr(residual_in), _ptr(residual_out), _ptr(weight), float(eps), _ptr(b), K,
+                                           codebook, _ptr(suh_cat), _ptr(svh_cat), _lib.int_array(shard_ends), shards, rows, k, n_total,
+                                           _ptr(out), _dtype_code(out, True), _ptr(ws), ws.numel(), _stream(b.device)), "exl3_rmsnorm_linear")
+    return out
+
+
 def run_glu(gate_up: torch.Tensor, b: torch.Tensor, suh: torch.Tensor, svh_cat: torch.Tensor, codebook: int, out: torch.Tensor,
             workspace: torch.Tensor | None = None, exchange=None) -> torch.Tensor:
     """Down projection of silu(gate) * up straight from `gate_up` [rows, 2k]: up to two rows the activation is computed inside

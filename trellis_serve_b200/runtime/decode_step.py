@@ -1,9 +1,9 @@
 """One decoded token through a dense transformer of EXL3 linears: the step either side of the kernels.
 
-    per layer:  residual += h;  a = RMSNorm(residual)          -> fused with the input rotation of q|k|v   (rmsnorm_rotate)
+    per layer:  residual += h;  a = RMSNorm(residual)          -> inside the input rotation of q|k|v       (rmsnorm linear)
                 q|k|v = EXL3(a);  RoPE(q, k);  KV cache append;  attention over the cache
                 o = EXL3(attention)                             -> rotation launch, then the GEMV
-                residual += o;  a = RMSNorm(residual)           -> fused with the input rotation of gate|up
+                residual += o;  a = RMSNorm(residual)           -> inside the input rotation of gate|up
                 g|u = EXL3(a);  act = SiLU(g) * u               -> computed inside down's own input rotation (glu linear; from three
                 h = EXL3(act)                                      rows up: silu_mul_rotate ahead of the GEMV)
 
@@ -114,12 +114,12 @@ class DecodeStep:
         # activations of the chain (static: the captured graph sees fixed addresses)
         mk = lambda w: torch.empty((rows, w), dtype=dtype, device=dev)
         self.h_in = torch.zeros((rows, h), dtype=dtype, device=dev)          # the step's input: the token's embedding
-        self.h, self.residual = mk(h), mk(h)
+        self.h, self.residual, self.residual2 = mk(h), mk(h), mk(h)        # the residual stream alternates between two buffers
         self.qkv, self.attn, self.o_out, self.gu, self.out = mk(q + 2 * kv), mk(q), mk(h), mk(2 * f), mk(h)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.linear_launches = s.layers * 4
-        glu = 0 if rows <= 2 else 1                                   # the activation kernel runs only from three rows up
-        self.fused_launches = s.layers * ((2 if attention == "library" else 3) + glu)   # rmsnorm_rotate x2 (+ rotation ahead of o)
+        small = 0 if rows <= 2 else 3                                 # normalisation x2 and activation kernels run only from three rows up
+        self.fused_launches = s.layers * ((0 if attention == "library" else 1) + small)   # (+ rotation ahead of o with stock attention)
         self.attention_launches = s.layers if attention == "library" else None   # RoPE, append, attention and merge in one
 
     # ---- bytes
@@ -173,14 +173,12 @@ class DecodeStep:
         self.residual.zero_()
         h = self.h_in
         for i, (qkv, o, gu, down, norms) in enumerate(self.layers):
-            lin.rmsnorm_rotate(h, self.residual, norms[0], self.shape.eps, qkv.suh, cb, ws)
-            lin.run_prerotated(rows, qkv.packed, qkv.svh, qkv.ends, cb, self.qkv, ws)
+            lin.run_rmsnorm(h, self.residual, self.residual2, norms[0], self.shape.eps, qkv.packed, qkv.suh, qkv.svh, qkv.ends, cb, self.qkv, ws)
             if not self._attention(i, o.suh):
                 lin.rotate_fragments(self.attn, o.suh, cb, ws)
             lin.run_prerotated(rows, o.packed, o.svh, o.ends, cb, self.o_out, ws, exchange=ex)
             self._reduce(self.o_out)
-            lin.rmsnorm_rotate(self.o_out, self.residual, norms[1], self.shape.eps, gu.suh, cb, ws)
-            lin.run_prerotated(rows, gu.packed, gu.svh, gu.ends, cb, self.gu, ws)
+            lin.run_rmsnorm(self.o_out, self.residual2, self.residual, norms[1], self.shape.eps, gu.packed, gu.suh, gu.svh, gu.ends, cb, self.gu, ws)
             lin.run_glu(self.gu, down.packed, down.suh, down.svh, cb, self.h, ws, exchange=ex)
             self._reduce(self.h)
             h = self.h
