@@ -130,25 +130,35 @@ exl3_status exl3_silu_mul_rotate(const void *gate_up, int dtype, const uint16_t 
 exl3_status exl3_linear_prerotated(const uint32_t *packed, int K, int codebook, const uint16_t *svh_cat, const int *shard_ends,
                                    int n_shards, int rows, int k, int n_total, void *y, int y_dtype, void *workspace,
                                    size_t workspace_bytes, void *const *peer_regions, int rank, int world, size_t max_elems,
-                                   int *state, void *stream);
+                                   int *state, const void *residual_in, void *residual_out, float *ssq_out, void *stream);
 
 /* A down projection fed straight from the gate | up output: y = linear(fp16(silu(gate) * up)) with gate_up [rows, 2k] in
  * x_dtype, suh [k], n_shards = 1.  Up to two rows the activation is computed inside the GEMV's own input rotation (one launch,
  * no activation buffer); above that the library runs the activation kernel ahead of it.  Same bits as exl3_silu_mul_rotate
  * followed by exl3_linear_prerotated.  The exchange arguments are those of exl3_linear_prerotated (world <= 1: none).
- * The reference's engine runs its activation kernel between the two launches; no counterpart there. */
+ * The reference's engine runs its activation kernel between the two launches; no counterpart there.
+ *
+ * Residual stream carried by the linears (exl3_linear_prerotated and exl3_glu_linear, the row-parallel ends of a block):
+ * with residual_in / residual_out / ssq_out set (all three or none) the epilogue adds the output block -- summed over the
+ * ranks first, if there is an exchange -- to residual_in [rows, n_total], writes the sum, rounded to y_dtype, to residual_out
+ * (a second buffer) and the sum of its squares per (row, 128 columns) to ssq_out [rows, n_total / 128]; y may then be NULL
+ * (no exchange, up to two rows).  exl3_normed_linear is the consumer: the fused group on rmsnorm(z) * norm_weight, where z is
+ * such a stream and ssq its sums of squares; up to two rows the GEMV normalises on the way into its own rotation, so a
+ * transformer block is four launches plus attention.  exl3_residual_ssq starts a chain (z = x + residual_in, or x itself, and
+ * its sums of squares); exl3_rmsnorm_linear = exl3_residual_ssq + exl3_normed_linear for a caller without a producer.
+ * From three rows up the library runs its normalisation / stream kernels around a plain GEMV (y must then be given).
+ * The reference's engine runs residual add and RMSNorm as kernels of its own ahead of had_in; no counterpart there. */
 exl3_status exl3_glu_linear(const void *gate_up, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh,
                             const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
                             int y_dtype, void *workspace, size_t workspace_bytes, void *const *peer_regions, int rank, int world,
-                            size_t max_elems, int *state, void *stream);
-
-/* A fused group whose input is the normalised residual stream: residual_out = x + residual_in (rounded to x_dtype),
- * y = linear(rmsnorm(residual_out, eps) * norm_weight).  residual_in may be NULL (no residual: x itself is normalised and
- * residual_out is ignored); otherwise residual_out is a second buffer (it must not alias residual_in: up to two rows every CTA
- * of the GEMV forms the rows' mean square itself while one of them stores the sum, so the whole step is one launch).
- * From three rows up the library runs its normalisation kernel ahead of the GEMV.  The mean square is added in a different
- * order than in exl3_rmsnorm_rotate, so results may differ from that sequence in the last bit of the normalisation factor.
- * The reference's engine runs residual add and RMSNorm as kernels of its own ahead of had_in; no counterpart there. */
+                            size_t max_elems, int *state, const void *residual_in, void *residual_out, float *ssq_out,
+                            void *stream);
+exl3_status exl3_residual_ssq(const void *x, const void *residual_in, int dtype, int rows, int k, void *residual_out, float *ssq,
+                              void *stream);
+exl3_status exl3_normed_linear(const void *z, int x_dtype, const float *ssq, const void *norm_weight, float eps,
+                               const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat, const uint16_t *svh_cat,
+                               const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y, int y_dtype,
+                               void *workspace, size_t workspace_bytes, void *stream);
 exl3_status exl3_rmsnorm_linear(const void *x, int x_dtype, const void *residual_in, void *residual_out, const void *norm_weight,
                                 float eps, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
                                 const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,

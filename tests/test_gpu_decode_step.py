@@ -86,6 +86,57 @@ def test_normalisation_inside_the_linear(rows, dtype, K, cb):
     lin.device_error(DEV)
 
 
+@pytest.mark.parametrize("rows,dtype,glu", [(1, torch.float16, False), (2, torch.bfloat16, True), (1, torch.bfloat16, True), (2, torch.float16, False),
+                                            (5, torch.float16, True), (6, torch.bfloat16, False)])
+def test_residual_stream_in_the_epilogue_and_its_consumer(rows, dtype, glu):
+    """A row-parallel end of a block (o or down) with the residual epilogue: the new stream is exactly round(y + z) for the y the
+    plain call stores, its sums of squares per 128 columns are those of the stored stream, y may be left out; the consumer
+    (`run_normed`) on that stream agrees with the normalisation kernel + linear to the last bit of the normalisation factor.
+    Five and six rows take the kernels around a plain GEMV."""
+    k, n, K, cb = 768, 1024, 3, 0
+    packed, suh, svh, ends, ws, gen = _group(k, [n], K, 13 * rows + glu)
+    z = torch.randn((rows, n), device=DEV, generator=gen).to(dtype)
+    y = torch.empty((rows, n), dtype=dtype, device=DEV)
+    z2, ssq = torch.full_like(z, float("nan")), torch.full((rows, n // 128), float("nan"), dtype=torch.float32, device=DEV)
+    if glu:
+        gu = torch.randn((rows, 2 * k), device=DEV, generator=gen).to(dtype)
+        lin.run_glu(gu, packed, suh.view(-1), svh, cb, y, ws)
+        plain = y.clone()
+        lin.run_glu(gu, packed, suh.view(-1), svh, cb, y, ws, residual=(z, z2, ssq))
+    else:
+        x = torch.randn((rows, k), device=DEV, generator=gen).to(dtype)
+        lin.rotate_fragments(x, suh, cb, ws)
+        lin.run_prerotated(rows, packed, svh, ends, cb, y, ws)
+        plain = y.clone()
+        lin.rotate_fragments(x, suh, cb, ws)
+        lin.run_prerotated(rows, packed, svh, ends, cb, y, ws, residual=(z, z2, ssq))
+    torch.cuda.synchronize()
+    assert torch.equal(y, plain)
+    want = (plain.float() + z.float()).to(dtype)
+    assert torch.equal(z2, want)
+    want_ssq = want.float().view(rows, n // 128, 128).pow(2).sum(-1)
+    assert float(((ssq - want_ssq).abs() / want_ssq).max()) <= 1e-5
+    if rows <= 2:                                      # y is optional when the epilogue carries the stream
+        z3, ssq3 = torch.full_like(z, float("nan")), torch.zeros_like(ssq)
+        if glu:
+            lin.run_glu(gu, packed, suh.view(-1), svh, cb, None, ws, residual=(z, z3, ssq3))
+        else:
+            lin.rotate_fragments(x, suh, cb, ws)
+            lin.run_prerotated(rows, packed, svh, ends, cb, None, ws, residual=(z, z3, ssq3))
+        assert torch.equal(z3, z2) and torch.equal(ssq3, ssq)
+    # the consumer of that stream: a fused group of the stream's width
+    packed2, suh2, svh2, ends2, ws2, gen2 = _group(n, [640, 384], 4, 5 + rows)
+    weight = (1.0 + 0.1 * torch.randn(n, device=DEV, generator=gen2)).to(dtype)
+    got, ref = torch.empty((rows, 1024), dtype=dtype, device=DEV), torch.empty((rows, 1024), dtype=dtype, device=DEV)
+    lin.run_normed(z2, ssq, weight, 1e-6, packed2, suh2, svh2, ends2, 1, got, ws2)
+    lin.rmsnorm_rotate(z2, None, weight, 1e-6, suh2, 1, ws2)
+    lin.run_prerotated(rows, packed2, svh2, ends2, 1, ref, ws2)
+    torch.cuda.synchronize()
+    scale = float(ref.float().pow(2).mean().sqrt())
+    assert float((got.float() - ref.float()).abs().max()) <= 2e-3 * scale
+    lin.device_error(DEV)
+
+
 @pytest.mark.parametrize("rows,dtype", [(1, torch.float16), (2, torch.bfloat16), (7, torch.float16)])
 def test_silu_mul_rotation_feeds_the_down_projection(rows, dtype):
     inter, n, K, cb = 768, 512, 3, 0

@@ -38,9 +38,13 @@ SIGNATURES = {
     "exl3_rotate_fragments": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "exl3_rmsnorm_rotate": (_i, [_vp, _vp, _vp, ctypes.c_float, _i, _vp, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "exl3_silu_mul_rotate": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
-    "exl3_linear_prerotated": (_i, [_vp, _i, _i, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),
+    "exl3_linear_prerotated": (_i, [_vp, _i, _i, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp, _vp, _vp,
+                                    _vp]),
     "exl3_rmsnorm_linear": (_i, [_vp, _i, _vp, _vp, _vp, ctypes.c_float, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
-    "exl3_glu_linear": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp]),
+    "exl3_residual_ssq": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "exl3_normed_linear": (_i, [_vp, _i, _vp, _vp, ctypes.c_float, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "exl3_glu_linear": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _ip, _i, _i, _i, _i, _vp, _i, _vp, _sz, ctypes.POINTER(_vp), _i, _i, _sz, _vp, _vp, _vp, _vp,
+                             _vp]),
     "exl3_attention_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "exl3_rope_append": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "exl3_decode_attention": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, ctypes.c_float, _vp, _sz, _vp, _vp, _i, _vp, _sz, _vp]),

@@ -176,18 +176,23 @@ size_t exl3_linear_workspace_bytes(int rows, int k, int n_total, int n_shards)
 }
 
 namespace {
-struct NormArgs {                // residual add + RMSNorm ahead of the group (exl3_rmsnorm_linear)
+struct NormArgs {                // consumer of a residual stream: x = z, normalised on the way in (exl3_normed_linear)
     const void* weight;
+    const float* ssq;            // [rows, k/128]
+    float eps;
+};
+struct ResidualArgs {            // producer: the epilogue adds res_in, writes the new stream and its sums of squares
     const void* res_in;
     void* res_out;
-    float eps;
+    float* ssq_out;              // [rows, n_total/128]
 };
 }  // namespace
 
 static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor, const uint32_t* packed, int K, int codebook,
                          const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k,
                          int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, cudaStream_t st, bool rotated,
-                         const TpExchange* tp = nullptr, bool prerotated = false, bool glu = false, const NormArgs* norm = nullptr)
+                         const TpExchange* tp = nullptr, bool prerotated = false, bool glu = false, const NormArgs* norm = nullptr,
+                         const ResidualArgs* res = nullptr)
 {
     if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
     if (rows < 0) return EXL3_ERR_BAD_SHAPE;
@@ -200,7 +205,10 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
     if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
     if ((size_t)(n_total / 128) > WS_MAX_COUNTERS) return EXL3_ERR_BAD_SHAPE;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
-    if (!aligned(packed, 16) || !aligned(y, 16)) return EXL3_ERR_BAD_POINTER;
+    if (!aligned(packed, 16) || (!aligned(y, 16) && !(res && y == nullptr))) return EXL3_ERR_BAD_POINTER;
+    if (res && (!aligned(res->res_in, 8) || !aligned(res->res_out, 8) || !aligned(res->ssq_out, 4) || res->res_in == res->res_out ||
+                (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16)))
+        return EXL3_ERR_BAD_POINTER;
     if (prerotated ? !aligned(svh_cat, 8)
                    : rotated ? !aligned(xh_rowmajor, 2) : (!aligned(x, 2) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8)))
         return EXL3_ERR_BAD_POINTER;
@@ -226,7 +234,12 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
     for (int r0 = 0; r0 < rows; r0 += GEMV_MAX_ROWS) {
         const int r = rows - r0 < GEMV_MAX_ROWS ? rows - r0 : GEMV_MAX_ROWS;
         a.rows = r;
-        a.out = reinterpret_cast<unsigned char*>(y) + (size_t)r0 * n_total * osz;
+        a.out = y ? reinterpret_cast<unsigned char*>(y) + (size_t)r0 * n_total * osz : nullptr;
+        if (res) {
+            a.res_in = reinterpret_cast<const unsigned char*>(res->res_in) + (size_t)r0 * n_total * 2;
+            a.res_out = reinterpret_cast<unsigned char*>(res->res_out) + (size_t)r0 * n_total * 2;
+            a.ssq_out = res->ssq_out + (size_t)r0 * (n_total / 128);
+        }
         int rc;
         if (prerotated) {
             // The fragments are in the workspace already (exl3_rotate_fragments, exl3_rmsnorm_rotate, exl3_silu_mul_rotate):
@@ -234,6 +247,16 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
             a.x = nullptr;
             a.xf_staged = 1;
             if (!gemv_rotates_input(a)) a.xf_staged = 0;
+            if (res && !a.xf_staged) {          // more rows than the residual epilogue serves: plain GEMV, then the stream kernel
+                if (!y) return EXL3_ERR_BAD_POINTER;
+                a.res_out = nullptr;
+                rc = launch_gemv(a, st);
+                if (rc) return rc;
+                rc = launch_residual_ssq(a.out, a.res_in, y_dtype == EXL3_BF16, r, n_total, reinterpret_cast<unsigned char*>(res->res_out) + (size_t)r0 * n_total * 2,
+                                         res->ssq_out + (size_t)r0 * (n_total / 128), st);
+                if (rc) return rc;
+                continue;
+            }
         } else if (rotated) {
             // shard s reads slab s of xh: rows [s*rows + r0, s*rows + r0 + r)
             for (int s = 0; s < n_shards; s++) {
@@ -252,23 +275,34 @@ static int linear_common(const void* x, int x_dtype, const uint16_t* xh_rowmajor
             a.x_glu = glu ? 1 : 0;
             if (norm) {
                 a.norm_weight = norm->weight;
-                a.norm_res_in = norm->res_in ? reinterpret_cast<const unsigned char*>(norm->res_in) + (size_t)r0 * k * esz : nullptr;
-                a.norm_res_out = norm->res_out ? reinterpret_cast<unsigned char*>(norm->res_out) + (size_t)r0 * k * esz : nullptr;
+                a.ssq_in = norm->ssq + (size_t)r0 * (k / 128);
                 a.norm_eps = norm->eps;
             }
             if (!gemv_rotates_input(a)) {
                 a.x = nullptr;
-                if (norm) {
-                    // more rows than the kernel rotates itself: the normalisation kernel runs ahead of it
-                    const void* res_in = a.norm_res_in;
-                    void* res_out = a.norm_res_out;
+                if (norm || res) {
+                    // more rows than the kernel rotates itself: the normalisation / activation kernel ahead of a plain GEMV, and
+                    // the stream kernel behind it where the epilogue would have added the residual
                     a.norm_weight = nullptr;
-                    rc = launch_rmsnorm_rotate(xr, const_cast<void*>(res_in), norm->weight, norm->eps, x_dtype == EXL3_BF16,
-                                               reinterpret_cast<const __half*>(suh_cat), n_shards, r, k, nullptr, const_cast<uint32_t*>(a.xf),
-                                               a.mode == GEMV_SPLIT ? 1 : 2, st, res_in ? res_out : nullptr);
+                    void* res_out = a.res_out;
+                    a.res_out = nullptr;
+                    if (res && !y) return EXL3_ERR_BAD_POINTER;
+                    if (norm)
+                        rc = launch_rmsnorm_rotate(xr, nullptr, norm->weight, norm->eps, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat),
+                                                   n_shards, r, k, nullptr, const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
+                    else if (glu)
+                        rc = launch_silu_mul_rotate(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), r, k, nullptr,
+                                                    const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
+                    else
+                        rc = launch_had_in(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), n_shards, r, k,
+                                           const_cast<uint32_t*>(a.xf), a.mode == GEMV_SPLIT ? 1 : 2, st);
                     if (rc) return rc;
                     rc = launch_gemv(a, st);
                     if (rc) return rc;
+                    if (res) {
+                        rc = launch_residual_ssq(a.out, a.res_in, y_dtype == EXL3_BF16, r, n_total, res_out, a.ssq_out, st);
+                        if (rc) return rc;
+                    }
                     continue;
                 }
                 rc = glu ? launch_silu_mul_rotate(xr, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), r, k, nullptr,
@@ -430,34 +464,67 @@ static int make_exchange(TpExchange& tp, void* const* peer_regions, int rank, in
     return EXL3_OK;
 }
 
+static int residual_args(ResidualArgs& r, const void* residual_in, void* residual_out, float* ssq_out, const void* y, int world)
+{
+    if (!residual_in && !residual_out && !ssq_out) return 0;
+    if (!residual_in || !residual_out || !ssq_out) return EXL3_ERR_BAD_POINTER;
+    if (world > 1 && !y) return EXL3_ERR_BAD_POINTER;              // the exchange sums in the output buffer
+    r = {residual_in, residual_out, ssq_out};
+    return 1;
+}
+
 exl3_status exl3_linear_prerotated(const uint32_t* packed, int K, int codebook, const uint16_t* svh_cat, const int* shard_ends,
                                    int n_shards, int rows, int k, int n_total, void* y, int y_dtype, void* workspace,
                                    size_t workspace_bytes, void* const* peer_regions, int rank, int world, size_t max_elems, int* state,
-                                   void* stream)
+                                   const void* residual_in, void* residual_out, float* ssq_out, void* stream)
 {
-    if (world <= 1)
-        return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
-                             y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, true);
+    ResidualArgs res;
+    const int has = residual_args(res, residual_in, residual_out, ssq_out, y, world);
+    if (has > 1) return has;
     TpExchange tp;
-    if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
+    if (world > 1)
+        if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
     return linear_common(nullptr, EXL3_F16, nullptr, packed, K, codebook, nullptr, svh_cat, shard_ends, n_shards, rows, k, n_total, y,
-                         y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, true);
+                         y_dtype, workspace, workspace_bytes, (cudaStream_t)stream, false, world > 1 ? &tp : nullptr, true, false, nullptr,
+                         has ? &res : nullptr);
 }
 
 exl3_status exl3_glu_linear(const void* gate_up, int x_dtype, const uint32_t* packed, int K, int codebook, const uint16_t* suh,
                             const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y, int y_dtype,
                             void* workspace, size_t workspace_bytes, void* const* peer_regions, int rank, int world, size_t max_elems,
-                            int* state, void* stream)
+                            int* state, const void* residual_in, void* residual_out, float* ssq_out, void* stream)
 {
     if (n_shards != 1) return EXL3_ERR_BAD_SHAPE;               // one input, one sign vector: a down projection is not a fused group
     if (rows > 0 && !aligned(gate_up, 8)) return EXL3_ERR_BAD_POINTER;
-    if (world <= 1)
-        return linear_common(gate_up, x_dtype, nullptr, packed, K, codebook, suh, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
-                             workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, false, true);
+    ResidualArgs res;
+    const int has = residual_args(res, residual_in, residual_out, ssq_out, y, world);
+    if (has > 1) return has;
     TpExchange tp;
-    if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
+    if (world > 1)
+        if (int rc = make_exchange(tp, peer_regions, rank, world, max_elems, state, rows, n_total, y_dtype)) return rc;
     return linear_common(gate_up, x_dtype, nullptr, packed, K, codebook, suh, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
-                         workspace, workspace_bytes, (cudaStream_t)stream, false, &tp, false, true);
+                         workspace, workspace_bytes, (cudaStream_t)stream, false, world > 1 ? &tp : nullptr, false, true, nullptr,
+                         has ? &res : nullptr);
+}
+
+exl3_status exl3_residual_ssq(const void* x, const void* residual_in, int dtype, int rows, int k, void* residual_out, float* ssq, void* stream)
+{
+    if (dtype != EXL3_F16 && dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
+    if (rows < 0 || k <= 0 || k % 128) return EXL3_ERR_BAD_SHAPE;
+    if (rows == 0) return EXL3_OK;
+    if (!aligned(x, 8) || (residual_in && !aligned(residual_in, 8)) || (residual_out && !aligned(residual_out, 8)) || !aligned(ssq, 4))
+        return EXL3_ERR_BAD_POINTER;
+    return launch_residual_ssq(x, residual_in, dtype == EXL3_BF16, rows, k, residual_out, ssq, (cudaStream_t)stream);
+}
+
+exl3_status exl3_normed_linear(const void* z, int x_dtype, const float* ssq, const void* norm_weight, float eps, const uint32_t* packed, int K,
+                               int codebook, const uint16_t* suh_cat, const uint16_t* svh_cat, const int* shard_ends, int n_shards, int rows,
+                               int k, int n_total, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (rows > 0 && (!aligned(z, 8) || !aligned(norm_weight, 8) || !aligned(suh_cat, 8) || !aligned(ssq, 4))) return EXL3_ERR_BAD_POINTER;
+    NormArgs norm = {norm_weight, ssq, eps};
+    return linear_common(z, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
+                         workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, false, false, &norm);
 }
 
 exl3_status exl3_rmsnorm_linear(const void* x, int x_dtype, const void* residual_in, void* residual_out, const void* norm_weight, float eps,
@@ -465,11 +532,19 @@ exl3_status exl3_rmsnorm_linear(const void* x, int x_dtype, const void* residual
                                 const int* shard_ends, int n_shards, int rows, int k, int n_total, void* y, int y_dtype, void* workspace,
                                 size_t workspace_bytes, void* stream)
 {
-    if (rows > 0 && (!aligned(x, 8) || !aligned(norm_weight, 8) || !aligned(suh_cat, 8))) return EXL3_ERR_BAD_POINTER;
+    if (int rc = check_matrix(k, n_total, K, codebook)) return rc;
+    if (rows <= 0) return rows < 0 ? EXL3_ERR_BAD_SHAPE : EXL3_OK;
+    if (!aligned(x, 8) || !aligned(norm_weight, 8) || !aligned(suh_cat, 8)) return EXL3_ERR_BAD_POINTER;
     if (residual_in && (!aligned(residual_in, 8) || !aligned(residual_out, 8) || residual_in == residual_out)) return EXL3_ERR_BAD_POINTER;
-    NormArgs norm = {norm_weight, residual_in, residual_in ? residual_out : nullptr, eps};
-    return linear_common(x, x_dtype, nullptr, packed, K, codebook, suh_cat, svh_cat, shard_ends, n_shards, rows, k, n_total, y, y_dtype,
-                         workspace, workspace_bytes, (cudaStream_t)stream, false, nullptr, false, false, &norm);
+    const WorkspaceLayout wl = workspace_layout(rows, k, n_total, n_shards);
+    if (!aligned(workspace, 256) || workspace_bytes < wl.total) return EXL3_ERR_WORKSPACE;
+    // The stream's sums of squares live where the fragments of a pre-rotated call would: this call has none (the GEMV rotates
+    // its own input; from three rows up the normalisation kernel recomputes the statistics and overwrites the region).
+    float* ssq = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + wl.xf_off);
+    if (int rc = launch_residual_ssq(x, residual_in, x_dtype == EXL3_BF16, rows, k, residual_in ? residual_out : nullptr, ssq, (cudaStream_t)stream))
+        return rc;
+    return exl3_normed_linear(residual_in ? residual_out : x, x_dtype, ssq, norm_weight, eps, packed, K, codebook, suh_cat, svh_cat, shard_ends,
+                              n_shards, rows, k, n_total, y, y_dtype, workspace, workspace_bytes, stream);
 }
 
 size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)

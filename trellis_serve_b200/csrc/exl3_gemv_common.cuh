@@ -90,90 +90,23 @@ __device__ __forceinline__ float gemv_round_act(float v, bool bf16)
     return bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
 }
 
-// Residual stream element z = x (+ residual, rounded to the activation type), as the stand-alone normalisation kernel forms it.
-__device__ __forceinline__ float gemv_residual_sum(const void* x, const void* res, long long idx, bool bf16)
+// The normalised activation z * rstd * weight, rounded to the activation type (as the stand-alone normalisation kernel stores
+// it) and taken as fp16.
+__device__ __forceinline__ float gemv_load_norm(const void* z, const void* weight, long long idx, long long col, float rstd, bool bf16)
 {
-    const float xv = gemv_raw(x, idx, bf16);
-    return res ? gemv_round_act(xv + gemv_raw(res, idx, bf16), bf16) : xv;
-}
-
-// The normalised activation rmsnorm(z) * weight, rounded to the activation type and taken as fp16.
-__device__ __forceinline__ float gemv_load_norm(const void* x, const void* res, const void* weight, long long idx, long long col, float rstd,
-                                                bool bf16)
-{
-    const float a = gemv_round_act(gemv_residual_sum(x, res, idx, bf16) * rstd * gemv_raw(weight, col, bf16), bf16);
+    const float a = gemv_round_act(gemv_raw(z, idx, bf16) * rstd * gemv_raw(weight, col, bf16), bf16);
     return __half2float(__float2half_rn(a));
 }
 
-// 1 / sqrt(mean square + eps) of row `row` of the residual stream x (+ residual), formed by the whole CTA (all consumer
-// warps call this): per-thread sums, warp sums by shuffle, the warps' sums added in warp order through `scratch`
-// (`warps` floats of shared memory, `warps` = warps of the CTA); `store` makes this CTA write the stream to norm_res_out.  Kept out of
-// line: it runs once per launch and must not weigh on the register allocation of the decode loop.
-static __device__ __noinline__ float gemv_row_rstd(const GemvArgs& a, int row, bool store, float* scratch, int warps)
+// 1 / sqrt(mean square + eps) of a row of the residual stream from its per-block sums of squares (one warp, every lane gets
+// the value): lane-strided loads, then a shuffle tree -- the same order in every CTA and every launch.
+__device__ __forceinline__ float gemv_row_rstd(const float* ssq_row, int blocks, int k, float eps, int lane)
 {
-    const bool bf16 = a.x_bf16 != 0;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float ss = 0.f;
-    // Four activations per 8-byte load (the rows are 8-byte aligned), all of a thread's loads issued before they are used:
-    // every CTA of the launch reads the same few KB at the same moment, so requests are kept few.
-    constexpr int MAXIT = 4;                                    // k <= MAXIT * warps * 128 is covered without a second round
-    for (int i0 = threadIdx.x * 4; i0 < a.k; i0 += MAXIT * warps * 128) {
-        uint2 xr[MAXIT], rr[MAXIT];
-#pragma unroll
-        for (int j = 0; j < MAXIT; j++) {
-            const int i = i0 + j * warps * 128;
-            if (i < a.k) {
-                const long long at = ((long long)row * a.k + i) * 2;
-                xr[j] = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(a.x) + at);
-                rr[j] = a.norm_res_in ? *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(a.norm_res_in) + at) : make_uint2(0u, 0u);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < MAXIT; j++) {
-            const int i = i0 + j * warps * 128;
-            if (i < a.k) {
-                float xv[4], rv[4], z[4];
-                if (bf16) {
-                    const __nv_bfloat162 x0 = *reinterpret_cast<const __nv_bfloat162*>(&xr[j].x), x1 = *reinterpret_cast<const __nv_bfloat162*>(&xr[j].y);
-                    const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr[j].x), r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr[j].y);
-                    xv[0] = __low2float(x0); xv[1] = __high2float(x0); xv[2] = __low2float(x1); xv[3] = __high2float(x1);
-                    rv[0] = __low2float(r0); rv[1] = __high2float(r0); rv[2] = __low2float(r1); rv[3] = __high2float(r1);
-                } else {
-                    const __half2 x0 = *reinterpret_cast<const __half2*>(&xr[j].x), x1 = *reinterpret_cast<const __half2*>(&xr[j].y);
-                    const __half2 r0 = *reinterpret_cast<const __half2*>(&rr[j].x), r1 = *reinterpret_cast<const __half2*>(&rr[j].y);
-                    xv[0] = __low2float(x0); xv[1] = __high2float(x0); xv[2] = __low2float(x1); xv[3] = __high2float(x1);
-                    rv[0] = __low2float(r0); rv[1] = __high2float(r0); rv[2] = __low2float(r1); rv[3] = __high2float(r1);
-                }
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    z[e] = a.norm_res_in ? gemv_round_act(xv[e] + rv[e], bf16) : xv[e];
-                    ss += z[e] * z[e];
-                }
-                if (store && a.norm_res_out) {
-                    const long long at = (long long)row * a.k + i;
-                    if (bf16) {
-                        __nv_bfloat16 o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) o[e] = __float2bfloat16_rn(z[e]);
-                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.norm_res_out) + at) = *reinterpret_cast<uint2*>(o);
-                    } else {
-                        __half o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) o[e] = __float2half_rn(z[e]);
-                        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.norm_res_out) + at) = *reinterpret_cast<uint2*>(o);
-                    }
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
-    ptx::named_bar_sync(1, warps * 32);                      // scratch is free (an earlier row's sums have been read)
-    if (lane == 0) scratch[warp] = ss;
-    ptx::named_bar_sync(1, warps * 32);
     float t = 0.f;
-    for (int w = 0; w < warps; w++) t += scratch[w];
-    return rsqrtf(t / (float)a.k + a.norm_eps);
+    for (int i = lane; i < blocks; i += 32) t += ssq_row[i];
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, m);
+    return rsqrtf(t / (float)k + eps);
 }
 
 // Row-parallel shard: 4 consecutive columns (index o) of one output row are a partial sum.  They go, rounded to the
@@ -252,6 +185,42 @@ static __device__ __noinline__ void gemv_exchange_store(const TpExchange& tp, ui
         res = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
     }
     *reinterpret_cast<uint2*>(out + o) = res;
+}
+
+// Residual epilogue of one row's block of 128 outputs (one warp, four columns per lane): y -- summed over the ranks first, if
+// there is an exchange -- rounded as it would be stored, plus the residual stream: the new stream goes to res_out, this block's
+// share of its mean square to ssq_out, y itself to `out` only if that is set.  Out of line: once per 128 outputs.
+static __device__ __noinline__ void gemv_residual_store(const GemvArgs& a, uint32_t tp_epoch, const float (&v)[4], long long o, int m, int fnb,
+                                                        int lane)
+{
+    const bool bf = a.out_dtype == EXL3_BF16;
+    float y[4];
+    if (a.tp.world > 1) {
+        gemv_exchange_store(a.tp, tp_epoch, bf, v, o, reinterpret_cast<uint16_t*>(a.out), a.err);
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[e] = gemv_raw(a.out, o + e, bf);       // what the exchange stored
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[e] = gemv_round_act(__half2float(__float2half_rn(v[e])), bf);
+        if (a.out) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                if (bf) reinterpret_cast<__nv_bfloat16*>(a.out)[o + e] = __float2bfloat16_rn(y[e]);
+                else reinterpret_cast<__half*>(a.out)[o + e] = __float2half_rn(y[e]);
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float z = gemv_round_act(y[e] + gemv_raw(a.res_in, o + e, bf), bf);
+        ss += z * z;
+        if (bf) reinterpret_cast<__nv_bfloat16*>(a.res_out)[o + e] = __float2bfloat16_rn(z);
+        else reinterpret_cast<__half*>(a.res_out)[o + e] = __float2half_rn(z);
+    }
+#pragma unroll
+    for (int m2 = 16; m2 > 0; m2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m2);
+    if (lane == 0) a.ssq_out[(size_t)m * (a.n_total >> 7) + fnb] = ss;
 }
 
 }  // namespace exl3

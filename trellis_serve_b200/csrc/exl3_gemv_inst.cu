@@ -7,7 +7,7 @@
 
 namespace exl3 {
 
-template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0>
+template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0, int EPI = 0>
 static int launch_one(const GemvLaunch& l, size_t smem, cudaStream_t st)
 {
     // Launched with programmatic stream serialization: its prologue and weight copies overlap the tail of the kernel
@@ -22,13 +22,13 @@ static int launch_one(const GemvLaunch& l, size_t smem, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cuda_status(cudaLaunchKernelEx(&cfg, gemv_kernel<K, MODE, FAM, MB, XR, XIN>, l));
+    return cuda_status(cudaLaunchKernelEx(&cfg, gemv_kernel<K, MODE, FAM, MB, XR, XIN, EPI>, l));
 }
 
-template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0>
+template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0, int EPI = 0>
 static int set_attr(int max_smem)
 {
-    return cuda_status(cudaFuncSetAttribute(gemv_kernel<K, MODE, FAM, MB, XR, XIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    return cuda_status(cudaFuncSetAttribute(gemv_kernel<K, MODE, FAM, MB, XR, XIN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
 }
 
 template <int K, int MODE, int FAM>
@@ -37,6 +37,11 @@ static int launch_variant(const GemvLaunch& l, size_t smem, cudaStream_t st)
     if (l.a.x && l.a.norm_weight) {               // the kernel normalises the residual stream and rotates it
         if (l.a.rows == 1) return launch_one<K, MODE, FAM, 1, 1, 1>(l, smem, st);
         if (l.a.rows == 2) return launch_one<K, MODE, FAM, 1, 2, 1>(l, smem, st);
+        return EXL3_ERR_UNSUPPORTED_ROWS;
+    }
+    if ((l.a.x || l.a.xf_staged) && l.a.res_out) {   // ... and its epilogue adds the residual stream
+        if (l.a.rows == 1) return launch_one<K, MODE, FAM, 1, 1, 0, 1>(l, smem, st);
+        if (l.a.rows == 2) return launch_one<K, MODE, FAM, 1, 2, 0, 1>(l, smem, st);
         return EXL3_ERR_UNSUPPORTED_ROWS;
     }
     if (l.a.x || l.a.xf_staged) {                 // the kernel rotates the input itself, or stages ready-made fragments
@@ -56,6 +61,8 @@ static int set_attr_variants(int max_smem)
     if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 2>(max_smem);
     if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 1, 1>(max_smem);
     if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 2, 1>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 1, 0, 1>(max_smem);
+    if (rc == EXL3_OK) rc = set_attr<K, MODE, FAM, 1, 2, 0, 1>(max_smem);
     return rc;
 }
 

@@ -57,8 +57,9 @@ __host__ __device__ constexpr uint32_t gemv_xs_slot_bytes(int mode, int rows) { 
 //     x * suh of a few of the CTA's units into fragments in shared memory (one slot per unit, in unit order), so the
 //     linear is ONE launch and the main loop reads its activations with immediate-offset shared loads.
 // XIN: what the in-kernel rotation (XR > 0) reads -- 0: x as it is (or gate | up, a run-time flag); 1: the residual stream, which
-// it normalises itself (an instance of its own: the statistics pass must not touch the code of the others).
-template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0>
+// it normalises on the way in.  EPI: 1 = the epilogue adds the residual stream and writes the new one with its sums of squares.
+// Both are instances of their own so that the code of the plain kernel stays as it is.
+template <int K, int MODE, int FAM, int MB, int XR, int XIN = 0, int EPI = 0>
 __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(const __grid_constant__ GemvLaunch p)
 {
     static_assert(XR == 0 || MB == 1, "in-kernel rotation serves one 8-row group");
@@ -149,7 +150,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 v[1] *= HAD_SCALE * __high2float(s01);
                 v[2] *= HAD_SCALE * __low2float(s23);
                 v[3] *= HAD_SCALE * __high2float(s23);
-                if (p.a.out_dtype == EXL3_F32) {
+                if constexpr (EPI == 1) {
+                    gemv_residual_store(p.a, tp_epoch, v, o, m, fnb, lane);
+                } else if (p.a.out_dtype == EXL3_F32) {
                     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.a.out) + o) = make_float4(v[0], v[1], v[2], v[3]);
                 } else if (p.a.tp.world > 1) {
                     gemv_exchange_store(p.a.tp, tp_epoch, p.a.out_dtype == EXL3_BF16, v, o, reinterpret_cast<uint16_t*>(p.a.out), p.a.err);
@@ -291,19 +294,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         } else {
         const int items = (int)(u1 - u0) * XR;
         const bool bf16 = p.a.x_bf16 != 0;
-        // Normalised input: every CTA forms the rows' mean square itself (the rows are a few KB in L2), warps' sums added in
-        // warp order; CTA 0 also stores the new residual stream.
         float rstd[XR];
 #pragma unroll
         for (int r = 0; r < XR; r++) rstd[r] = 1.f;
-        if constexpr (XIN == 1) {
-            ptx::grid_dependency_wait();
-            waited = true;
-            EXL3_STAMP(1);
-#pragma unroll
-            for (int r = 0; r < XR; r++)
-                if (r < rows) rstd[r] = gemv_row_rstd(p.a, r, cta == 0, P, GEMV_CONSUMER_WARPS);
-        }
         constexpr int BATCH = 3;                      // rotations in flight per warp: their loads overlap
         for (int it0 = warp; it0 < items; it0 += GEMV_CONSUMER_WARPS * BATCH) {
             float v[BATCH][4];
@@ -328,6 +321,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 ptx::grid_dependency_wait();
                 waited = true;
                 EXL3_STAMP(1);
+                if constexpr (XIN == 1) {
+#pragma unroll
+                    for (int r = 0; r < XR; r++)
+                        if (r < rows) rstd[r] = gemv_row_rstd(p.a.ssq_in + (size_t)r * p.KG, p.KG, p.a.k, p.a.norm_eps, lane);
+                }
             }
 #pragma unroll
             for (int b = 0; b < BATCH; b++) {
@@ -336,7 +334,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                     for (int e = 0; e < 4; e++) {
                         if constexpr (XIN == 1) {
                             const int row = (it0 + GEMV_CONSUMER_WARPS * b) % XR;
-                            v[b][e] *= gemv_load_norm(p.a.x, p.a.norm_res_in, p.a.norm_weight, xi[b] + e, xi[b] + e - (long long)row * p.a.k,
+                            v[b][e] *= gemv_load_norm(p.a.x, p.a.norm_weight, xi[b] + e, xi[b] + e - (long long)row * p.a.k,
                                                       XR > 1 && row == 1 ? rstd[XR - 1] : rstd[0], bf16);
                         } else {
                             v[b][e] *= p.a.x_glu ? gemv_load_glu(p.a.x, xi[b] + e, p.a.k, bf16) : gemv_load_x(p.a.x, xi[b] + e, bf16);

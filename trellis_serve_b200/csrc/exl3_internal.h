@@ -65,10 +65,17 @@ struct GemvArgs {
     const __half* suh;          //   and the input sign vectors [n_shards][k]
     int x_bf16;
     int x_glu;                  // x is gate | up [rows, 2k]: the input is silu(gate) * up (a down projection's activation)
-    const void* norm_weight;    // set: the input is rmsnorm(x + norm_res_in) * norm_weight (residual add and normalisation of the
-    const void* norm_res_in;    //   layer ahead of a q|k|v or gate|up group); norm_res_in may be null (no residual).  CTA 0 writes
-    void* norm_res_out;         //   x + norm_res_in to norm_res_out (null: not wanted), which must not alias norm_res_in
+    // Normalised input (consumer side of a residual block, XR > 0): x is the residual stream z [rows, k], its sums of squares
+    // per 128 columns are in ssq [rows, k/128] (written by the epilogue of the linear ahead or by the stats kernel), and the
+    // input proper is z * rsqrt(mean square + eps) * norm_weight.
+    const void* norm_weight;
+    const float* ssq_in;
     float norm_eps;
+    // Residual epilogue (producer side): the output block y is added to res_in, the sum z (rounded to the output type) goes to
+    // res_out and its sum of squares per (row, 128 columns) to ssq_out [rows, n_total/128]; y itself is stored only if `out` is set.
+    const void* res_in;
+    void* res_out;
+    float* ssq_out;
     int xf_staged;              // rows <= 2 without x: the fragments in xf are copied to shared memory once (bulk copies)
                                 //   instead of being read from global memory tile by tile
     const __half* svh;          // [n_total]; unused when rotated
@@ -109,6 +116,7 @@ int launch_moe_combine(const __half* yd, const float* w, const int* topk_ids, in
 // exl3_step.cu ------------------------------------------------------------------------------------------
 int launch_rmsnorm_rotate(const void* x, void* residual, const void* weight, float eps, int bf16, const __half* suh, int shards, int rows,
                           int k, void* normed, uint32_t* xf, int mode, cudaStream_t st, void* residual_out = nullptr);
+int launch_residual_ssq(const void* x, const void* res_in, int bf16, int rows, int k, void* res_out, float* ssq, cudaStream_t st);
 int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows, int inter, void* act, uint32_t* xf, int mode,
                            cudaStream_t st);
 size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);

@@ -181,6 +181,40 @@ __global__ void silu_mul_rotate_kernel(const void* __restrict__ gu, int bf16, co
     rotate_store(a, suh + kg * 128, xf, mode, 0, inter >> 4, rows, row, kg, lane);
 }
 
+// z = x (+ res_in, rounded to the activation type) -> res_out, and the sums of squares of z per (row, 128 columns) -> ssq.
+// One warp per (row, block).  The start of a chain of residual blocks whose linears carry the stream in their epilogues.
+__global__ void residual_ssq_kernel(const void* __restrict__ x, const void* __restrict__ res_in, int bf16, int rows, int k,
+                                    void* __restrict__ res_out, float* __restrict__ ssq)
+{
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int kgs = k >> 7;
+    const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)rows * kgs) return;
+    const bool b = bf16 != 0;
+    const long long at = (item / kgs) * k + (item % kgs) * 128 + 4 * lane;
+    float z[4], r[4];
+    load_act4(x, at, b, z);
+    if (res_in) {
+        load_act4(res_in, at, b, r);
+#pragma unroll
+        for (int e = 0; e < 4; e++) z[e] = round_act(z[e] + r[e], b);
+    }
+    if (res_out) store_act4(res_out, at, z, b);
+    float ss = z[0] * z[0] + z[1] * z[1] + z[2] * z[2] + z[3] * z[3];
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
+    if (lane == 0) ssq[item] = ss;
+}
+
+int launch_residual_ssq(const void* x, const void* res_in, int bf16, int rows, int k, void* res_out, float* ssq, cudaStream_t st)
+{
+    const long long items = (long long)rows * (k / 128);
+    if (items == 0) return EXL3_OK;
+    return launch_chained(residual_ssq_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, st, x, res_in, bf16, rows, k, res_out, ssq);
+}
+
 int launch_rmsnorm_rotate(const void* x, void* residual, const void* weight, float eps, int bf16, const __half* suh, int shards, int rows,
                           int k, void* normed, uint32_t* xf, int mode, cudaStream_t st, void* residual_out)
 {

@@ -276,10 +276,20 @@ def silu_mul_rotate(gate_up: torch.Tensor, suh: torch.Tensor, codebook: int, wor
                                                     _ptr(ws), ws.numel(), _stream(gate_up.device)), "exl3_silu_mul_rotate")
 
 
-def run_prerotated(rows: int, b: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int], codebook: int, out: torch.Tensor,
-                   workspace: torch.Tensor, exchange=None) -> torch.Tensor:
+def _residual_ptrs(residual):
+    """residual = (stream in, stream out, sums of squares out) or None -> three pointers for the C ABI."""
+    if residual is None:
+        return None, None, None
+    res_in, res_out, ssq_out = residual
+    return _ptr(res_in), _ptr(res_out), _ptr(ssq_out)
+
+
+def run_prerotated(rows: int, b: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int], codebook: int, out: torch.Tensor | None,
+                   workspace: torch.Tensor, exchange=None, residual=None, out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
     """The fused group on the fragments the kernel ahead left in the workspace; `out` [rows, n_total] fp16 / bf16 (fp32:
-    unrounded accumulators).  `exchange`: row-parallel shard, summed over the ranks inside the kernel."""
+    unrounded accumulators).  `exchange`: row-parallel shard, summed over the ranks inside the kernel.  `residual` =
+    (stream in, stream out, sums of squares out float32 [rows, n_total / 128]): the epilogue carries the residual stream;
+    `out` may then be None (give `out_dtype`)."""
     lib = _lib.load()
     _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
     k, n_total, K = _geometry(b)
@@ -289,19 +299,20 @@ def run_prerotated(rows: int, b: torch.Tensor, svh_cat: torch.Tensor, shard_ends
     ws = _own_or_given(workspace, b.device, workspace_bytes(rows, k, n_total, shards), _workspace)
     ex = exchange if exchange is not None and exchange.world > 1 else None
     with torch.cuda.device(b.device):
+        code = _dtype_code(out, True) if out is not None else _dtype_code(residual[1])
         _lib.check(lib.exl3_linear_prerotated(_ptr(b), K, codebook, _ptr(svh_cat), _lib.int_array(shard_ends), shards, rows, k, n_total,
-                                              _ptr(out), _dtype_code(out, True), _ptr(ws), ws.numel(),
+                                              _ptr(out), code, _ptr(ws), ws.numel(),
                                               ex.peer_regions if ex else None, ex.rank if ex else 0, ex.world if ex else 1,
-                                              ex.max_elems if ex else 0, _ptr(ex.state) if ex else None, _stream(b.device)),
-                   "exl3_linear_prerotated")
+                                              ex.max_elems if ex else 0, _ptr(ex.state) if ex else None, *_residual_ptrs(residual),
+                                              _stream(b.device)), "exl3_linear_prerotated")
     return out
 
 
 def run_rmsnorm(x: torch.Tensor, residual_in: torch.Tensor | None, residual_out: torch.Tensor | None, weight: torch.Tensor, eps: float,
                 b: torch.Tensor, suh_cat: torch.Tensor, svh_cat: torch.Tensor, shard_ends: list[int], codebook: int, out: torch.Tensor,
                 workspace: torch.Tensor | None = None) -> torch.Tensor:
-    """The fused group on rmsnorm(x + residual_in) * weight, with residual_out = x + residual_in written to a second buffer: up
-    to two rows one launch (every CTA of the GEMV forms the mean square itself)."""
+    """The fused group on rmsnorm(x + residual_in) * weight, with residual_out = x + residual_in written to a second buffer:
+    `residual_ssq` followed by `run_normed`, for a caller whose stream does not come out of a linear's epilogue."""
     _require_cuda(x, "x")
     lib = _lib.load()
     _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
@@ -315,10 +326,37 @@ def run_rmsnorm(x: torch.Tensor, residual_in: torch.Tensor | None, residual_out:
     return out
 
 
-def run_glu(gate_up: torch.Tensor, b: torch.Tensor, suh: torch.Tensor, svh_cat: torch.Tensor, codebook: int, out: torch.Tensor,
-            workspace: torch.Tensor | None = None, exchange=None) -> torch.Tensor:
+def residual_ssq(x: torch.Tensor, residual_in: torch.Tensor | None, residual_out: torch.Tensor | None, ssq: torch.Tensor) -> None:
+    """z = x (+ residual_in) -> residual_out (optional) and the sums of squares of z per (row, 128 columns) -> ssq float32
+    [rows, k / 128]: the start of a chain of residual blocks whose linears carry the stream in their epilogues."""
+    _require_cuda(x, "x")
+    rows, k = x.shape
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().exl3_residual_ssq(_ptr(x), _ptr(residual_in), _dtype_code(x), rows, k, _ptr(residual_out), _ptr(ssq),
+                                                 _stream(x.device)), "exl3_residual_ssq")
+
+
+def run_normed(z: torch.Tensor, ssq: torch.Tensor, weight: torch.Tensor, eps: float, b: torch.Tensor, suh_cat: torch.Tensor,
+               svh_cat: torch.Tensor, shard_ends: list[int], codebook: int, out: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """The fused group on rmsnorm(z) * weight, z a residual stream and ssq its sums of squares per 128 columns (from a linear's
+    residual epilogue or `residual_ssq`): up to two rows the GEMV normalises on the way into its own rotation (one launch)."""
+    _require_cuda(z, "z")
+    lib = _lib.load()
+    _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
+    k, n_total, K = _geometry(b)
+    rows, shards = z.shape[0], len(shard_ends) + 1
+    ws = _own_or_given(workspace, b.device, workspace_bytes(rows, k, n_total, shards), _workspace)
+    with torch.cuda.device(b.device):
+        _lib.check(lib.exl3_normed_linear(_ptr(z), _dtype_code(z), _ptr(ssq), _ptr(weight), float(eps), _ptr(b), K, codebook, _ptr(suh_cat),
+                                          _ptr(svh_cat), _lib.int_array(shard_ends), shards, rows, k, n_total, _ptr(out), _dtype_code(out, True),
+                                          _ptr(ws), ws.numel(), _stream(b.device)), "exl3_normed_linear")
+    return out
+
+
+def run_glu(gate_up: torch.Tensor, b: torch.Tensor, suh: torch.Tensor, svh_cat: torch.Tensor, codebook: int, out: torch.Tensor | None,
+            workspace: torch.Tensor | None = None, exchange=None, residual=None) -> torch.Tensor | None:
     """Down projection of silu(gate) * up straight from `gate_up` [rows, 2k]: up to two rows the activation is computed inside
-    the GEMV's own input rotation (one launch, no activation buffer).  `exchange` as in `run_prerotated`."""
+    the GEMV's own input rotation (one launch, no activation buffer).  `exchange` and `residual` as in `run_prerotated`."""
     _require_cuda(gate_up, "gate_up")
     lib = _lib.load()
     _lib.init_device(b.device.index if b.device.index is not None else torch.cuda.current_device())
@@ -329,10 +367,12 @@ def run_glu(gate_up: torch.Tensor, b: torch.Tensor, suh: torch.Tensor, svh_cat: 
     ws = _own_or_given(workspace, b.device, workspace_bytes(rows, k, n_total, 1), _workspace)
     ex = exchange if exchange is not None and exchange.world > 1 else None
     with torch.cuda.device(b.device):
+        code = _dtype_code(out, True) if out is not None else _dtype_code(residual[1])
         _lib.check(lib.exl3_glu_linear(_ptr(gate_up), _dtype_code(gate_up), _ptr(b), K, codebook, _ptr(suh), _ptr(svh_cat), _lib.int_array([]), 1,
-                                       rows, k, n_total, _ptr(out), _dtype_code(out, True), _ptr(ws), ws.numel(),
+                                       rows, k, n_total, _ptr(out), code, _ptr(ws), ws.numel(),
                                        ex.peer_regions if ex else None, ex.rank if ex else 0, ex.world if ex else 1,
-                                       ex.max_elems if ex else 0, _ptr(ex.state) if ex else None, _stream(b.device)), "exl3_glu_linear")
+                                       ex.max_elems if ex else 0, _ptr(ex.state) if ex else None, *_residual_ptrs(residual),
+                                       _stream(b.device)), "exl3_glu_linear")
     return out
 
 

@@ -1,11 +1,12 @@
 """One decoded token through a dense transformer of EXL3 linears: the step either side of the kernels.
 
-    per layer:  residual += h;  a = RMSNorm(residual)          -> inside the input rotation of q|k|v       (rmsnorm linear)
+    per layer:  a = RMSNorm(residual)                          -> inside the input rotation of q|k|v       (normed linear)
                 q|k|v = EXL3(a);  RoPE(q, k);  KV cache append;  attention over the cache
                 o = EXL3(attention)                             -> rotation launch, then the GEMV
-                residual += o;  a = RMSNorm(residual)           -> inside the input rotation of gate|up
+                residual += o                                   -> in the epilogue of o (with the stream's sums of squares)
+                a = RMSNorm(residual)                           -> inside the input rotation of gate|up
                 g|u = EXL3(a);  act = SiLU(g) * u               -> computed inside down's own input rotation (glu linear; from three
-                h = EXL3(act)                                      rows up: silu_mul_rotate ahead of the GEMV)
+                h = EXL3(act);  residual += h                      rows up: silu_mul_rotate ahead of the GEMV); the sum in down's epilogue
 
 Every linear is ONE decode-GEMV launch whose activations were rotated by the kernel ahead of it; rotary embedding, cache
 append and attention are stock torch (`scaled_dot_product_attention`): they are not part of the quantized-linear path and
@@ -115,11 +116,13 @@ class DecodeStep:
         mk = lambda w: torch.empty((rows, w), dtype=dtype, device=dev)
         self.h_in = torch.zeros((rows, h), dtype=dtype, device=dev)          # the step's input: the token's embedding
         self.h, self.residual, self.residual2 = mk(h), mk(h), mk(h)        # the residual stream alternates between two buffers
+        self.ssq = torch.zeros((rows, h // 128), dtype=torch.float32, device=dev)     # its sums of squares per 128 columns
+        self.ssq2 = torch.zeros_like(self.ssq)
         self.qkv, self.attn, self.o_out, self.gu, self.out = mk(q + 2 * kv), mk(q), mk(h), mk(2 * f), mk(h)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.linear_launches = s.layers * 4
-        small = 0 if rows <= 2 else 3                                 # normalisation x2 and activation kernels run only from three rows up
-        self.fused_launches = s.layers * ((0 if attention == "library" else 1) + small)   # (+ rotation ahead of o with stock attention)
+        small = 0 if rows <= 2 else 5                                 # normalisation x2, activation and stream x2 kernels: only from three rows up
+        self.fused_launches = 1 + s.layers * ((0 if attention == "library" else 1) + small)   # the stream's start (+ rotation ahead of o with stock attention)
         self.attention_launches = s.layers if attention == "library" else None   # RoPE, append, attention and merge in one
 
     # ---- bytes
@@ -170,20 +173,27 @@ class DecodeStep:
     def step(self) -> torch.Tensor:
         """One token through all layers on the current stream; returns the final normalised hidden state."""
         cb, ws, ex, rows = self.codebook, self.workspace, self.exchange, self.rows
-        self.residual.zero_()
-        h = self.h_in
+        fused = ex is not None or self.tp_size == 1      # the linears' epilogues carry the residual stream (NCCL sums outside them)
+        z, z2, ssq, ssq2 = self.residual, self.residual2, self.ssq, self.ssq2
+        lin.residual_ssq(self.h_in, None, z, ssq)           # the stream starts as the token's embedding
         for i, (qkv, o, gu, down, norms) in enumerate(self.layers):
-            lin.run_rmsnorm(h, self.residual, self.residual2, norms[0], self.shape.eps, qkv.packed, qkv.suh, qkv.svh, qkv.ends, cb, self.qkv, ws)
+            lin.run_normed(z, ssq, norms[0], self.shape.eps, qkv.packed, qkv.suh, qkv.svh, qkv.ends, cb, self.qkv, ws)
             if not self._attention(i, o.suh):
                 lin.rotate_fragments(self.attn, o.suh, cb, ws)
-            lin.run_prerotated(rows, o.packed, o.svh, o.ends, cb, self.o_out, ws, exchange=ex)
-            self._reduce(self.o_out)
-            lin.run_rmsnorm(self.o_out, self.residual2, self.residual, norms[1], self.shape.eps, gu.packed, gu.suh, gu.svh, gu.ends, cb, self.gu, ws)
-            lin.run_glu(self.gu, down.packed, down.suh, down.svh, cb, self.h, ws, exchange=ex)
-            self._reduce(self.h)
-            h = self.h
-        self.out.copy_(torch.nn.functional.rms_norm((self.residual + h).float(), (self.shape.hidden,), self.final_norm.float(),
-                                                    self.shape.eps).to(self.dtype))
+            if fused:
+                lin.run_prerotated(rows, o.packed, o.svh, o.ends, cb, self.o_out, ws, exchange=ex, residual=(z, z2, ssq2))
+            else:
+                lin.run_prerotated(rows, o.packed, o.svh, o.ends, cb, self.o_out, ws)
+                self._reduce(self.o_out)
+                lin.residual_ssq(self.o_out, z, z2, ssq2)
+            lin.run_normed(z2, ssq2, norms[1], self.shape.eps, gu.packed, gu.suh, gu.svh, gu.ends, cb, self.gu, ws)
+            if fused:
+                lin.run_glu(self.gu, down.packed, down.suh, down.svh, cb, self.h, ws, exchange=ex, residual=(z2, z, ssq))
+            else:
+                lin.run_glu(self.gu, down.packed, down.suh, down.svh, cb, self.h, ws)
+                self._reduce(self.h)
+                lin.residual_ssq(self.h, z2, z, ssq)
+        self.out.copy_(torch.nn.functional.rms_norm(z.float(), (self.shape.hidden,), self.final_norm.float(), self.shape.eps).to(self.dtype))
         return self.out
 
     def capture(self, warmup: int = 2) -> None:
