@@ -424,6 +424,12 @@ def decode_step_rate(dev, args, rank: int, world: int, reducer, dist, layers: in
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
     ms = timed(step.replay, 20)
+    same = True
+    if dist is not None and world > 1:
+        # The residual stream is replicated: after the exchanges every rank must hold the same bits.
+        outs = [torch.empty_like(step.residual) for _ in range(world)]
+        dist.all_gather(outs, step.residual)
+        same = all(torch.equal(o.view(torch.int16), outs[0].view(torch.int16)) for o in outs)
     hin = torch.randn(step.h_in.shape).to(step.dtype).pin_memory()
     hout = torch.empty(step.out.shape, dtype=step.dtype).pin_memory()
     ms_e2e = timed(lambda: step.forward_host(hin, hout), 20)
@@ -436,7 +442,7 @@ def decode_step_rate(dev, args, rank: int, world: int, reducer, dist, layers: in
            "frac_of_hbm_per_rank": (step.packed_bytes + step.kv_bytes) / ms / 1e6 / peak, "peak_source": f"of {kind}",
            "launches_per_token": {"exl3_linears": step.linear_launches, "fused_producers": step.fused_launches,
                                   "attention_and_rope": step.attention_launches or "stock torch"},
-           "outputs_finite": finite}
+           "outputs_finite": finite, "same_bits_on_every_rank": same}
     del step
     torch.cuda.empty_cache()
     return res

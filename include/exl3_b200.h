@@ -180,8 +180,10 @@ exl3_status exl3_rmsnorm_linear(const void *x, int x_dtype, const void *residual
  *                          the queries as it loads them (qkv is left unrotated) and the warp that owns cache slot `*position`
  *                          rotates the new key into k_cache and copies the new value into v_cache before it reads them; same
  *                          roundings, same bits.  qkv must be 8-byte aligned.
- * Before it waits for the kernel ahead of it in the stream, an attention call walks through its merge code once on what the
- * scratch buffer holds, storing nothing (instruction-cache warm-up): the scratch must be readable then, nothing else is touched.
+ * Before it waits for the kernel ahead of it in the stream, an attention call reads `*position` and requests the cache rows
+ * below it (like weights: they must be complete in memory before the call is enqueued behind this library's kernels; rows
+ * written by earlier steps are), and walks through its merge code once on what the scratch buffer holds, storing nothing
+ * (instruction-cache warm-up).  Row `*position` and qkv are read after the wait.
  * The reference leaves attention to its engine; no counterpart there. */
 size_t exl3_attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);
 exl3_status exl3_rope_append(void *qkv, int dtype, int rows, int q_heads, int kv_heads, int head_dim, const float *cos_table,

@@ -55,6 +55,39 @@ def _worker(rank, world, port, out_dir):
         ar.check()
         lin.device_error(dev)
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (rank, "fused", call)
+    # The residual epilogue behind the fused exchange (one and two rows, a pre-rotated input and a gate | up input): the new
+    # stream is round(sum over ranks of y + z), the same bits on every rank, and its sums of squares are those of what was stored.
+    for call, (rows, k, n, K, dtype, glu) in enumerate([(1, 1024, 5120, 3, torch.float16, False), (2, 512, 5120, 4, torch.bfloat16, True),
+                                                        (1, 640, 5120, 3, torch.bfloat16, True), (2, 2176, 5120, 3, torch.float16, False)]):
+        gen.manual_seed(9000 + 10 * call + rank)
+        w = random_packed(k, n, K, gen, dev)
+        suh, svh = random_signs(k, gen, dev, 1), (random_signs(n, gen, dev).view(-1) / 16).half()
+        ws = torch.zeros(lin.workspace_bytes(16, k, n, 1), dtype=torch.uint8, device=dev)
+        gen.manual_seed(9500 + call)                                        # the residual stream is replicated: same on every rank
+        z = torch.randn((rows, n), device=dev, generator=gen).to(dtype)
+        gen.manual_seed(9700 + 10 * call + rank)
+        y, z2 = torch.empty((rows, n), dtype=dtype, device=dev), torch.empty((rows, n), dtype=dtype, device=dev)
+        ssq = torch.zeros((rows, n // 128), dtype=torch.float32, device=dev)
+        if glu:
+            gu = torch.randn((rows, 2 * k), device=dev, generator=gen).to(dtype)
+            want_y = ar(lin.run_glu(gu, w, suh.view(-1), svh, 0, torch.empty_like(y), ws))
+            lin.run_glu(gu, w, suh.view(-1), svh, 0, y, ws, exchange=ar, residual=(z, z2, ssq))
+        else:
+            x = torch.randn((rows, k), device=dev, generator=gen).to(dtype)
+            want_y = ar(lin.run(x, w, suh, svh, [], 0))
+            lin.rotate_fragments(x, suh, 0, ws)
+            lin.run_prerotated(rows, w, svh, [], 0, y, ws, exchange=ar, residual=(z, z2, ssq))
+        torch.cuda.synchronize()
+        ar.check()
+        lin.device_error(dev)
+        assert torch.equal(y.view(torch.int16), want_y.view(torch.int16)), (rank, "residual y", call)
+        want_z = (want_y.float() + z.float()).to(dtype)
+        assert torch.equal(z2.view(torch.int16), want_z.view(torch.int16)), (rank, "residual stream", call)
+        want_ssq = want_z.float().view(rows, n // 128, 128).pow(2).sum(-1)
+        assert float(((ssq - want_ssq).abs() / want_ssq).max()) <= 1e-5, (rank, "sums of squares", call)
+        both = [torch.empty_like(z2) for _ in range(world)]
+        dist.all_gather(both, z2)
+        assert all(torch.equal(b.view(torch.int16), both[0].view(torch.int16)) for b in both), (rank, "replicated stream", call)
     # CUDA-graph replay: the call counter lives on the device, so a replay is a new call
     buf = torch.zeros((1, 5120), dtype=torch.float16, device=dev)
     src = torch.zeros_like(buf)

@@ -469,17 +469,16 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     // Nothing to do until the kernel ahead has finished: walk through the merge code once without storing anything, so that
     // the CTA that ends up merging runs it from the instruction cache (it reads last step's partials; they are only looked at).
     attention_merge_cta<G>(part, red, blockIdx.z, blockIdx.y, kv_heads, q_heads, gridDim.x, rows, y_out, bf16 != 0, suh, xf, mode, true);
-    ptx::grid_dependency_wait();
-    ATT_STAMP(1);
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = *pos_ptr;
     const int T = pos + 1;                                        // valid cache positions
     const int heads = q_heads + 2 * kv_heads;
     const bool b = bf16 != 0;
-    // Cache rows below `pos` are requested first and all at once -- the key row of the lane's position whole and all of the
-    // warp's 32 value rows -- so one round of memory latency covers them; row `pos` itself may come from this kernel's own
-    // append and is fetched after it.
+    // Cache rows below `pos` were written by earlier steps: like weights they are constants of this launch and are requested
+    // before the wait for the kernel ahead and all at once -- the key row of the lane's position whole and all of the warp's
+    // 32 value rows -- so their trip from memory overlaps that kernel's tail; row `pos` itself comes from the kernel ahead or
+    // from this kernel's own append and is fetched after the wait.
     const int t0 = split * ATT_CHUNK + warp * 32;
     const int t = t0 + lane;
     const long long rowbase = (((long long)row * kv_heads + kvh) * t_max) * ATT_D;
@@ -493,6 +492,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     }
 #pragma unroll
     for (int u = 0; u < 32; u++) vw[u] = (t0 + u < pos) ? *reinterpret_cast<const uint2*>(vbase + (long long)u * ATT_D * 2) : make_uint2(0u, 0u);
+    ptx::grid_dependency_wait();
+    ATT_STAMP(1);
     const int splits = gridDim.x;
     float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
     __shared__ float wgt[G][ATT_WARPS];
