@@ -82,6 +82,8 @@ static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLau
     size_t xs_bytes = 0;
     if (fused) xs_bytes = GEMV_XS_ZERO_BYTES + (size_t)(l.units_q + 1) * gemv_xs_slot_bytes(a.mode, a.rows);
     const size_t budget = (size_t)d->max_smem_optin / GEMV_CTAS_PER_SM - 2048 - GEMV_FIXED_SMEM;
+    // Without the in-kernel rotation the fragments of a stage's units are copied behind its weights (see the kernel).
+    const uint32_t frag_bytes = fused ? 0u : gemv_xs_slot_bytes(a.mode, a.rows);
     int stages = 0;
     for (size_t target = GEMV_STAGE_TARGET; target >= 8 * 1024 && stages < 2; target -= 8 * 1024) {
         int ups = (int)((target + unit_bytes - 1) / unit_bytes);
@@ -90,7 +92,7 @@ static int plan_gemv(const GemvArgs& a, const DeviceInfo* d, bool fused, GemvLau
         if (per_cta_max < ups) ups = (int)per_cta_max;
         if (ups < 1) ups = 1;
         l.units_per_stage = ups;
-        l.stage_stride = (uint32_t)ups * unit_bytes;
+        l.stage_stride = (uint32_t)ups * (unit_bytes + frag_bytes);
         if (xs_bytes + 2 * (size_t)l.stage_stride > budget) continue;
         stages = (int)(GEMV_RING_TARGET / l.stage_stride);
         const int cap = (int)((budget - xs_bytes) / l.stage_stride);

@@ -84,12 +84,34 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     // stage number j is simply units [u0 + j * ups, +ups) and lives in slot j % stages.
     const int ups = p.units_per_stage;
     const int n_fills = (int)((u1 - u0 + ups - 1) / ups);
-    auto issue_fill = [&](int j, int slot) {       // one thread: start the copy of stage number j into `slot`
+    // Without the in-kernel rotation (XR == 0: three rows and more) the activation fragments of a stage's units travel with
+    // its weights: [weights of ups units][fragments of ups units], F_BYTES of fragments per unit, copied from the fragment
+    // buffer the rotation kernel ahead wrote (units of a column block are consecutive there) -- every fragment crosses the
+    // L2 once per CTA instead of once per warp and tile.
+    const uint32_t F_BYTES = XR == 0 ? gemv_xs_slot_bytes(MODE, rows) : 0u;
+    auto issue_frags = [&](long long u, int n, int slot) {      // one thread, after the wait for the kernel ahead
+        unsigned char* dst = stage0 + (size_t)slot * p.stage_stride + (size_t)ups * W_BYTES;
+        while (n > 0) {
+            const int unb = (int)(u / p.KG), ukg = (int)(u - (long long)unb * p.KG);
+            int run = p.KG - ukg;
+            if (run > n) run = n;
+            int s = 0;
+            while (s < p.a.n_shards - 1 && unb >= p.a.shard_end_blocks[s]) s++;
+            ptx::bulk_g2s(dst, p.a.xf + s * p.xf_shard_stride + (long long)ukg * (F_BYTES / 4), (uint32_t)run * F_BYTES, &full[slot]);
+            dst += (size_t)run * F_BYTES;
+            u += run;
+            n -= run;
+        }
+    };
+    auto issue_fill = [&](int j, int slot, bool frags) {       // one thread: start the copy of stage number j into `slot`
         const long long u = u0 + (long long)j * ups;
         const long long left = u1 - u;
-        const uint32_t bytes = (uint32_t)(left < ups ? left : ups) * W_BYTES;
-        ptx::mbar_arrive_expect_tx(&full[slot], bytes);
+        const int n = (int)(left < ups ? left : ups);
+        const uint32_t bytes = (uint32_t)n * W_BYTES;
+        ptx::mbar_arrive_expect_tx(&full[slot], bytes + (uint32_t)n * F_BYTES);
         ptx::bulk_g2s(stage0 + (size_t)slot * p.stage_stride, p.a.packed + (long long)u * (512 * K), bytes, &full[slot]);
+        if constexpr (XR == 0)
+            if (frags) issue_frags(u, n, slot);
     };
     EXL3_STAMP(0);
     if (threadIdx.x == 0) {
@@ -102,7 +124,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
         if constexpr (XR > 0) ptx::mbar_init(xbar, 1);
         ptx::mbar_fence_init();
         // Weights are constants: the first lap of copies starts before the kernel ahead of this one has finished.
-        for (int j = 0; j < p.stages && j < n_fills; j++) issue_fill(j, j);
+        for (int j = 0; j < p.stages && j < n_fills; j++) issue_fill(j, j, false);
     }
     __syncthreads();
 
@@ -111,8 +133,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     // ---------------------------------------------------------------------- consumers
     // Everything below reads or writes memory other kernels write (activations, workspace, output) and so comes after
     // the wait for the kernel ahead; with the in-kernel rotation the (constant) sign vectors are fetched before it.
-    if constexpr (XR == 0) ptx::grid_dependency_wait();
-    if constexpr (XR == 0) EXL3_STAMP(1);
+    if constexpr (XR == 0) {
+        ptx::grid_dependency_wait();
+        EXL3_STAMP(1);
+        if (threadIdx.x == 0) {                 // the fragments of the first lap follow their weights now that they exist
+            reinterpret_cast<uint4*>(smem + 224)[0] = make_uint4(0u, 0u, 0u, 0u);      // read by lanes whose batch row does not exist
+            for (int j = 0; j < p.stages && j < n_fills; j++) {
+                const long long u = u0 + (long long)j * ups;
+                const long long left = u1 - u;
+                issue_frags(u, (int)(left < ups ? left : ups), j);
+            }
+        }
+        __syncthreads();
+    }
     const int nt = warp & 7, kq = warp >> 3;
     const int g = lane >> 2, q = lane & 3;
     const CodebookConst cbc = {p.mul, p.add};
@@ -249,9 +282,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     //   XR == 0: straight from global memory (they are tiny and stay in L1/L2), written by the kernel ahead;
     //   XR  > 0: from the shared-memory slots filled below, slot i = unit u0 + i.
     using Frag = typename std::conditional<FW == 4, uint4, uint2>::type;
-    const Frag* x_base[MB];
-    uint32_t x_lane[MB], x_tile[MB], x_unit[MB];      // element offsets: lane, per 16-row tile, per unit (8 tiles)
-    const uint32_t x_shard_elems = (uint32_t)(p.xf_shard_stride / FW);
+    uint32_t f_lane[MB], f_tile[MB], f_unit[MB];      // XR == 0: byte offsets in a stage's fragment area: lane, per tile, per unit
     uint32_t xaddr = 0, xstep = 0;                    // XR > 0: shared address of the lane's fragments, bytes per unit
     constexpr uint32_t XS_TILE = (uint32_t)(XR > 0 ? XR : 1) * 4u * FW * 4u;      // bytes per 16-row tile in a slot
     constexpr uint32_t XS_SLOT = 8u * XS_TILE;
@@ -259,10 +290,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 #pragma unroll
         for (int mb = 0; mb < MB; mb++) {
             const bool ok = (g + 8 * mb) < rows;
-            x_base[mb] = reinterpret_cast<const Frag*>(ok ? static_cast<const void*>(p.a.xf) : p.zeros);
-            x_lane[mb] = ok ? (uint32_t)((g + 8 * mb) * 4 + q + kq * 4 * rows * 4) : 0u;
-            x_tile[mb] = ok ? (uint32_t)(rows * 4) : 0u;
-            x_unit[mb] = ok ? (uint32_t)(8 * rows * 4) : 0u;
+            f_lane[mb] = ok ? (uint32_t)ups * W_BYTES + (uint32_t)((kq * 4 * rows + g + 8 * mb) * 4 + q) * FW * 4u : 0u;
+            f_tile[mb] = ok ? (uint32_t)(rows * 4) * FW * 4u : 0u;
+            f_unit[mb] = ok ? F_BYTES : 0u;
         }
     } else {
         unsigned char* xs = smem + p.xs_off;
@@ -397,11 +427,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
     int slot = 0, stage_left = ups, stage_no = 0;
     uint32_t phase = 0;
     uint32_t waddr = stage0_addr + w_off;
-    uint32_t xu[MB];
+    uint32_t fx[MB];                                  // XR == 0: shared address of the lane's fragments of the current unit
+    const uint32_t zero_addr = ptx::smem_addr(smem + 224);
     if constexpr (XR == 0) {
 #pragma unroll
-        for (int mb = 0; mb < MB; mb++)
-            xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems + (uint32_t)kg * x_unit[mb] : 0u);
+        for (int mb = 0; mb < MB; mb++) fx[mb] = f_unit[mb] ? stage0_addr + f_lane[mb] : zero_addr;
     }
     int remaining = (int)(u1 - u0);
     if (remaining > 0) wait_stage(0, 0);
@@ -427,7 +457,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
 #pragma unroll
                 for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-                    for (int T = 0; T < 4; T++) bfrag[mb][T] = __ldg(x_base[mb] + (xu[mb] + T * x_tile[mb]));
+                    for (int T = 0; T < 4; T++) {
+                        if constexpr (FW == 4) bfrag[mb][T] = ptx::lds128(fx[mb] + T * f_tile[mb]);
+                        else bfrag[mb][T] = ptx::lds64(fx[mb] + T * f_tile[mb]);
+                    }
             } else {
 #pragma unroll
                 for (int T = 0; T < 4; T++) {
@@ -464,7 +497,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             waddr += W_BYTES;
             if constexpr (XR == 0) {
 #pragma unroll
-                for (int mb = 0; mb < MB; mb++) xu[mb] += x_unit[mb];
+                for (int mb = 0; mb < MB; mb++) fx[mb] += f_unit[mb];
             } else {
                 xaddr += xstep;
             }
@@ -475,7 +508,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
             // it are ordered ahead of the copy by the acquire-release counter update).
             if (lane == 0 && ptx::atom_add_acq_rel_cta_shared(&released[slot], 1) == GEMV_CONSUMER_WARPS - 1) {
                 released[slot] = 0;
-                if (stage_no + p.stages < n_fills) issue_fill(stage_no + p.stages, slot);
+                if (stage_no + p.stages < n_fills) issue_fill(stage_no + p.stages, slot, true);
             }
             stage_no++;
             stage_left = ups;
@@ -484,17 +517,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, GEMV_CTAS_PER_SM) gemv_kernel(co
                 phase ^= 1;
             }
             waddr = stage0_addr + (uint32_t)slot * p.stage_stride + w_off;
+            if constexpr (XR == 0) {
+#pragma unroll
+                for (int mb = 0; mb < MB; mb++) fx[mb] = f_unit[mb] ? stage0_addr + (uint32_t)slot * p.stage_stride + f_lane[mb] : zero_addr;
+            }
             if (remaining > 0) wait_stage(slot, phase);
         }
         if (kg == p.KG) {                                    // column block finished
             flush(nb);
             kg = 0;
             nb++;
-            if constexpr (XR == 0) {
-                while (shard < p.a.n_shards - 1 && nb >= p.a.shard_end_blocks[shard]) shard++;
-#pragma unroll
-                for (int mb = 0; mb < MB; mb++) xu[mb] = x_lane[mb] + (x_unit[mb] ? (uint32_t)shard * x_shard_elems : 0u);
-            }
+
         }
     }
     EXL3_STAMP(4);
