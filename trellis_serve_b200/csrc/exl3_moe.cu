@@ -290,11 +290,12 @@ int launch_moe_gemm(MoeGemmLaunch l, int K, int codebook, int mode, cudaStream_t
     int grid = d->sm_count * MOE_CTAS_PER_SM;
     if (grid > GEMV_MAX_GRID) grid = GEMV_MAX_GRID;
     const uint32_t unit_bytes = 2048u * K;
+    const uint32_t frag_bytes = 8u * MOE_BLOCK_ROWS * 4u * (uint32_t)gemv_frag_words(mode) * 4u;   // a unit's fragments ride with its weights
     int ups = (int)((24u * 1024u + unit_bytes - 1) / unit_bytes);
     const int UB = l.KG * l.NB;
     if (ups > UB) ups = UB;
     l.units_per_stage = ups;
-    l.stage_stride = (uint32_t)ups * unit_bytes;
+    l.stage_stride = (uint32_t)ups * (unit_bytes + frag_bytes);
     const size_t fixed = 256 + GEMV_MAX_ROWS * 128 * 4;
     int stages = (int)((96u * 1024u) / l.stage_stride);
     const int cap = (int)((d->max_smem_optin / MOE_CTAS_PER_SM - 2048 - fixed) / l.stage_stride);

@@ -53,6 +53,9 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
 {
     constexpr int FW = gemv_frag_words(MODE);
     constexpr uint32_t W_BYTES = 2048u * K;
+    // Fragments of one unit (8 k-tiles x 8 rows x 4 lanes x FW words): they are copied into the stage behind its weights,
+    // [weights of units_per_stage units][fragments of units_per_stage units], so a fragment crosses the L2 once per CTA.
+    constexpr uint32_t F_BYTES = 8u * MOE_BLOCK_ROWS * 4u * FW * 4u;
     using Frag = typename std::conditional<FW == 4, uint4, uint2>::type;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -104,9 +107,24 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
                 }
                 const int e = p.expert_ids[b];
                 const uint32_t bytes = (uint32_t)n * W_BYTES;
-                ptx::mbar_arrive_expect_tx(&full[s], bytes);
+                ptx::mbar_arrive_expect_tx(&full[s], bytes + (uint32_t)n * F_BYTES);
                 ptx::bulk_g2s(stage0 + (size_t)s * p.stage_stride, p.packed + e * p.expert_stride + (long long)in_blk * (512ll * K), bytes,
                               &full[s]);
+                {   // the units' fragments: consecutive row blocks of a column block are consecutive in the fragment buffer
+                    unsigned char* dst = stage0 + (size_t)s * p.stage_stride + (size_t)p.units_per_stage * W_BYTES;
+                    int at = in_blk, todo = n;
+                    while (todo > 0) {
+                        const int fnb = at / p.KG, fkg = at - fnb * p.KG;
+                        int run = p.KG - fkg;
+                        if (run > todo) run = todo;
+                        const long long shard = fnb >= p.shard_end_block ? 1 : 0;
+                        const uint32_t* src = p.xf + (shard * p.xf_shard_stride + ((long long)b * (p.KG * 8) + fkg * 8) * 32) * FW;
+                        ptx::bulk_g2s(dst, src, (uint32_t)run * F_BYTES, &full[s]);
+                        dst += (size_t)run * F_BYTES;
+                        at += run;
+                        todo -= run;
+                    }
+                }
                 left -= n;
                 in_blk += n;
                 if (in_blk == UB) {
@@ -216,8 +234,8 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
     if (stage_units > UB - in_blk) stage_units = UB - in_blk;
     if (stage_units > left) stage_units = left;
     uint32_t waddr = stage0_addr + w_off;
-    const Frag* xbase = reinterpret_cast<const Frag*>(p.xf);
-    const uint32_t lane_elem = (uint32_t)(g * 4 + q) + (uint32_t)(kq * 4) * 32u;
+    const uint32_t f_off = (uint32_t)p.units_per_stage * W_BYTES + ((uint32_t)(g * 4 + q) + (uint32_t)(kq * 4) * 32u) * FW * 4u;
+    uint32_t faddr = stage0_addr + f_off;
     bool dirty = false;
     wait_stage(0, 0);
 
@@ -227,8 +245,6 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
         int run = p.KG - kg;
         if (run > stage_units - in_stage) run = stage_units - in_stage;
         if (run > left) run = left;
-        const uint32_t shard = nb >= p.shard_end_block ? 1u : 0u;
-        const Frag* xp = xbase + (shard * p.xf_shard_stride + ((long long)b * KT + kg * 8) * 32 + lane_elem);
         left -= run;
         in_blk += run;
         in_stage += run;
@@ -241,7 +257,10 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
             for (int i = 0; i < K; i++) L[i] = ptx::lds32(waddr + i * 128u);
             Frag bfrag[4];
 #pragma unroll
-            for (int T = 0; T < 4; T++) bfrag[T] = __ldg(xp + T * 32);
+            for (int T = 0; T < 4; T++) {
+                if constexpr (FW == 4) bfrag[T] = ptx::lds128(faddr + T * 32u * FW * 4u);
+                else bfrag[T] = ptx::lds64(faddr + T * 32u * FW * 4u);
+            }
 
             auto tile = [&](auto tconst) {
                 constexpr int T = decltype(tconst)::value;
@@ -265,7 +284,7 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
             tile(std::integral_constant<int, 2>{});
             tile(std::integral_constant<int, 3>{});
             waddr += W_BYTES;
-            xp += 8 * 32;
+            faddr += F_BYTES;
         }
         const bool stage_done = in_stage == stage_units;
         if (stage_done) {
@@ -292,6 +311,7 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
             if (stage_units > UB - in_blk) stage_units = UB - in_blk;
             if (stage_units > left) stage_units = left;
             waddr = stage0_addr + (uint32_t)slot * p.stage_stride + w_off;
+            faddr = stage0_addr + (uint32_t)slot * p.stage_stride + f_off;
             wait_stage(slot, phase);
         }
     }
