@@ -173,7 +173,8 @@ exl3_status exl3_rmsnorm_linear(const void *x, int x_dtype, const void *residual
  *                          multiple of kv_heads, ratio 1, 2, 4, 5 or 8), split over the cache in chunks of 128 positions
  *                          and merged in a fixed order by the last CTA of each (row, KV head) to finish (one launch);
  *                          out [rows, q_heads * 128] in `dtype` (may be NULL).  scratch: exl3_attention_scratch_bytes(),
- *                          zero-filled once before its first use (arrival counters; every call leaves them zero).  suh_next != NULL: a head is one rotation block of the o
+ *                          256-byte aligned, zero-filled once before its first use (an error word that exl3_device_error reads,
+ *                          then arrival counters that every call leaves zero); exl3_init_device must have run.  suh_next != NULL: a head is one rotation block of the o
  *                          projection's input, so the merge also writes that linear's rotated fragments into `workspace`
  *                          (as exl3_rotate_fragments would from `out`) and exl3_linear_prerotated can follow directly.
  *   exl3_rope_decode_attention  the two above in one call and one launch: the attention kernel rotates

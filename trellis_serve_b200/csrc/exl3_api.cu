@@ -94,6 +94,7 @@ exl3_status exl3_init_device(int device)
             d.ready = true;
             rc = gemv_init_device();
             if (rc == EXL3_OK) rc = moe_init_device();
+            if (rc == EXL3_OK) rc = attention_init_device();
             if (rc == EXL3_OK) rc = gemm_tc_init_device();
             if (rc != EXL3_OK) d.ready = false;
         }
@@ -579,7 +580,8 @@ static int attention_common(const void* qkv, int dtype, int rows, int q_heads, i
     if (rows < 0 || q_heads < 1 || kv_heads < 1 || head_dim != 128 || t_max < 1 || q_heads % kv_heads) return EXL3_ERR_BAD_SHAPE;
     if (!aligned(qkv, 8) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(position, 4) || (out && !aligned(out, 8)) || (!out && !suh_next))
         return EXL3_ERR_BAD_POINTER;
-    if (!aligned(scratch, 16) || scratch_bytes < attention_scratch_bytes(rows, q_heads, kv_heads, t_max)) return EXL3_ERR_WORKSPACE;
+    if (!aligned(scratch, 256) || scratch_bytes < attention_scratch_bytes(rows, q_heads, kv_heads, t_max)) return EXL3_ERR_WORKSPACE;
+    if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
     return launch_decode_attention(qkv, dtype == EXL3_BF16, rows, q_heads, kv_heads, k_cache, v_cache, t_max, position, scale, cos_table,
                                    sin_table, reinterpret_cast<float*>(scratch), out, reinterpret_cast<const __half*>(suh_next), xf,
                                    suh_next ? fragment_mode(codebook) : 0, (cudaStream_t)stream);

@@ -120,6 +120,7 @@ int launch_residual_ssq(const void* x, const void* res_in, int bf16, int rows, i
 int launch_silu_mul_rotate(const void* gu, int bf16, const __half* suh, int rows, int inter, void* act, uint32_t* xf, int mode,
                            cudaStream_t st);
 size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max);
+int attention_init_device();
 int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads, const float* cos_t, const float* sin_t, void* k_cache,
                        void* v_cache, int t_max, const int* pos, cudaStream_t st);
 int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, void* k_cache, void* v_cache, int t_max,

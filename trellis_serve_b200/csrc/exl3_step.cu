@@ -459,109 +459,129 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
                                                                            void* k_cache, void* v_cache, int t_max,
                                                                            const int* __restrict__ pos_ptr, float scale,
                                                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                                                           float* part, int* counters, int rows, void* __restrict__ y_out,
+                                                                           float* part, int* counters, int* err, int rows, void* __restrict__ y_out,
                                                                            const __half* __restrict__ suh, uint32_t* __restrict__ xf, int mode)
 {
-    __shared__ float qs[G][ATT_D];
+    // Dynamic shared memory: the CTA's chunk of keys and of values (ATT_CHUNK rows of 256 bytes each), brought in by two bulk
+    // copies.  The loops over them are short and rolled: a kernel whose every instruction runs once is bound by instruction
+    // fetch, not by arithmetic.
+    extern __shared__ __align__(128) unsigned char att_smem[];
+    unsigned char* ks = att_smem;
+    unsigned char* vs = att_smem + ATT_CHUNK * ATT_D * 2;
+    // queries, chunk-major: qs[g][half][chunk of 8 columns][4] so that lanes reading different chunks hit different banks
+    __shared__ __align__(16) float qs[G][2][16][4];
     __shared__ __align__(16) float red[ATT_WARPS][G][ATT_PART];
+    __shared__ __align__(8) uint64_t bar;
     ATT_STAMP(0);
     ptx::grid_launch_dependents();
-    // Nothing to do until the kernel ahead has finished: walk through the merge code once without storing anything, so that
-    // the CTA that ends up merging runs it from the instruction cache (it reads last step's partials; they are only looked at).
-    attention_merge_cta<G>(part, red, blockIdx.z, blockIdx.y, kv_heads, q_heads, gridDim.x, rows, y_out, bf16 != 0, suh, xf, mode, true);
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = *pos_ptr;
     const int T = pos + 1;                                        // valid cache positions
     const int heads = q_heads + 2 * kv_heads;
     const bool b = bf16 != 0;
-    // Cache rows below `pos` were written by earlier steps: like weights they are constants of this launch and are requested
-    // before the wait for the kernel ahead and all at once -- the key row of the lane's position whole and all of the warp's
-    // 32 value rows -- so their trip from memory overlaps that kernel's tail; row `pos` itself comes from the kernel ahead or
-    // from this kernel's own append and is fetched after the wait.
-    const int t0 = split * ATT_CHUNK + warp * 32;
+    const int chunk0 = split * ATT_CHUNK;
+    const int t0 = chunk0 + warp * 32;
     const int t = t0 + lane;
     const long long rowbase = (((long long)row * kv_heads + kvh) * t_max) * ATT_D;
-    const uint4* kr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(k_cache) + (rowbase + (long long)t * ATT_D) * 2);
-    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(v_cache) + (rowbase + (long long)t0 * ATT_D + 4 * lane) * 2;
-    uint4 kw[16];
-    uint2 vw[32];
-    if (t < pos) {
-#pragma unroll
-        for (int j = 0; j < 16; j++) kw[j] = kr[j];
+    // Cache rows below `pos` were written by earlier steps: like weights they are constants of this launch and are requested
+    // before the wait for the kernel ahead, so their trip from memory overlaps that kernel's tail; row `pos` itself comes from
+    // the kernel ahead or from this kernel's own append and is put in place after the wait.
+    int old_rows = pos - chunk0;
+    old_rows = old_rows < 0 ? 0 : (old_rows > ATT_CHUNK ? ATT_CHUNK : old_rows);
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::mbar_fence_init();
+        if (old_rows > 0) {
+            const uint32_t bytes = (uint32_t)old_rows * ATT_D * 2;
+            ptx::mbar_arrive_expect_tx(&bar, 2 * bytes);
+            ptx::bulk_g2s(ks, reinterpret_cast<const unsigned char*>(k_cache) + (rowbase + (long long)chunk0 * ATT_D) * 2, bytes, &bar);
+            ptx::bulk_g2s(vs, reinterpret_cast<const unsigned char*>(v_cache) + (rowbase + (long long)chunk0 * ATT_D) * 2, bytes, &bar);
+        }
     }
-#pragma unroll
-    for (int u = 0; u < 32; u++) vw[u] = (t0 + u < pos) ? *reinterpret_cast<const uint2*>(vbase + (long long)u * ATT_D * 2) : make_uint2(0u, 0u);
+    // Nothing else to do until the kernel ahead has finished: walk through the merge code once without storing anything, so
+    // that the CTA that ends up merging runs it from the instruction cache (it looks at last step's partials).
+    attention_merge_cta<G>(part, red, row, kvh, kv_heads, q_heads, gridDim.x, rows, y_out, b, suh, xf, mode, true);
     ptx::grid_dependency_wait();
     ATT_STAMP(1);
-    const int splits = gridDim.x;
-    float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
-    __shared__ float wgt[G][ATT_WARPS];
-    __shared__ int last_s;
-    if (cos_t) {
-        for (int e = threadIdx.x; e < G * (ATT_D / 2); e += ATT_WARPS * 32) {
-            const int g = e / (ATT_D / 2), i = e % (ATT_D / 2);
-            const long long at = ((long long)row * heads + kvh * G + g) * ATT_D;
-            const float x1 = to_f32(qkv, at + i, b), x2 = to_f32(qkv, at + i + 64, b);
+    // queries (rotated here when the tables are given), scaled
+    for (int e = threadIdx.x; e < G * (ATT_D / 2); e += ATT_WARPS * 32) {
+        const int g = e / (ATT_D / 2), i = e % (ATT_D / 2);
+        const long long at = ((long long)row * heads + kvh * G + g) * ATT_D;
+        const float x1 = to_f32(qkv, at + i, b), x2 = to_f32(qkv, at + i + 64, b);
+        float y1 = x1, y2 = x2;
+        if (cos_t) {
             const float c = cos_t[(long long)pos * 64 + i], sn = sin_t[(long long)pos * 64 + i];
-            qs[g][i] = round_act(x1 * c - x2 * sn, b) * scale;
-            qs[g][i + 64] = round_act(x2 * c + x1 * sn, b) * scale;
+            y1 = round_act(x1 * c - x2 * sn, b);
+            y2 = round_act(x2 * c + x1 * sn, b);
         }
-        if (split == pos / ATT_CHUNK && warp == (pos % ATT_CHUNK) / 32) {
+        qs[g][(i >> 2) & 1][i >> 3][i & 3] = y1 * scale;
+        qs[g][((i + 64) >> 2) & 1][(i + 64) >> 3][i & 3] = y2 * scale;
+    }
+    // the new row: rotated key and value into the cache (with the tables) and, either way, into this CTA's chunk
+    if (pos >= t0 && pos < t0 + 32) {                             // warp-uniform: the warp that owns position `pos`
+        const long long cat = rowbase + (long long)pos * ATT_D;
+        const int r = pos - chunk0;
+        if (cos_t) {
             const long long kat = ((long long)row * heads + q_heads + kvh) * ATT_D, vat = kat + (long long)kv_heads * ATT_D;
-            const long long cat = (((long long)row * kv_heads + kvh) * t_max + pos) * ATT_D;
             for (int i = lane; i < 64; i += 32) {
                 const float x1 = to_f32(qkv, kat + i, b), x2 = to_f32(qkv, kat + i + 64, b);
                 const float c = cos_t[(long long)pos * 64 + i], sn = sin_t[(long long)pos * 64 + i];
                 const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+                uint16_t h1, h2;
                 if (b) {
-                    reinterpret_cast<__nv_bfloat16*>(k_cache)[cat + i] = __float2bfloat16_rn(y1);
-                    reinterpret_cast<__nv_bfloat16*>(k_cache)[cat + i + 64] = __float2bfloat16_rn(y2);
+                    h1 = __bfloat16_as_ushort(__float2bfloat16_rn(y1));
+                    h2 = __bfloat16_as_ushort(__float2bfloat16_rn(y2));
                 } else {
-                    reinterpret_cast<__half*>(k_cache)[cat + i] = __float2half_rn(y1);
-                    reinterpret_cast<__half*>(k_cache)[cat + i + 64] = __float2half_rn(y2);
+                    h1 = __half_as_ushort(__float2half_rn(y1));
+                    h2 = __half_as_ushort(__float2half_rn(y2));
                 }
+                reinterpret_cast<uint16_t*>(k_cache)[cat + i] = h1;
+                reinterpret_cast<uint16_t*>(k_cache)[cat + i + 64] = h2;
+                reinterpret_cast<uint16_t*>(ks)[r * ATT_D + i] = h1;
+                reinterpret_cast<uint16_t*>(ks)[r * ATT_D + i + 64] = h2;
             }
-            reinterpret_cast<uint2*>(reinterpret_cast<unsigned char*>(v_cache) + cat * 2)[lane] =
-                reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(qkv) + vat * 2)[lane];
-            __syncwarp();                                         // the warp's own stores are visible to its loads below
+            const uint2 vv = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(qkv) + vat * 2)[lane];
+            reinterpret_cast<uint2*>(reinterpret_cast<unsigned char*>(v_cache) + cat * 2)[lane] = vv;
+            reinterpret_cast<uint2*>(vs + (size_t)r * ATT_D * 2)[lane] = vv;
+        } else {
+            reinterpret_cast<uint2*>(ks + (size_t)r * ATT_D * 2)[lane] = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(k_cache) + cat * 2)[lane];
+            reinterpret_cast<uint2*>(vs + (size_t)r * ATT_D * 2)[lane] = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(v_cache) + cat * 2)[lane];
         }
-    } else {
-        for (int e = threadIdx.x; e < G * ATT_D; e += ATT_WARPS * 32)
-            qs[e / ATT_D][e % ATT_D] = to_f32(qkv, ((long long)row * heads + kvh * G + e / ATT_D) * ATT_D + e % ATT_D, b) * scale;
     }
     __syncthreads();
-    if (t == pos) {
-#pragma unroll
-        for (int j = 0; j < 16; j++) kw[j] = kr[j];
-    }
-    if (pos >= t0 && pos < t0 + 32) {                             // warp-uniform
-#pragma unroll
-        for (int u = 0; u < 32; u++)
-            if (t0 + u == pos) vw[u] = *reinterpret_cast<const uint2*>(vbase + (long long)u * ATT_D * 2);
-    }
+    if (old_rows > 0 && !ptx::mbar_wait(&bar, 0) && lane == 0) atomicExch(err, 1);
+    const int splits = gridDim.x;
+    float* out = part + (((long long)row * kv_heads + kvh) * splits + split) * (G * ATT_PART);
+    // scores: lane = position; its key row in 16 chunks of 8 columns, taken in an order rotated by the lane number so that
+    // the lanes of a quarter warp read different banks (rows are 256 bytes apart); the query chunk follows the same order
     float sc[G];
 #pragma unroll
     for (int g = 0; g < G; g++) sc[g] = 0.f;
     if (t < T) {
-#pragma unroll
+        const uint32_t krow = ptx::smem_addr(ks) + (uint32_t)(warp * 32 + lane) * (ATT_D * 2);
+#pragma unroll 2
         for (int j = 0; j < 16; j++) {
-            const uint4 w = kw[j];
+            const int c = (j + lane) & 15;
+            const uint4 w = ptx::lds128(krow + c * 16);
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            float kf[8];
 #pragma unroll
             for (int h2 = 0; h2 < 4; h2++) {
-                float k0, k1;
                 if (b) {
                     const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&ww[h2]);
-                    k0 = __low2float(v);
-                    k1 = __high2float(v);
+                    kf[2 * h2] = __low2float(v);
+                    kf[2 * h2 + 1] = __high2float(v);
                 } else {
                     const __half2 v = *reinterpret_cast<const __half2*>(&ww[h2]);
-                    k0 = __low2float(v);
-                    k1 = __high2float(v);
+                    kf[2 * h2] = __low2float(v);
+                    kf[2 * h2 + 1] = __high2float(v);
                 }
+            }
 #pragma unroll
-                for (int g = 0; g < G; g++) sc[g] += k0 * qs[g][j * 8 + h2 * 2] + k1 * qs[g][j * 8 + h2 * 2 + 1];
+            for (int g = 0; g < G; g++) {
+                const float4 qa = *reinterpret_cast<const float4*>(&qs[g][0][c][0]), qb = *reinterpret_cast<const float4*>(&qs[g][1][c][0]);
+                sc[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
             }
         }
     }
@@ -579,20 +599,23 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
         l[g] = s;
     }
+    // values: the warp walks its positions, each lane four of the 128 columns
     float acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; g++)
 #pragma unroll
         for (int e = 0; e < 4; e++) acc[g][e] = 0.f;
-    const int n = T - t0 < 32 ? T - t0 : 32;                      // warp-uniform; rows past the end hold zeros and weigh zero
-#pragma unroll
-    for (int u = 0; u < 32; u++) {
+    const int n = T - t0 < 32 ? (T - t0 < 0 ? 0 : T - t0) : 32;   // warp-uniform: positions of this warp that exist
+    const uint32_t vrow = ptx::smem_addr(vs) + (uint32_t)(warp * 32) * (ATT_D * 2) + lane * 8;
+#pragma unroll 4
+    for (int u = 0; u < n; u++) {
+        const uint2 w = ptx::lds64(vrow + u * (ATT_D * 2));
         float v[4];
         if (b) {
-            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&vw[u].x), c = *reinterpret_cast<const __nv_bfloat162*>(&vw[u].y);
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w.x), c = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
             v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
         } else {
-            const __half2 a = *reinterpret_cast<const __half2*>(&vw[u].x), c = *reinterpret_cast<const __half2*>(&vw[u].y);
+            const __half2 a = *reinterpret_cast<const __half2*>(&w.x), c = *reinterpret_cast<const __half2*>(&w.y);
             v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(c); v[3] = __high2float(c);
         }
 #pragma unroll
@@ -603,6 +626,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
         }
     }
     ATT_STAMP(3);
+    __shared__ float wgt[G][ATT_WARPS];
+    __shared__ int last_s;
     // The four warps' partial results are merged inside the CTA (fixed warp order), so one partial per split goes out.
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -663,14 +688,28 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) decode_attention_kernel(const 
     ATT_STAMP(7);
 }
 
-// Scratch: one arrival counter per (row, KV head) -- zero before the first launch, left zero by every launch -- then the partials.
+// Scratch: an error word (set when the bounded wait for the cache copies gives up; exl3_device_error reads it), one arrival
+// counter per (row, KV head) -- zero before the first launch, left zero by every launch -- then the partials.
+constexpr size_t ATT_SCRATCH_HEADER = 256;
+constexpr size_t ATT_DYN_SMEM = 2 * (size_t)ATT_CHUNK * ATT_D * 2;
 static size_t attention_counter_bytes(int rows, int kv_heads) { return ((size_t)rows * kv_heads * sizeof(int) + 255) & ~(size_t)255; }
 
 size_t attention_scratch_bytes(int rows, int q_heads, int kv_heads, int t_max)
 {
     const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
     const int G = q_heads / (kv_heads > 0 ? kv_heads : 1);
-    return attention_counter_bytes(rows, kv_heads) + (size_t)rows * kv_heads * splits * G * ATT_PART * sizeof(float);
+    return ATT_SCRATCH_HEADER + attention_counter_bytes(rows, kv_heads) + (size_t)rows * kv_heads * splits * G * ATT_PART * sizeof(float);
+}
+
+// The kernels keep their cache chunk in dynamic shared memory beyond the default limit: opted in once per device.
+int attention_init_device()
+{
+    int rc = cuda_status(cudaFuncSetAttribute(decode_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_DYN_SMEM));
+    if (rc == EXL3_OK) rc = cuda_status(cudaFuncSetAttribute(decode_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_DYN_SMEM));
+    if (rc == EXL3_OK) rc = cuda_status(cudaFuncSetAttribute(decode_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_DYN_SMEM));
+    if (rc == EXL3_OK) rc = cuda_status(cudaFuncSetAttribute(decode_attention_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_DYN_SMEM));
+    if (rc == EXL3_OK) rc = cuda_status(cudaFuncSetAttribute(decode_attention_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_DYN_SMEM));
+    return rc;
 }
 
 int launch_rope_append(void* qkv, int bf16, int rows, int q_heads, int kv_heads, const float* cos_t, const float* sin_t, void* k_cache,
@@ -688,10 +727,12 @@ static int launch_attention_g(const void* qkv, int bf16, int rows, int q_heads, 
                               uint32_t* xf, int mode, cudaStream_t st)
 {
     const int splits = (t_max + ATT_CHUNK - 1) / ATT_CHUNK;
-    int* counters = reinterpret_cast<int*>(part);
-    float* partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(part) + attention_counter_bytes(rows, kv_heads));
-    return launch_chained(decode_attention_kernel<G>, dim3(splits, kv_heads, rows), dim3(ATT_WARPS * 32), 0, st, qkv, bf16, q_heads, kv_heads,
-                          k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, partials, counters, rows, out, suh, xf, mode);
+    unsigned char* base = reinterpret_cast<unsigned char*>(part);
+    int* err = reinterpret_cast<int*>(base);
+    int* counters = reinterpret_cast<int*>(base + ATT_SCRATCH_HEADER);
+    float* partials = reinterpret_cast<float*>(base + ATT_SCRATCH_HEADER + attention_counter_bytes(rows, kv_heads));
+    return launch_chained(decode_attention_kernel<G>, dim3(splits, kv_heads, rows), dim3(ATT_WARPS * 32), ATT_DYN_SMEM, st, qkv, bf16, q_heads,
+                          kv_heads, k_cache, v_cache, t_max, pos, scale, cos_t, sin_t, partials, counters, err, rows, out, suh, xf, mode);
 }
 
 int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, int kv_heads, void* k_cache, void* v_cache, int t_max,
