@@ -78,7 +78,8 @@ exl3_status exl3_reconstruct_packed(const uint32_t *packed, int k, int n, int K,
 exl3_status exl3_had_in(const void *x, int x_dtype, const uint16_t *suh, int shards, int rows, int k, uint16_t *xh,
                         void *stream);
 /* out[r, j] = Had128(y[r, :])[j] * svh[j] for j < n, written with row stride out_stride (elements) so a fused
- * group can fill adjacent column spans.  y_dtype EXL3_F16 or EXL3_F32; out_dtype EXL3_F16 or EXL3_BF16.
+ * group can fill adjacent column spans.  y_dtype EXL3_F16 or EXL3_F32; out_dtype EXL3_F16 or EXL3_BF16.  y, out and svh are
+ * 16-byte aligned and out_stride is a multiple of 8 (the kernel moves 16 bytes at a time).
  * Replaces had_out_into_marlin (cuda/csrc/exl3_marlin.cu:292-306). */
 exl3_status exl3_had_out(const void *y, int y_dtype, const uint16_t *svh, int rows, int n, void *out, int64_t out_stride,
                          int out_dtype, void *stream);
@@ -318,8 +319,8 @@ exl3_status exl3_moe_combine(const uint16_t *yd, const float *topk_weights, cons
  * with the same grouped kernel and larger moe blocks (moe_block_size picks 8..64 rows from T * top_k / E,
  * cuda/src/sglang_exl3/kernels/marlin_moe.py:52-57; launch at cuda/csrc/exl3_marlin_moe.cu:376-408); here the routing is
  * aligned to blocks of exl3_moe_tc_block_rows() = 128 rows and up to two blocks of one expert (four when hidden or inter is
- * not a multiple of 256) share every decoded weight block in a grouped tcgen05 GEMM.  x and the sign vectors must be 8-byte
- * aligned.  One call runs one bitrate class from the routing to the per-slot outputs:
+ * not a multiple of 256) share every decoded weight block in a grouped tcgen05 GEMM.  x, yd and the sign vectors must be
+ * 16-byte aligned.  One call runs one bitrate class from the routing to the per-slot outputs:
  *   align (expert_map as in exl3_moe_align_mapped, or NULL with num_local == num_experts) -> gate|up -> SiLU(gate) * up
  *   -> down -> yd[slot, :] (fp16 [tokens * top_k, hidden]; slots of experts outside the class are not written).
  * exl3_moe_combine then closes the layer.  w13 / suh13 / svh13 / w2 / suh2 / svh2 are the resident expert stacks of

@@ -161,11 +161,11 @@ exl3_status exl3_had_in(const void* x, int x_dtype, const uint16_t* suh, int sha
 exl3_status exl3_had_out(const void* y, int y_dtype, const uint16_t* svh, int rows, int n, void* out, int64_t out_stride,
                          int out_dtype, void* stream)
 {
-    if (rows < 0 || n < 0 || (n % 128) || out_stride < n || (out_stride % 4)) return EXL3_ERR_BAD_SHAPE;
+    if (rows < 0 || n < 0 || (n % 128) || out_stride < n || (out_stride % 8)) return EXL3_ERR_BAD_SHAPE;
     if ((y_dtype != EXL3_F16 && y_dtype != EXL3_F32) || (out_dtype != EXL3_F16 && out_dtype != EXL3_BF16))
         return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (rows == 0 || n == 0) return EXL3_OK;
-    if (!aligned(y, 2) || !aligned(out, 8)) return EXL3_ERR_BAD_POINTER;
+    if (!aligned(y, 16) || !aligned(out, 16) || (svh && !aligned(svh, 16))) return EXL3_ERR_BAD_POINTER;
     return launch_had_out(y, y_dtype == EXL3_F32, reinterpret_cast<const __half*>(svh), rows, n, out, out_stride,
                           out_dtype == EXL3_BF16, (cudaStream_t)stream);
 }
@@ -629,7 +629,7 @@ exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, i
     if ((x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) || (y_dtype != EXL3_F16 && y_dtype != EXL3_BF16)) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (rows == 0 || k == 0 || n_total == 0) return EXL3_OK;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
-    if (!aligned(x, 2) || !aligned(packed, 16) || !aligned(suh_cat, 2) || !aligned(svh_cat, 8) || !aligned(y, 8)) return EXL3_ERR_BAD_POINTER;
+    if (!aligned(x, 16) || !aligned(packed, 16) || !aligned(suh_cat, 16) || !aligned(svh_cat, 16) || !aligned(y, 16)) return EXL3_ERR_BAD_POINTER;
     if (!aligned(workspace, 256) || workspace_bytes < exl3_gemm_tc_workspace_bytes(rows, k, n_total, n_shards)) return EXL3_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
@@ -822,8 +822,8 @@ exl3_status exl3_moe_tc_experts(const void* x, int x_dtype, int tokens, int top_
     if (x_dtype != EXL3_F16 && x_dtype != EXL3_BF16) return EXL3_ERR_UNSUPPORTED_DTYPE;
     if (tokens == 0) return EXL3_OK;
     if (!current_device_info()) return EXL3_ERR_NOT_INITIALISED;
-    if (!aligned(x, 8) || !aligned(topk_ids, 4) || !aligned(w13, 16) || !aligned(w2, 16) || !aligned(suh13, 8) || !aligned(svh13, 8) ||
-        !aligned(suh2, 8) || !aligned(svh2, 8) || !aligned(yd, 8))
+    if (!aligned(x, 16) || !aligned(topk_ids, 4) || !aligned(w13, 16) || !aligned(w2, 16) || !aligned(suh13, 16) || !aligned(svh13, 16) ||
+        !aligned(suh2, 16) || !aligned(svh2, 16) || !aligned(yd, 16))
         return EXL3_ERR_BAD_POINTER;
     const int slots = tokens * top_k;
     if (!aligned(workspace, 256) || workspace_bytes < moe_tc_workspace_bytes(slots, num_local, hidden, inter)) return EXL3_ERR_WORKSPACE;

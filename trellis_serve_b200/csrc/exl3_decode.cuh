@@ -306,6 +306,34 @@ __device__ __forceinline__ void fwht128(float& v0, float& v1, float& v2, float& 
     }
 }
 
+// The same transform with a row spread over FOUR lanes (lane l holds elements 32 * (l & 3) .. + 31 of row l >> 2, eight rows
+// per warp): five stages stay inside the lane and only two cross lanes, 64 shuffles for eight rows where the layout above
+// needs 160 -- the shuffle unit is what bounds the rotation kernels of the many-row paths.  Same stage order (strides 1, 2, ...,
+// 64) and the same sums and differences, so the results are the same bits.
+__device__ __forceinline__ void fwht128_quad(float (&v)[32], int lane)
+{
+#pragma unroll
+    for (int stride = 1; stride < 32; stride <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            if ((i & stride) == 0) {
+                const float lo = v[i], hi = v[i + stride];
+                v[i] = lo + hi;
+                v[i + stride] = lo - hi;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1) {
+        const bool upper = (lane & m) != 0;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            const float p = __shfl_xor_sync(0xFFFFFFFFu, v[i], m);
+            v[i] = upper ? p - v[i] : v[i] + p;
+        }
+    }
+}
+
 constexpr float HAD_SCALE = 0.08838834764831845f;   // 1 / sqrt(128)
 
 }  // namespace exl3

@@ -374,31 +374,62 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
     }
 }
 
-// Rotated activations in the A-operand layout of gemm_tc_kernel.  One warp per (shard, row, 128-block); rows beyond
-// `rows` up to the next multiple of 512 must have been zero-filled by the caller.
+// Rotated activations in the A-operand layout of gemm_tc_kernel.  One warp per (shard, group of 8 rows, 128-block), four lanes
+// per row with 32 columns each (fwht128_quad): a lane's 32 results are four whole 16-byte core-matrix rows, and the eight
+// lanes that share a column range fill a 128-byte core matrix.  Rows beyond `rows` inside the last group are written as
+// zeros; those up to the next multiple of 512 must have been zero-filled by the caller.
+constexpr int HAD_IN_TC_ROWS = 8;
 __global__ void had_in_tc_kernel(const void* __restrict__ x, int x_bf16, const __half* __restrict__ suh, int shards, int rows, int k,
                                  __half* __restrict__ xa, long long shard_stride)
 {
     const int lane = threadIdx.x & 31;
     const int kgs = k >> 7;
+    const int groups = (rows + HAD_IN_TC_ROWS - 1) / HAD_IN_TC_ROWS;
     const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (long long)shards * rows * kgs) return;
+    if (item >= (long long)shards * groups * kgs) return;
     const int kg = (int)(item % kgs);
-    const int row = (int)((item / kgs) % rows);
-    const int s = (int)(item / ((long long)kgs * rows));
-    float v[4];
+    const int row = (int)((item / kgs) % groups) * HAD_IN_TC_ROWS + (lane >> 2);
+    const int s = (int)(item / ((long long)kgs * groups));
+    const int col = kg * 128 + 32 * (lane & 3);
+    float v[32];
+    if (row < rows) {
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        const int col = kg * 128 + 4 * lane + e;
-        float xv = x_bf16 ? __half2float(__float2half_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[(long long)row * k + col])))
-                          : __half2float(reinterpret_cast<const __half*>(x)[(long long)row * k + col]);
-        v[e] = xv * __half2float(suh[(long long)s * k + col]);
+        for (int i = 0; i < 4; i++) {
+            const uint4 raw = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (long long)row * k + col)[i];
+            const uint4 sraw = reinterpret_cast<const uint4*>(suh + (long long)s * k + col)[i];
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w}, sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float x0, x1;
+                if (x_bf16) {
+                    const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+                    x0 = __half2float(__float2half_rn(__low2float(bb)));
+                    x1 = __half2float(__float2half_rn(__high2float(bb)));
+                } else {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                    x0 = __low2float(h);
+                    x1 = __high2float(h);
+                }
+                const __half2 sh = *reinterpret_cast<const __half2*>(&sw[j]);
+                v[8 * i + 2 * j] = x0 * __low2float(sh);
+                v[8 * i + 2 * j + 1] = x1 * __high2float(sh);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = 0.f;
     }
-    fwht128(v[0], v[1], v[2], v[3], lane);
-    __half h[4];
+    fwht128_quad(v, lane);
 #pragma unroll
-    for (int e = 0; e < 4; e++) h[e] = __float2half_rn(v[e] * HAD_SCALE);
-    *reinterpret_cast<uint2*>(xa + s * shard_stride + tc_a_offset(row, kg * 128 + 4 * lane, kgs * 2)) = *reinterpret_cast<uint2*>(h);
+    for (int i = 0; i < 4; i++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 h = __floats2half2_rn(v[8 * i + 2 * j] * HAD_SCALE, v[8 * i + 2 * j + 1] * HAD_SCALE);
+            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(xa + s * shard_stride + tc_a_offset(row, col + 8 * i, kgs * 2)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
 }
 
 template <int K, int FAM, int MT, bool WIDE, bool SPLIT>
@@ -525,7 +556,7 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
     // Rows beyond `rows` inside the last 512-row super tile must read as zeros; with whole super tiles there are none.
     if (rows % TC_ROWS != 0)
         if (int rc = cuda_status(cudaMemsetAsync(xa, 0, gemm_tc_activation_bytes(rows, k, n_shards), st))) return rc;
-    const long long items = (long long)n_shards * rows * (k / 128);
+    const long long items = (long long)n_shards * ((rows + HAD_IN_TC_ROWS - 1) / HAD_IN_TC_ROWS) * (k / 128);
     had_in_tc_kernel<<<(unsigned)((items + 7) / 8), 256, 0, st>>>(x, x_bf16, suh_cat, n_shards, rows, k, xa, l.xa_shard_stride);
     if (int rc = cuda_status(cudaGetLastError())) return rc;
     // Wide tiles (256 x 256) need column blocks that pair up inside every shard.  They halve the rows that share a decoded

@@ -258,29 +258,72 @@ __device__ __forceinline__ void store_out4(void* out, long long idx, const float
     }
 }
 
-// out[row, col0 + j] = Had128(y[row, :])[j] * svh[j].  y is fp16 (IN_F32 = false) or fp32 [rows, n].
+// out[row, col0 + j] = Had128(y[row, :])[j] * svh[j].  y is fp16 (IN_F32 = false) or fp32 [rows, n].  One warp per (group of
+// HAD_OUT_ROWS rows, 128 columns), four lanes per row with 32 columns each (fwht128_quad).
+constexpr int HAD_OUT_ROWS = 8;
 template <bool IN_F32>
 __global__ void had_out_kernel(const void* __restrict__ y, const __half* __restrict__ svh, int rows, int n, void* __restrict__ out,
                                long long out_stride, int out_bf16)
 {
     const int lane = threadIdx.x & 31;
     const int nbs = n >> 7;
+    const int groups = (rows + HAD_OUT_ROWS - 1) / HAD_OUT_ROWS;
     long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (long long)rows * nbs) return;
+    if (item >= (long long)groups * nbs) return;
     const int nb = (int)(item % nbs);
-    const int row = (int)(item / nbs);
-    float v[4];
-    const long long base = (long long)row * n + nb * 128 + 4 * lane;
+    const int row = (int)(item / nbs) * HAD_OUT_ROWS + (lane >> 2);
+    const int col = nb * 128 + 32 * (lane & 3);
+    const bool live = row < rows;
+    float v[32];
+    if (live) {
+        const long long base = (long long)row * n + col;
+        if (IN_F32) {
 #pragma unroll
-    for (int e = 0; e < 4; e++)
-        v[e] = IN_F32 ? reinterpret_cast<const float*>(y)[base + e] : __half2float(reinterpret_cast<const __half*>(y)[base + e]);
-    fwht128(v[0], v[1], v[2], v[3], lane);
+            for (int i = 0; i < 8; i++) {
+                const float4 f = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + base)[i];
+                v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+            }
+        } else {
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        float sv = svh ? __half2float(svh[nb * 128 + 4 * lane + e]) : 1.0f;
-        v[e] = v[e] * (HAD_SCALE * sv);          // the same order as the epilogues fused into the GEMV kernels
+            for (int i = 0; i < 4; i++) {
+                const uint4 raw = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(y) + base)[i];
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                    v[8 * i + 2 * j] = __low2float(h);
+                    v[8 * i + 2 * j + 1] = __high2float(h);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = 0.f;
     }
-    store_out4(out, (long long)row * out_stride + nb * 128 + 4 * lane, v, out_bf16 != 0);
+    fwht128_quad(v, lane);                        // every lane takes part in the shuffles
+    if (!live) return;
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint4 sraw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);       // ones
+        if (svh) sraw = reinterpret_cast<const uint4*>(svh + col)[i];
+        const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 sh = *reinterpret_cast<const __half2*>(&sw[j]);
+            // the order of the fused epilogues: v * (scale * sign), rounded to fp16 first; bf16 is that value converted
+            const __half2 h = __floats2half2_rn(v[8 * i + 2 * j] * (HAD_SCALE * __low2float(sh)), v[8 * i + 2 * j + 1] * (HAD_SCALE * __high2float(sh)));
+            if (out_bf16) {
+                const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(h), __high2float(h));
+                packed[4 * i + j] = *reinterpret_cast<const uint32_t*>(&bb);
+            } else {
+                packed[4 * i + j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (long long)row * out_stride + col);
+#pragma unroll
+    for (int i = 0; i < 4; i++) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
 }
 
 // out[row, :] = Had128(fp16(sum over parts of part[s][row, :])) * svh: the output rotation of the many-row path when the
@@ -397,7 +440,7 @@ int launch_to_fragments(const __half* xh, int shards, int rows, int k, uint32_t*
 int launch_had_out(const void* y, int y_f32, const __half* svh, int rows, int n, void* out, long long out_stride, int out_bf16,
                    cudaStream_t st)
 {
-    long long items = (long long)rows * (n / 128);
+    long long items = (long long)((rows + HAD_OUT_ROWS - 1) / HAD_OUT_ROWS) * (n / 128);
     if (items == 0) return EXL3_OK;
     if (y_f32) had_out_kernel<true><<<blocks_for(items, 8), 256, 0, st>>>(y, svh, rows, n, out, out_stride, out_bf16);
     else had_out_kernel<false><<<blocks_for(items, 8), 256, 0, st>>>(y, svh, rows, n, out, out_stride, out_bf16);

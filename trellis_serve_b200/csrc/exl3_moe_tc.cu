@@ -64,51 +64,45 @@ __global__ void moe_tc_items_kernel(const int* __restrict__ expert_ids, const in
     if (threadIdx.x == 0) *n_items = carry_sh;
 }
 
-constexpr int MOE_TC_GROUP = 8;           // positions per warp: one row group of the A layout, eight independent rows in flight
+constexpr int MOE_TC_GROUP = 8;           // positions per warp: one row group of the A layout, four lanes per position (fwht128_quad)
 
-__device__ __forceinline__ void store_a4(__half* xa, long long off, const float (&v)[4])
+// 32 consecutive halves (64 bytes, 16-byte aligned) as floats, and back.
+__device__ __forceinline__ void load_h32(const __half* __restrict__ src, float (&v)[32])
 {
-    __half h[4];
 #pragma unroll
-    for (int e = 0; e < 4; e++) h[e] = __float2half_rn(v[e]);
-    *reinterpret_cast<uint2*>(xa + off) = *reinterpret_cast<uint2*>(h);
-}
-
-// Rows r and r + 1 of a row group, four columns per lane each, to the A layout as whole 16-byte core-matrix rows: the even lane
-// of a pair takes the eight columns of row r, the odd lane those of row r + 1 (two shuffles), so a warp store covers full
-// 32-byte sectors instead of halves.
-__device__ __forceinline__ void store_a_pair(__half* xa, int p_even, int col, int KB, int lane, const float (&va)[4], const float (&vb)[4])
-{
-    __half ha[4], hb[4];
+    for (int i = 0; i < 4; i++) {
+        const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        ha[e] = __float2half_rn(va[e]);
-        hb[e] = __float2half_rn(vb[e]);
+        for (int j = 0; j < 4; j++) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+            v[8 * i + 2 * j] = __low2float(h);
+            v[8 * i + 2 * j + 1] = __high2float(h);
+        }
     }
-    const uint2 a = *reinterpret_cast<uint2*>(ha), b = *reinterpret_cast<uint2*>(hb);
-    const bool odd = lane & 1;
-    const uint2 send = odd ? a : b;
-    uint2 recv;
-    recv.x = __shfl_xor_sync(0xFFFFFFFFu, send.x, 1);
-    recv.y = __shfl_xor_sync(0xFFFFFFFFu, send.y, 1);
-    const uint4 out = odd ? make_uint4(recv.x, recv.y, b.x, b.y) : make_uint4(a.x, a.y, recv.x, recv.y);
-    *reinterpret_cast<uint4*>(xa + tc_a_offset(p_even + (odd ? 1 : 0), col & ~7, KB)) = out;
 }
 
-__device__ __forceinline__ void load_h4(const __half* __restrict__ src, float (&v)[4])
+__device__ __forceinline__ uint4 pack_h8(const float* v)
 {
-    const uint2 raw = *reinterpret_cast<const uint2*>(src);
-    const __half2 h01 = *reinterpret_cast<const __half2*>(&raw.x), h23 = *reinterpret_cast<const __half2*>(&raw.y);
-    v[0] = __low2float(h01);
-    v[1] = __high2float(h01);
-    v[2] = __low2float(h23);
-    v[3] = __high2float(h23);
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// A lane's 32 results as four whole 16-byte core-matrix rows of the A layout.
+__device__ __forceinline__ void store_a32(__half* xa, int p, int col, int KB, const float (&v)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(xa + tc_a_offset(p, col + 8 * i, KB)) = pack_h8(&v[8 * i]);
 }
 
 // xa[shard][position p] = Had128(fp16(x[token(p)]) * suh[expert(p), shard]) in the A-operand layout; zero rows for padding.
-// One warp per (shard, group of 8 positions, 128-block): the eight rows are independent, so their loads and butterflies
-// overlap, and the warp fills whole 128-byte core matrices.  Positions at or beyond num_post are left untouched (no work
-// item reads them).
+// One warp per (shard, group of 8 positions, 128-block).  Positions at or beyond num_post are left untouched (no work item
+// reads them).
 __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, const __half* __restrict__ suh, int shards, int hidden,
                                      int top_k, int numel, int cap, const int* __restrict__ sorted_ids, const int* __restrict__ expert_ids,
                                      const int* __restrict__ num_post, __half* __restrict__ xa, long long shard_stride)
@@ -123,49 +117,50 @@ __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, con
     const int p0 = (int)((item / kgs) % groups) * MOE_TC_GROUP;
     const int s = (int)(item / ((long long)kgs * groups));
     if (p0 >= *num_post) return;
+    const int p = p0 + (lane >> 2);
     const int ex = expert_ids[p0 / MOE_TC_BLOCK_ROWS];
-    const int col = kg * 128 + 4 * lane;
-    float sg[4];
-    load_h4(suh + ((long long)ex * shards + s) * hidden + col, sg);
-    float v[MOE_TC_GROUP][4];
+    const int col = kg * 128 + 32 * (lane & 3);
+    const int slot = sorted_ids[p];
+    float v[32];
+    if (slot >= 0 && slot < numel) {
+        float sg[32];
+        load_h32(suh + ((long long)ex * shards + s) * hidden + col, sg);
+        const long long at = (long long)(slot / top_k) * hidden + col;
+        if (x_bf16) {
 #pragma unroll
-    for (int r = 0; r < MOE_TC_GROUP; r++) {
-        const int slot = sorted_ids[p0 + r];
-        if (slot >= 0 && slot < numel) {
-            const long long at = (long long)(slot / top_k) * hidden + col;
-            if (x_bf16) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(x) + at);
-                const __nv_bfloat162 b01 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b23 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                v[r][0] = __half2float(__float2half_rn(__low2float(b01)));
-                v[r][1] = __half2float(__float2half_rn(__high2float(b01)));
-                v[r][2] = __half2float(__float2half_rn(__low2float(b23)));
-                v[r][3] = __half2float(__float2half_rn(__high2float(b23)));
-            } else {
-                load_h4(reinterpret_cast<const __half*>(x) + at, v[r]);
+            for (int i = 0; i < 4; i++) {
+                const uint4 raw = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + at)[i];
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+                    v[8 * i + 2 * j] = __half2float(__float2half_rn(__low2float(bb)));
+                    v[8 * i + 2 * j + 1] = __half2float(__float2half_rn(__high2float(bb)));
+                }
             }
-#pragma unroll
-            for (int e = 0; e < 4; e++) v[r][e] *= sg[e];
         } else {
-#pragma unroll
-            for (int e = 0; e < 4; e++) v[r][e] = 0.f;
+            load_h32(reinterpret_cast<const __half*>(x) + at, v);
         }
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] *= sg[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = 0.f;
     }
+    fwht128_quad(v, lane);
 #pragma unroll
-    for (int r = 0; r < MOE_TC_GROUP; r++) {
-        fwht128(v[r][0], v[r][1], v[r][2], v[r][3], lane);
-#pragma unroll
-        for (int e = 0; e < 4; e++) v[r][e] *= HAD_SCALE;
-    }
-#pragma unroll
-    for (int r = 0; r < MOE_TC_GROUP; r += 2) store_a_pair(xa + s * shard_stride, p0 + r, col, kgs * 2, lane, v[r], v[r + 1]);
+    for (int i = 0; i < 32; i++) v[i] *= HAD_SCALE;
+    store_a32(xa + s * shard_stride, p, col, kgs * 2, v);
 }
 
-// 128 columns of a rotated-basis row back in the true basis: Had128(y) * svh, rounded to fp16 like the GEMV's output.
-__device__ __forceinline__ void unrotate4(float (&v)[4], const float (&sv)[4], int lane)
+// 32 columns of a rotated-basis row back in the true basis: Had128(y) * svh, rounded to fp16 like the GEMV's output.
+__device__ __forceinline__ void unrotate32(float (&v)[32], const __half* __restrict__ svh, int lane)
 {
-    fwht128(v[0], v[1], v[2], v[3], lane);
+    float sv[32];
+    load_h32(svh, sv);
+    fwht128_quad(v, lane);
 #pragma unroll
-    for (int e = 0; e < 4; e++) v[e] = __half2float(__float2half_rn(v[e] * (HAD_SCALE * sv[e])));
+    for (int i = 0; i < 32; i++) v[i] = __half2float(__float2half_rn(v[i] * (HAD_SCALE * sv[i])));
 }
 
 // xa2[position p] = Had128( fp16( silu(gate) * up ) * suh2[expert] ) with gate | up = Had128(gu_rot[p]) * svh13[expert].
@@ -183,39 +178,27 @@ __global__ void moe_tc_mid_kernel(const __half* __restrict__ gu_rot, const __hal
     const int kg = (int)(item % kgs);
     const int p0 = (int)(item / kgs) * MOE_TC_GROUP;
     if (p0 >= *num_post) return;
+    const int p = p0 + (lane >> 2);
     const int ex = expert_ids[p0 / MOE_TC_BLOCK_ROWS];
-    const int col = kg * 128 + 4 * lane;
-    float sg[4], su[4], s2[4];
-    load_h4(svh13 + (long long)ex * 2 * inter + col, sg);
-    load_h4(svh13 + (long long)ex * 2 * inter + inter + col, su);
-    load_h4(suh2 + (long long)ex * inter + col, s2);
-    // two rows at a time: enough loads in flight without holding all sixteen gate / up vectors in registers
-#pragma unroll 1
-    for (int r = 0; r < MOE_TC_GROUP; r += 2) {
-        float g[2][4], u[2][4], v[2][4];
-        bool valid[2];
+    const int col = kg * 128 + 32 * (lane & 3);
+    const int slot = sorted_ids[p];
+    const bool valid = slot >= 0 && slot < numel;
+    float g[32], u[32];
+    load_h32(gu_rot + (long long)p * 2 * inter + col, g);
+    load_h32(gu_rot + (long long)p * 2 * inter + inter + col, u);
+    unrotate32(g, svh13 + (long long)ex * 2 * inter + col, lane);
+    unrotate32(u, svh13 + (long long)ex * 2 * inter + inter + col, lane);
+    float s2[32];
+    load_h32(suh2 + (long long)ex * inter + col, s2);
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int slot = sorted_ids[p0 + r + i];
-            valid[i] = slot >= 0 && slot < numel;
-            load_h4(gu_rot + (long long)(p0 + r + i) * 2 * inter + col, g[i]);
-            load_h4(gu_rot + (long long)(p0 + r + i) * 2 * inter + inter + col, u[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            unrotate4(g[i], sg, lane);
-            unrotate4(u[i], su, lane);
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float act = __half2float(__float2half_rn(g[i][e] / (1.0f + __expf(-g[i][e])) * u[i][e]));
-                v[i][e] = valid[i] ? act * s2[e] : 0.f;
-            }
-            fwht128(v[i][0], v[i][1], v[i][2], v[i][3], lane);
-#pragma unroll
-            for (int e = 0; e < 4; e++) v[i][e] *= HAD_SCALE;
-        }
-        store_a_pair(xa2, p0 + r, col, kgs * 2, lane, v[0], v[1]);
+    for (int i = 0; i < 32; i++) {
+        const float act = __half2float(__float2half_rn(g[i] / (1.0f + __expf(-g[i])) * u[i]));
+        g[i] = valid ? act * s2[i] : 0.f;
     }
+    fwht128_quad(g, lane);
+#pragma unroll
+    for (int i = 0; i < 32; i++) g[i] *= HAD_SCALE;
+    store_a32(xa2, p, col, kgs * 2, g);
 }
 
 // yd[slot(p), :] = fp16( Had128(yd_rot[p]) * svh2[expert] ) for the valid positions.  One warp per (group of 8 positions,
@@ -233,21 +216,17 @@ __global__ void moe_tc_out_kernel(const __half* __restrict__ yd_rot, const __hal
     const int nb = (int)(item % nbs);
     const int p0 = (int)(item / nbs) * MOE_TC_GROUP;
     if (p0 >= *num_post) return;
+    const int p = p0 + (lane >> 2);
     const int ex = expert_ids[p0 / MOE_TC_BLOCK_ROWS];
-    const int col = nb * 128 + 4 * lane;
-    float sv[4];
-    load_h4(svh2 + (long long)ex * hidden + col, sv);
-    float v[MOE_TC_GROUP][4];
-    int slot[MOE_TC_GROUP];
+    const int col = nb * 128 + 32 * (lane & 3);
+    const int slot = sorted_ids[p];
+    float v[32];
+    load_h32(yd_rot + (long long)p * hidden + col, v);
+    unrotate32(v, svh2 + (long long)ex * hidden + col, lane);
+    if (slot >= 0 && slot < numel) {
+        uint4* dst = reinterpret_cast<uint4*>(yd + (long long)slot * hidden + col);
 #pragma unroll
-    for (int r = 0; r < MOE_TC_GROUP; r++) {
-        slot[r] = sorted_ids[p0 + r];
-        load_h4(yd_rot + (long long)(p0 + r) * hidden + col, v[r]);
-    }
-#pragma unroll
-    for (int r = 0; r < MOE_TC_GROUP; r++) {
-        unrotate4(v[r], sv, lane);
-        if (slot[r] >= 0 && slot[r] < numel) store_a4(yd, (long long)slot[r] * hidden + col, v[r]);
+        for (int i = 0; i < 4; i++) dst[i] = pack_h8(&v[8 * i]);
     }
 }
 
