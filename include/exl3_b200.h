@@ -343,10 +343,12 @@ exl3_status exl3_device_error(void *workspace, size_t workspace_bytes, void *str
  * 1 = paired (weights rounded to fp16 first, as the reference decoder's table).  No counterpart in the reference. */
 void exl3_set_gemv_mode(int mode);
 /* Measurement / test knob: output tiling of exl3_linear_tc.  -1 = library default, 0 = 512 x 128 tiles, 1 = 256 x 256 tiles
- * (used only where the column blocks pair up inside every shard), 2 = 384 x 128 tiles.  No counterpart in the reference. */
+ * (used only where the column blocks pair up inside every shard), 2 = 384 x 128 tiles, 3 = 512 x 256 tiles on pairs of CTAs
+ * (clusters of two, cta_group::2 MMAs; same condition as 1).  No counterpart in the reference. */
 void exl3_set_tc_tiling(int tiling);
 /* Measurement / test knob: upper bound of the parts the reduction of a tile is cut into when exl3_linear_tc has fewer
- * tiles than SMs (0 = library default, 1 = never split).  No counterpart in the reference. */
+ * tiles than SMs, or, with tiling 3, for the tiles of a last wave that does not fill the CTA pairs (0 = library default,
+ * 1 = never split).  No counterpart in the reference. */
 void exl3_set_tc_ksplit(int parts);
 
 #ifdef __cplusplus

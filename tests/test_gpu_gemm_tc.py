@@ -26,7 +26,8 @@ def _default_tiling():
     lin.set_tc_ksplit(0)
 
 
-@pytest.mark.parametrize("tiling", [0, 1, 2])       # 512 x 128; 256 x 256 (n = 384, 640, 128 have an odd block: narrow); 384 x 128
+# 512 x 128; 256 x 256 (n = 384, 640, 128 have an odd block: narrow); 384 x 128; 512 x 256 on a CTA pair (same condition)
+@pytest.mark.parametrize("tiling", [0, 1, 2, 3])
 @pytest.mark.parametrize("K,cb,k,n,rows", [(4, 1, 256, 256, 130), (3, 0, 512, 384, 512), (4, 1, 1024, 640, 700),
                                            (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025),
                                            (3, 0, 384, 768, 300), (6, 1, 256, 512, 257)])
@@ -63,3 +64,28 @@ def test_fused_group_and_bf16_through_the_tensor_core_path(ns):
     y16 = lin.run_tc(_t(x), b, suh_cat, svh_cat, ends, cb)
     dec = lin.run(_t(x), b, suh_cat, svh_cat, ends, cb)
     assert orc.rel_norm(y16.float().cpu().numpy(), dec.float().cpu().numpy()) <= 2e-3     # same answer as the decode kernel
+
+
+@pytest.mark.parametrize("k,n,rows,ksplit", [(2048, 512, 700, 0),        # 4 tiles: every tile cut (no whole ones)
+                                             (1024, 10240, 1024, 0),     # 80 tiles on the device's CTA pairs: a whole wave and a cut tail
+                                             (1024, 10240, 1000, 2)])    # the same with ragged rows and at most two parts
+def test_pair_tiling_with_a_cut_last_wave_matches_the_narrow_tiling(k, n, rows, ksplit):
+    K, cb = 3, 0
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(k + n)
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    w = random_packed(k, n, K, gen, torch.device(DEV))
+    suh, svh = random_signs(k, gen, torch.device(DEV), 1), random_signs(n, gen, torch.device(DEV)).view(-1)
+    x = torch.randn((rows, k), device=DEV, generator=gen).half()
+    lin.set_tc_tiling(0)
+    ref = lin.run_tc(x, w, suh, svh, [], cb).float()
+    lin.set_tc_tiling(3)
+    lin.set_tc_ksplit(ksplit)
+    got = lin.run_tc(x, w, suh, svh, [], cb).float()
+    again = lin.run_tc(x, w, suh, svh, [], cb).float()
+    torch.cuda.synchronize()
+    lin.device_error(torch.device(DEV))
+    assert torch.equal(got, again)                                   # parts are added in a fixed order
+    err = (got - ref).norm() / ref.norm()
+    assert err <= 1e-3, float(err)
+    assert float((got - ref).abs().max() / ref.pow(2).mean().sqrt()) <= 4e-3

@@ -636,12 +636,15 @@ exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, i
     __half* xa = reinterpret_cast<__half*>(ws + 256);
     __half* rot = reinterpret_cast<__half*>(ws + 256 + tc_up(gemm_tc_activation_bytes(rows, k, n_shards)));
     float* part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(rot) + tc_up((size_t)rows * n_total * sizeof(__half)));
-    int parts = 1;
+    TcSplit split = {1, 0, 0, 0};
     if (int rc = launch_gemm_tc(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), packed, K, codebook, a.shard_end_blocks,
-                                n_shards, rows, k, n_total, xa, rot, part, &parts, reinterpret_cast<int*>(ws), st))
+                                n_shards, rows, k, n_total, xa, rot, part, &split, reinterpret_cast<int*>(ws), st))
         return rc;
-    if (parts > 1)
-        return launch_had_out_sum(part, parts, (long long)rows * n_total, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y,
+    if (split.parts > 1 && split.tile_slabs)
+        return launch_had_out_tiles(rot, part, split.parts, split.tail_first, split.row_tiles, reinterpret_cast<const __half*>(svh_cat), rows,
+                                    n_total, y, y_dtype == EXL3_BF16, st);
+    if (split.parts > 1)
+        return launch_had_out_sum(part, split.parts, (long long)rows * n_total, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y,
                                   y_dtype == EXL3_BF16, st);
     return launch_had_out(rot, 0, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y, n_total, y_dtype == EXL3_BF16, st);
 }
@@ -882,7 +885,8 @@ size_t exl3_static_workspace_bytes(void) { return EXL3_STATIC_WORKSPACE_BYTES; }
 /* Test / measurement knob: force how hash-codebook weights enter the MMA (-1 default, 0 split, 1 paired). */
 void exl3_set_gemv_mode(int mode) { gemv_set_mode_override(mode); }
 
-/* Test / measurement knob: output tiling of the many-row tensor-core GEMM (-1 choose, 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128). */
+/* Test / measurement knob: output tiling of the many-row tensor-core GEMM (-1 choose, 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128,
+ * 3 = 512 x 256 on CTA pairs). */
 void exl3_set_tc_tiling(int tiling) { gemm_tc_set_tiling(tiling); }
 
 /* Test / measurement knob: at most `parts` parts of the reduction per tile in exl3_linear_tc (0 choose, 1 no split). */

@@ -63,6 +63,7 @@ struct GemmTcLaunch {
     long long xa_shard_stride;   // halves between shards
     uint32_t mul, add;
     int ksplit;                  // > 1: the reduction of every tile is cut into this many parts, each on its own CTA
+    int tail_first;              // pair tiling: tiles before this one are not cut
     float* part;                 //      which stores its fp32 accumulators into slab [part index][rows][n_total]
     long long part_slab;         //      floats per slab
     // Grouped (routed experts): work items come from a device-side list built after the routing alignment.  Item i =
@@ -117,6 +118,41 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 16 x 16 tile T of a reduction block: the warp's 16 columns x k 16T..16T+15, decoded from the warp's K x 32 words into the
+// B operand block at `bst`.  Pair j of a lane: k chunk 2T + (j & 1), column group cg0 + (j >> 1), row lane / 4 of the core
+// matrix, bytes 4 (lane % 4) .. + 3.
+template <int K, int FAM, int NCOLS, int T>
+__device__ __forceinline__ void tc_decode_tile(const uint32_t (&L)[K], unsigned char* bst, int cg0, int lane, const CodebookConst& cbc, const Pow2& pw)
+{
+    uint32_t own[2];
+    own_words<K, T>(L, own);
+    const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
+    const LaneRegs<K> R = lane_regs<K>(own, prev0);
+    uint32_t st[8];
+    st[0] = window_low<K, 0>(R, pw); st[1] = window_low<K, 1>(R, pw); st[2] = window_low<K, 2>(R, pw);
+    st[3] = window_low<K, 3>(R, pw); st[4] = window_low<K, 4>(R, pw); st[5] = window_low<K, 5>(R, pw);
+    st[6] = window_low<K, 6>(R, pw); st[7] = window_low<K, 7>(R, pw);
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) w[j] = FAM == FAM_HASH ? hash_pair_rounded(st[2 * j], st[2 * j + 1], cbc) : mul1_pair(st[2 * j], st[2 * j + 1], cbc);
+    const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int c = 2 * T + (j & 1), jn = cg0 + (j >> 1);
+        *reinterpret_cast<uint32_t*>(bst + (c * (NCOLS / 8) + jn) * 128 + g * 16 + q * 4) = w[j];
+    }
+}
+
+// The warp's 16 columns of one reduction block (64 deep): four tiles.
+template <int K, int FAM, int NCOLS>
+__device__ __forceinline__ void tc_decode_block(const uint32_t (&L)[K], unsigned char* bst, int cg0, int lane, const CodebookConst& cbc, const Pow2& pw)
+{
+    tc_decode_tile<K, FAM, NCOLS, 0>(L, bst, cg0, lane, cbc, pw);
+    tc_decode_tile<K, FAM, NCOLS, 1>(L, bst, cg0, lane, cbc, pw);
+    tc_decode_tile<K, FAM, NCOLS, 2>(L, bst, cg0, lane, cbc, pw);
+    tc_decode_tile<K, FAM, NCOLS, 3>(L, bst, cg0, lane, cbc, pw);
 }
 
 // SPLIT: the reduction of a tile may be cut into p.ksplit parts (work items); without it the part count is the constant 1
@@ -175,7 +211,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
 
     if (warp < DW) {
         // ------------------------------------------------------------------ decode + epilogue
-        const int nt = warp & 7, nbh = warp >> 3, g = lane >> 2, q = lane & 3;
+        const int nt = warp & 7, nbh = warp >> 3;
         const CodebookConst cbc = {p.mul, p.add};
         uint32_t it = 0, acc_round = 0;
         // The warp's words of the next reduction block are requested one block ahead, so their L2 latency hides
@@ -229,31 +265,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                 }
                 if (round > 0 && !failed && !ptx::mbar_wait(&empty[s], (round - 1) & 1)) fail();
                 unsigned char* bst = stage0 + (size_t)s * TT::STAGE_BYTES + TT::A_STAGE_BYTES;
-                auto tile = [&](auto tconst) {
-                    constexpr int T = decltype(tconst)::value;
-                    uint32_t own[2];
-                    own_words<K, T>(L, own);
-                    const uint32_t prev0 = __shfl_sync(0xFFFFFFFFu, own[0], (lane + 31) & 31);
-                    const LaneRegs<K> R = lane_regs<K>(own, prev0);
-                    uint32_t st[8];
-                    st[0] = window_low<K, 0>(R, p.pw); st[1] = window_low<K, 1>(R, p.pw); st[2] = window_low<K, 2>(R, p.pw);
-                    st[3] = window_low<K, 3>(R, p.pw); st[4] = window_low<K, 4>(R, p.pw); st[5] = window_low<K, 5>(R, p.pw);
-                    st[6] = window_low<K, 6>(R, p.pw); st[7] = window_low<K, 7>(R, p.pw);
-                    uint32_t w[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        w[j] = FAM == FAM_HASH ? hash_pair_rounded(st[2 * j], st[2 * j + 1], cbc) : mul1_pair(st[2 * j], st[2 * j + 1], cbc);
-                    // pair j: k chunk 2T + (j & 1), column group 2 * (8 * nbh + nt) + (j >> 1), row g of the core matrix, bytes 4q..4q+3
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const int c = 2 * T + (j & 1), jn = 2 * (8 * nbh + nt) + (j >> 1);
-                        *reinterpret_cast<uint32_t*>(bst + (c * (TT::NCOLS / 8) + jn) * 128 + g * 16 + q * 4) = w[j];
-                    }
-                };
-                tile(std::integral_constant<int, 0>{});
-                tile(std::integral_constant<int, 1>{});
-                tile(std::integral_constant<int, 2>{});
-                tile(std::integral_constant<int, 3>{});
+                tc_decode_block<K, FAM, TT::NCOLS>(L, bst, 2 * (8 * nbh + nt), lane, cbc, p.pw);
                 fence_async_smem();                     // generic-proxy stores -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&b_full[s]);
@@ -374,6 +386,271 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
     }
 }
 
+// ------------------------------------------------------------------------------------------------ CTA pairs
+// Two CTAs of a cluster on neighbouring SMs work on one 512 x 256 output tile with 256 x 256 x 16 MMAs (cta_group::2): each
+// CTA holds 128 rows of every MMA's A operand and accumulator and decodes 128 of the 256 columns of B; the tensor cores read
+// the other half from the partner's shared memory.  Against the single-CTA 512 x 128 tile this halves the operand bytes an SM
+// reads from shared memory per flop and the activation bytes it pulls from L2, at the same 512 rows per decoded weight.
+struct TcPair {
+    static constexpr int M_TILES = 2;                                        // 256-row MMAs stacked in a tile
+    static constexpr int ROWS = 256 * M_TILES;
+    static constexpr int STAGES = 4;
+    static constexpr int DECODE_WARPS = 8;
+    static constexpr int THREADS = (DECODE_WARPS + 2) * 32;
+    static constexpr uint32_t A_STAGE_BYTES = TC_A_TILE_BYTES * M_TILES;    // this CTA's 128 rows of each MMA
+    static constexpr uint32_t B_STAGE_BYTES = 128 * TC_KB * 2;              // this CTA's 128 columns
+    static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES;
+    static constexpr uint32_t B_LBO = (128 / 8) * 128;
+    // fp16 x fp16 -> fp32, both operands K-major, N = 256, M = 256 over the pair
+    static constexpr uint32_t IDESC = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+};
+
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far have completed.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(ptx::smem_addr(bar)),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+
+// Launched as clusters of two CTAs.  Work items, dealt to the pairs in turn: the first p.tail_first tiles whole, then every
+// remaining tile as p.ksplit parts of its reduction, so that the last wave of a tile count that does not divide by the
+// pairs is short: its parts store fp32 accumulators, slab [(tile - tail_first) * ksplit + part][512][256], which the output
+// rotation adds in part order.  Tile t = column tile t / row tiles, row tile t % row tiles.  Roles
+// per CTA: 8 decode + epilogue warps, an activation producer, and a warp whose first lane issues the MMAs of the pair (rank
+// 0) or reports this CTA's filled stages to rank 0 (rank 1).  Barriers sit at the same offsets in both CTAs; `empty` and
+// `acc_full` are signalled in both by the tensor core, `peer_full` and `acc_empty` of rank 0 by threads of rank 1.
+template <int K, int FAM>
+__global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const GemmTcLaunch p)
+{
+    using TT = TcPair;
+    constexpr int DW = TT::DECODE_WARPS, STAGES = TT::STAGES;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* a_full = reinterpret_cast<uint64_t*>(smem);            // [stages]
+    uint64_t* b_full = a_full + STAGES;
+    uint64_t* peer_full = b_full + STAGES;
+    uint64_t* empty = peer_full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    unsigned char* stage0 = smem + 1024;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_cta_rank();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            ptx::mbar_init(&a_full[s], 1);
+            ptx::mbar_init(&b_full[s], DW);
+            ptx::mbar_init(&peer_full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, 2 * DW);
+        ptx::mbar_fence_init();
+    }
+    if (warp == DW + 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_addr(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();                           // the partner's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int KB = p.KG * 2;                           // reduction blocks of 64
+    const int MT = (p.rows + TT::ROWS - 1) / TT::ROWS; // row tiles
+    const int NT = p.NB / 2;                           // column tiles
+    const int KS = p.ksplit;
+    const long long n_whole = p.tail_first;
+    const long long n_tiles = n_whole + ((long long)MT * NT - n_whole) * KS;     // work items
+    const long long first = blockIdx.x >> 1, step = gridDim.x >> 1;
+    auto tile_of = [&](long long t) { return t < n_whole ? t : n_whole + (t - n_whole) / KS; };
+    auto part_of = [&](long long t) { return t < n_whole ? 0 : (int)((t - n_whole) % KS); };
+    auto kb_begin = [&](long long t) { return t < n_whole ? 0 : (int)((long long)KB * part_of(t) / KS); };
+    auto kb_end = [&](long long t) { return t < n_whole ? KB : (int)((long long)KB * (part_of(t) + 1) / KS); };
+    bool failed = false;
+    auto fail = [&]() {
+        if (!failed) {
+            failed = true;
+            atomicExch(p.err, TC_ERR_WAIT);
+        }
+    };
+
+    if (warp < DW) {
+        // ------------------------------------------------------------------ decode + epilogue
+        const int nt = warp;
+        const CodebookConst cbc = {p.mul, p.add};
+        uint32_t it = 0, acc_round = 0;
+        auto block_of = [&](long long t) { return (int)(tile_of(t) / MT) * 2 + (int)rank; };
+        auto words_ptr = [&](int nb_, int kb) {
+            return p.packed + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
+        };
+        uint32_t Lnext[K];
+        if (first < n_tiles) {
+            const uint32_t* src = words_ptr(block_of(first), kb_begin(first));
+#pragma unroll
+            for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
+        }
+        for (long long t = first; t < n_tiles; t += step) {
+            const long long tile = tile_of(t);
+            const int ms = (int)(tile % MT), ct = (int)(tile / MT);
+            const int kb0 = kb_begin(t), kb1 = kb_end(t);
+            const long long t_next = t + step;
+            const int nb_cur = block_of(t), nb_next = t_next < n_tiles ? block_of(t_next) : 0;
+            const int kb_next = t_next < n_tiles ? kb_begin(t_next) : 0;
+            for (int kb = kb0; kb < kb1; kb++, it++) {
+                const int s = it % STAGES;
+                const uint32_t round = it / STAGES;
+                uint32_t L[K];
+#pragma unroll
+                for (int i = 0; i < K; i++) L[i] = Lnext[i];
+                {
+                    const bool last = kb + 1 == kb1;
+                    if (!last || t_next < n_tiles) {
+                        const uint32_t* src = last ? words_ptr(nb_next, kb_next) : words_ptr(nb_cur, kb + 1);
+#pragma unroll
+                        for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
+                    }
+                }
+                if (round > 0 && !failed && !ptx::mbar_wait(&empty[s], (round - 1) & 1)) fail();
+                tc_decode_block<K, FAM, 128>(L, stage0 + (size_t)s * TT::STAGE_BYTES + TT::A_STAGE_BYTES, 2 * nt, lane, cbc, p.pw);
+                fence_async_smem();                     // generic-proxy stores -> visible to the tensor cores' reads
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&b_full[s]);
+            }
+            // ---- epilogue: this CTA's 128 rows of both MMAs.  A warp reads the 32 tensor-memory lanes of its quarter and
+            // 128 of the tile's 256 columns.
+            if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
+            tc_fence_after();
+            const int quarter = warp & 3, cgroup = warp >> 2;
+#pragma unroll 1
+            for (int mt = 0; mt < TT::M_TILES; mt++) {
+                const int row_in = mt * 256 + (int)rank * 128 + quarter * 32 + lane, row = ms * TT::ROWS + row_in;
+#pragma unroll 1
+                for (int cc = 0; cc < 4; cc++) {
+                    const int col = cgroup * 128 + cc * 32;
+                    uint32_t r[32];
+                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * 256 + col), r);
+                    if (row < p.rows && t >= n_whole) {
+                        float* dst = p.part + ((size_t)(tile - n_whole) * KS + part_of(t)) * (TT::ROWS * 256) + (size_t)row_in * 256 + col;
+#pragma unroll
+                        for (int v = 0; v < 32; v += 4)
+                            *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
+                    } else if (row < p.rows) {
+                        __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * 256 + col;
+#pragma unroll
+                        for (int v = 0; v < 32; v += 8) {
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(__uint_as_float(r[v]), __uint_as_float(r[v + 1]));
+                            __half2 h1 = __floats2half2_rn(__uint_as_float(r[v + 2]), __uint_as_float(r[v + 3]));
+                            __half2 h2 = __floats2half2_rn(__uint_as_float(r[v + 4]), __uint_as_float(r[v + 5]));
+                            __half2 h3 = __floats2half2_rn(__uint_as_float(r[v + 6]), __uint_as_float(r[v + 7]));
+                            o.x = *reinterpret_cast<uint32_t*>(&h0);
+                            o.y = *reinterpret_cast<uint32_t*>(&h1);
+                            o.z = *reinterpret_cast<uint32_t*>(&h2);
+                            o.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(dst + v) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) ptx::mbar_arrive(acc_empty);
+                else ptx::mbar_arrive_cluster(acc_empty, 0);
+            }
+            acc_round++;
+        }
+    } else if (warp == DW) {
+        // ------------------------------------------------------------------ activation producer: rows 128 rank .. + 127 of each MMA
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (long long t = first; t < n_tiles; t += step) {
+                const int ms = (int)(tile_of(t) % MT), nb = (int)(tile_of(t) / MT) * 2;
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                int shard = 0;
+                while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
+                    ptx::mbar_arrive_expect_tx(&a_full[s], TT::A_STAGE_BYTES);
+                    for (int mt = 0; mt < TT::M_TILES; mt++) {
+                        // 128-row tile 2 mt + rank of the 512-row super tile ms
+                        const __half* src = p.xa + shard * p.xa_shard_stride + (((long long)ms * KB + kb) * 4 + 2 * mt + (int)rank) * (TC_A_TILE_BYTES / 2);
+                        ptx::bulk_g2s(stage0 + (size_t)s * TT::STAGE_BYTES + (size_t)mt * TC_A_TILE_BYTES, src, TC_A_TILE_BYTES, &a_full[s]);
+                    }
+                }
+            }
+            // The tensor core's last arrivals on `empty` land in this CTA's shared memory: seen before the CTA may leave.
+            for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++)
+                if (!failed && !ptx::mbar_wait_relaxed(&empty[j % STAGES], (j / STAGES) & 1)) fail();
+        }
+    } else if (lane == 0) {
+        uint32_t it = 0, acc_round = 0;
+        if (rank == 0) {
+            // -------------------------------------------------------------- MMA issue for the pair
+            for (long long t = first; t < n_tiles; t += step) {
+                if (acc_round > 0 && !failed && !ptx::mbar_wait_cluster(acc_empty, (acc_round - 1) & 1)) fail();
+                tc_fence_after();
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (!failed && !ptx::mbar_wait(&a_full[s], round & 1)) fail();
+                    if (!failed && !ptx::mbar_wait(&b_full[s], round & 1)) fail();
+                    if (!failed && !ptx::mbar_wait_cluster(&peer_full[s], round & 1)) fail();
+                    tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_addr(stage0 + (size_t)s * TT::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TT::A_STAGE_BYTES;
+#pragma unroll
+                    for (int mt = 0; mt < TT::M_TILES; mt++)
+#pragma unroll
+                        for (int ks = 0; ks < TC_KB / 16; ks++)
+                            tc_mma_pair(tmem_base + (uint32_t)(mt * 256), tc_smem_desc(a_addr + mt * TC_A_TILE_BYTES + ks * 4096, 2048),
+                                        tc_smem_desc(b_addr + ks * 2 * TT::B_LBO, TT::B_LBO), TT::IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
+                    tc_commit_pair(&empty[s]);          // the stage is reusable in both CTAs once these MMAs have read it
+                }
+                tc_commit_pair(acc_full);               // accumulators complete in both CTAs
+                acc_round++;
+            }
+        } else {
+            // -------------------------------------------------------------- this CTA's stages reported to rank 0
+            for (long long t = first; t < n_tiles; t += step) {
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (!failed && !ptx::mbar_wait(&a_full[s], round & 1)) fail();
+                    if (!failed && !ptx::mbar_wait(&b_full[s], round & 1)) fail();
+                    ptx::mbar_arrive_cluster(&peer_full[s], 0);
+                }
+            }
+        }
+    }
+
+    // Neither CTA may leave, nor free tensor memory, while its partner can still signal it or the pair's MMAs run.
+    tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    if (warp == DW + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 // Rotated activations in the A-operand layout of gemm_tc_kernel.  One warp per (shard, group of 8 rows, 128-block), four lanes
 // per row with 32 columns each (fwht128_quad): a lane's 32 results are four whole 16-byte core-matrix rows, and the eight
 // lanes that share a column range fill a 128-byte core matrix.  Rows beyond `rows` inside the last group are written as
@@ -448,10 +725,36 @@ static int launch_tc_variant(const GemmTcLaunch& l, int sm_count, cudaStream_t s
     return l.ksplit > 1 ? launch_tc_kernel<K, FAM, MT, WIDE, true>(l, sm_count, st) : launch_tc_kernel<K, FAM, MT, WIDE, false>(l, sm_count, st);
 }
 
-// tiling: 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128
+// CTA pairs that can be resident at once (clusters of two on neighbouring SMs); 0 until a device is initialised or when the
+// query fails, which switches the pair tiling off.
+static int g_tc_pairs = 0;
+
+template <int K, int FAM>
+static int launch_tc_pair(const GemmTcLaunch& l, cudaStream_t st)
+{
+    const long long tiles = (long long)((l.rows + TcPair::ROWS - 1) / TcPair::ROWS) * (l.NB / 2);
+    const long long work = l.tail_first + (tiles - l.tail_first) * l.ksplit;
+    const int pairs = work < g_tc_pairs ? (int)work : g_tc_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(TcPair::THREADS);
+    cfg.dynamicSmemBytes = TcPair::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<K, FAM>, l));
+}
+
+// tiling: 0 = 512 x 128, 1 = 256 x 256, 2 = 384 x 128, 3 = 512 x 256 on a CTA pair
 template <int K, int FAM>
 static int launch_tc_fam(const GemmTcLaunch& l, int tiling, int sm_count, cudaStream_t st)
 {
+    if (tiling == 3) return launch_tc_pair<K, FAM>(l, st);
     if (tiling == 1) return launch_tc_variant<K, FAM, 2, true>(l, sm_count, st);
     if (tiling == 2) return launch_tc_variant<K, FAM, 3, false>(l, sm_count, st);
     return launch_tc_variant<K, FAM, 4, false>(l, sm_count, st);
@@ -490,6 +793,8 @@ static int tc_set_attr_k()
         rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_HASH, 4, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TN::SMEM_BYTES));
     if (rc == EXL3_OK)
         rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_MUL1, 4, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TN::SMEM_BYTES));
+    if (rc == EXL3_OK) rc = cuda_status(cudaFuncSetAttribute(gemm_tc_pair_kernel<K, FAM_HASH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPair::SMEM_BYTES));
+    if (rc == EXL3_OK) rc = cuda_status(cudaFuncSetAttribute(gemm_tc_pair_kernel<K, FAM_MUL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPair::SMEM_BYTES));
     using TG = TcTile<TC_GROUPED_MT, true>;
     if (rc == EXL3_OK)
         rc = cuda_status(cudaFuncSetAttribute(gemm_tc_kernel<K, FAM_HASH, TC_GROUPED_MT, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TG::SMEM_BYTES));
@@ -507,13 +812,36 @@ int gemm_tc_init_device()
     if (rc == EXL3_OK) rc = tc_set_attr_k<6>();
     if (rc == EXL3_OK) rc = tc_set_attr_k<7>();
     if (rc == EXL3_OK) rc = tc_set_attr_k<8>();
+    if (rc == EXL3_OK) {
+        // How many clusters of two fit on the device at once (every instance has the same footprint).
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2);
+        cfg.blockDim = dim3(TcPair::THREADS);
+        cfg.dynamicSmemBytes = TcPair::SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<4, FAM_HASH>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        g_tc_pairs = n;
+    }
     return rc;
 }
 
+int gemm_tc_pairs() { return g_tc_pairs; }
+
 constexpr int TC_MAX_KSPLIT = 8;
+constexpr int TC_PAIR_MAX_KSPLIT = 16;     // parts of a tile of the pair tiling's last wave
 static int g_tc_ksplit = 0;           // 0 = choose; n >= 1 = at most n parts (1 switches the split off)
 void gemm_tc_set_ksplit(int n) { g_tc_ksplit = n; }
-static int g_tc_tiling = -1;          // -1 = choose; 0 = 512 x 128; 1 = 256 x 256 where the shape allows; 2 = 384 x 128
+static int g_tc_tiling = -1;          // -1 = choose; 0 = 512 x 128; 1 = 256 x 256 where the shape allows; 2 = 384 x 128; 3 = 512 x 256 on CTA pairs, same condition
 void gemm_tc_set_tiling(int t) { g_tc_tiling = t; }
 
 size_t gemm_tc_activation_bytes(int rows, int k, int shards)
@@ -532,7 +860,7 @@ size_t gemm_tc_part_bytes(int rows, int n_total)
 }
 
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
-                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, int* ksplit_out, int* err, cudaStream_t st)
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, TcSplit* split_out, int* err, cudaStream_t st)
 {
     const DeviceInfo* d = current_device_info();
     if (!d) return EXL3_ERR_NOT_INITIALISED;
@@ -566,18 +894,49 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
     // rows per tile (160 tiles of 512 rows on 148 SMs are two waves; 240 tiles of 384 rows are two shorter ones).
     bool can_wide = (l.NB % 2) == 0;
     for (int s = 0; s < n_shards - 1; s++) can_wide = can_wide && (shard_end_blocks[s] % 2) == 0;
+    // The CTA-pair tiling (512 x 256 on two SMs, same condition on the column blocks) shares a decoded block over 512 rows
+    // like the narrow one but reads half the operand bytes per flop; when its tile count does not divide by the resident
+    // pairs, the tiles of the last wave are cut along the reduction into parts that fill the pairs once (fp32 slabs per
+    // tile, added by the output rotation): 80 tiles on 74 pairs are 1.08 waves instead of 2.
+    const long long pair_tiles = (long long)((rows + TcPair::ROWS - 1) / TcPair::ROWS) * (l.NB / 2);
+    long long pair_whole = pair_tiles, pair_parts = 1;
+    if (g_tc_pairs > 0 && pair_tiles % g_tc_pairs != 0) {
+        const long long rem = pair_tiles % g_tc_pairs;
+        long long ks = g_tc_pairs / rem;
+        if (ks > TC_PAIR_MAX_KSPLIT) ks = TC_PAIR_MAX_KSPLIT;
+        if (ks > l.KG / 2) ks = l.KG / 2;                       // at least four reduction blocks per part
+        while (ks > 1 && (size_t)rem * ks * TcPair::ROWS * 256 * sizeof(float) > gemm_tc_part_bytes(rows, n_total)) ks--;
+        if (g_tc_ksplit >= 1 && ks > g_tc_ksplit) ks = g_tc_ksplit;
+        if (part && ks > 1) {
+            pair_parts = ks;
+            pair_whole = pair_tiles - rem;
+        }
+    }
     int tiling = g_tc_tiling;
     if (tiling < 0) {
         auto cost = [&](int mt) {
             const long long tiles = (long long)((rows + 128 * mt - 1) / (128 * mt)) * l.NB;
-            return (tiles + d->sm_count - 1) / d->sm_count * mt;
+            return (double)((tiles + d->sm_count - 1) / d->sm_count * mt);
         };
         tiling = rows <= 256 ? 1 : (cost(3) < cost(4) ? 2 : 0);
+        if (rows > 256 && can_wide && g_tc_pairs > 0) {
+            const double waves = pair_parts > 1 ? (double)(pair_whole / g_tc_pairs) + 1.0 / (double)pair_parts
+                                                : (double)((pair_tiles + g_tc_pairs - 1) / g_tc_pairs);
+            if (4.0 * waves <= (cost(3) < cost(4) ? cost(3) : cost(4))) tiling = 3;
+        }
     }
-    if (tiling == 1 && !can_wide) tiling = 0;
-    // Few tiles (narrow outputs at small row counts) leave most SMs idle: the reduction of every tile is then cut into
-    // parts that run on CTAs of their own and store fp32 slabs, which the output rotation adds in part order.
-    {
+    if ((tiling == 1 || tiling == 3) && !can_wide) tiling = 0;
+    if (tiling == 3 && g_tc_pairs < 1) tiling = 0;
+    l.part = part;
+    l.part_slab = (long long)rows * n_total;
+    l.tail_first = 0;
+    if (tiling == 3) {
+        l.ksplit = (int)pair_parts;
+        l.tail_first = (int)pair_whole;
+        if (split_out) *split_out = TcSplit{l.ksplit, 1, l.tail_first, (rows + TcPair::ROWS - 1) / TcPair::ROWS};
+    } else {
+        // Few tiles (narrow outputs at small row counts) leave most SMs idle: the reduction of every tile is then cut into
+        // parts that run on CTAs of their own and store fp32 slabs, which the output rotation adds in part order.
         const int tile_rows = tiling == 1 ? 256 : tiling == 2 ? 384 : 512;
         const long long tiles = (long long)((rows + tile_rows - 1) / tile_rows) * (l.NB / (tiling == 1 ? 2 : 1));
         long long parts = tiles > 0 ? d->sm_count / tiles : 1;
@@ -586,9 +945,7 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
         while (parts > 1 && (size_t)parts * rows * n_total * sizeof(float) > gemm_tc_part_bytes(rows, n_total)) parts--;
         if (g_tc_ksplit >= 1 && parts > g_tc_ksplit) parts = g_tc_ksplit;
         l.ksplit = part && parts > 1 ? (int)parts : 1;
-        l.part = part;
-        l.part_slab = (long long)rows * n_total;
-        if (ksplit_out) *ksplit_out = l.ksplit;
+        if (split_out) *split_out = TcSplit{l.ksplit, 0, 0, 0};
     }
     const int fam = codebook_family(codebook);
     switch (K) {

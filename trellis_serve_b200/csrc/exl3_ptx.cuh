@@ -65,6 +65,44 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// ---- thread-block clusters: a barrier of the other CTA of a pair, and the cluster-wide barrier
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// All threads of every CTA of the cluster (convergent warps).
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
+{
+    asm volatile("{\n .reg .b32 ra;\n mapa.shared::cluster.u32 ra, %0, %1;\n mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n}" ::"r"(
+                     smem_addr(bar)),
+                 "r"(cta)
+                 : "memory");
+}
+
+// Bounded wait on a barrier of this CTA that threads of the other CTA arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < MBAR_MAX_POLLS; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(smem_addr(bar)), "r"(parity), "r"(MBAR_SUSPEND_NS)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // Shared-memory counter update with acquire-release semantics inside the CTA.
 __device__ __forceinline__ int atom_add_acq_rel_cta_shared(int* addr, int v)
 {

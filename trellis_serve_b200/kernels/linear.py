@@ -479,7 +479,8 @@ def device_error(device: torch.device) -> None:
 
 
 def set_tc_tiling(tiling: int) -> None:
-    """Knob: output tiling of `run_tc`: -1 default, 0 tiles of 512 x 128, 1 of 256 x 256 (where the shape allows), 2 of 384 x 128."""
+    """Knob: output tiling of `run_tc`: -1 default, 0 tiles of 512 x 128, 1 of 256 x 256 (where the shape allows), 2 of 384 x 128,
+    3 of 512 x 256 on pairs of CTAs (same condition as 1)."""
     _lib.load().exl3_set_tc_tiling(int(tiling))
 
 
