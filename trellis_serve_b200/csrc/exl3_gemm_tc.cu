@@ -394,13 +394,17 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
 struct TcPair {
     static constexpr int M_TILES = 2;                                        // 256-row MMAs stacked in a tile
     static constexpr int ROWS = 256 * M_TILES;
-    static constexpr int STAGES = 4;
+    static constexpr int STAGES = 3;
     static constexpr int DECODE_WARPS = 8;
     static constexpr int THREADS = (DECODE_WARPS + 2) * 32;
     static constexpr uint32_t A_STAGE_BYTES = TC_A_TILE_BYTES * M_TILES;    // this CTA's 128 rows of each MMA
     static constexpr uint32_t B_STAGE_BYTES = 128 * TC_KB * 2;              // this CTA's 128 columns
     static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES;
+    // Output staging: per epilogue warp 32 rows x 128 fp16 columns, rows 16 bytes apart from a multiple of 128 so that the
+    // lanes' 16-byte stores fall on different banks.
+    static constexpr uint32_t OUT_PITCH = 128 * 2 + 16;
+    static constexpr uint32_t OUT_WARP_BYTES = 32 * OUT_PITCH;
+    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)DECODE_WARPS * OUT_WARP_BYTES;
     static constexpr uint32_t B_LBO = (128 / 8) * 128;
     // fp16 x fp16 -> fp32, both operands K-major, N = 256, M = 256 over the pair
     static constexpr uint32_t IDESC = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
@@ -444,6 +448,7 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
     uint64_t* acc_empty = acc_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     unsigned char* stage0 = smem + 1024;
+    unsigned char* out_stage = stage0 + (size_t)STAGES * TcPair::STAGE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_cta_rank();
@@ -530,25 +535,30 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
                 if (lane == 0) ptx::mbar_arrive(&b_full[s]);
             }
             // ---- epilogue: this CTA's 128 rows of both MMAs.  A warp reads the 32 tensor-memory lanes of its quarter and
-            // 128 of the tile's 256 columns.
+            // 128 of the tile's 256 columns; a lane rounds its row to fp16 into the warp's staging slice and sends the 256 bytes
+            // to global memory as one bulk copy, which completes behind the next tile's MMAs.  Tensor memory is handed back
+            // as soon as it has been read.  Parts of a cut tile store their fp32 accumulators directly.
             if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
             tc_fence_after();
             const int quarter = warp & 3, cgroup = warp >> 2;
+            unsigned char* my_row = out_stage + (size_t)warp * TT::OUT_WARP_BYTES + (size_t)lane * TT::OUT_PITCH;
 #pragma unroll 1
             for (int mt = 0; mt < TT::M_TILES; mt++) {
                 const int row_in = mt * 256 + (int)rank * 128 + quarter * 32 + lane, row = ms * TT::ROWS + row_in;
+                ptx::bulk_wait_read_all();              // the lane's previous copy has left its staging row
 #pragma unroll 1
                 for (int cc = 0; cc < 4; cc++) {
                     const int col = cgroup * 128 + cc * 32;
                     uint32_t r[32];
                     tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * 256 + col), r);
-                    if (row < p.rows && t >= n_whole) {
-                        float* dst = p.part + ((size_t)(tile - n_whole) * KS + part_of(t)) * (TT::ROWS * 256) + (size_t)row_in * 256 + col;
+                    if (t >= n_whole) {
+                        if (row < p.rows) {
+                            float* dst = p.part + ((size_t)(tile - n_whole) * KS + part_of(t)) * (TT::ROWS * 256) + (size_t)row_in * 256 + col;
 #pragma unroll
-                        for (int v = 0; v < 32; v += 4)
-                            *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
-                    } else if (row < p.rows) {
-                        __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * 256 + col;
+                            for (int v = 0; v < 32; v += 4)
+                                *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
+                        }
+                    } else {
 #pragma unroll
                         for (int v = 0; v < 32; v += 8) {
                             uint4 o;
@@ -560,19 +570,27 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
                             o.y = *reinterpret_cast<uint32_t*>(&h1);
                             o.z = *reinterpret_cast<uint32_t*>(&h2);
                             o.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(dst + v) = o;
+                            *reinterpret_cast<uint4*>(my_row + cc * 64 + v * 2) = o;
                         }
                     }
                 }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if (rank == 0) ptx::mbar_arrive(acc_empty);
-                else ptx::mbar_arrive_cluster(acc_empty, 0);
+                if (mt == TT::M_TILES - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rank == 0) ptx::mbar_arrive(acc_empty);
+                        else ptx::mbar_arrive_cluster(acc_empty, 0);
+                    }
+                }
+                if (t < n_whole && row < p.rows) {
+                    fence_async_smem();                 // the lane's own stores -> visible to the copy engine
+                    ptx::bulk_s2g(p.out + (size_t)row * p.n_total + (size_t)ct * 256 + cgroup * 128, my_row, 256);
+                    ptx::bulk_commit();
+                }
             }
             acc_round++;
         }
+        ptx::bulk_wait_all();                           // the lane's output copies have completed
     } else if (warp == DW) {
         // ------------------------------------------------------------------ activation producer: rows 128 rank .. + 127 of each MMA
         if (lane == 0) {

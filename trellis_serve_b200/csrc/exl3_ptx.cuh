@@ -147,6 +147,16 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start before
 // the kernel ahead of it in the stream has finished.  `grid_dependency_wait` blocks until that kernel has completed
 // and its writes are visible; `grid_launch_dependents` lets the next kernel in the stream start its own prologue.
+// 1-D bulk copy shared -> global (16-byte aligned on both sides, size a multiple of 16), tracked by the issuing thread's
+// bulk groups: commit, then wait until the source may be overwritten (.read) or until the copies have completed.
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_addr(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
