@@ -228,7 +228,7 @@ def run_prefill(args) -> None:
                       "config": {"workload": f"one 27B-shape layer (qkv, o, gate_up, down), {rows} rows, K=4 MCG, fused tcgen05 GEMM",
                                  "rows": rows, "l2": "weights 165 MB per layer, larger than L2"},
                       "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
-                                   "peak_source": "of measured (burst)", "kernel": "gemm_tc_kernel"},
+                                   "peak_source": "of measured (burst)", "kernel": "gemm_tc_pair_kernel"},
                       "gpu_launches": 16 * args.steps, "clocks": clocks.summary()}))
 
 
