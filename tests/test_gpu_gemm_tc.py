@@ -30,7 +30,8 @@ def _default_tiling():
 @pytest.mark.parametrize("tiling", [0, 1, 2, 3])
 @pytest.mark.parametrize("K,cb,k,n,rows", [(4, 1, 256, 256, 130), (3, 0, 512, 384, 512), (4, 1, 1024, 640, 700),
                                            (5, 2, 256, 128, 33), (2, 0, 384, 256, 1), (8, 1, 256, 256, 1025),
-                                           (3, 0, 384, 768, 300), (6, 1, 256, 512, 257)])
+                                           (3, 0, 384, 768, 300), (6, 1, 256, 512, 257), (5, 2, 256, 512, 300),
+                                           (7, 2, 1024, 256, 520)])
 @pytest.mark.parametrize("ksplit", [0, 1, 3])     # reduction of a tile cut into parts when tiles are few: default, never, at most 3
 def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows, tiling, ksplit):
     tr, suh, svh = seeded_trellis(K * 7 + cb, k // 16, n // 16, K), seeded_signs(1, k), seeded_signs(2, n)
@@ -47,9 +48,11 @@ def test_tensor_core_gemm_matches_the_oracle(K, cb, k, n, rows, tiling, ksplit):
     assert orc.max_over_rms(got, ref) <= 4e-3, orc.max_over_rms(got, ref)
 
 
+@pytest.mark.parametrize("tiling", [-1, 3])
 @pytest.mark.parametrize("ns", [[256, 128], [256, 512]])       # an odd shard boundary forces narrow tiles; even ones pair up
-def test_fused_group_and_bf16_through_the_tensor_core_path(ns):
+def test_fused_group_and_bf16_through_the_tensor_core_path(ns, tiling):
     K, cb, k, rows = 4, 1, 512, 300
+    lin.set_tc_tiling(tiling)
     parts = [(seeded_trellis(80 + i, k // 16, n // 16, K), seeded_signs(81 + i, k), seeded_signs(84 + i, n)) for i, n in enumerate(ns)]
     b, suh_cat, svh_cat, ends = lin.prepare([_t(p[0]) for p in parts], [_t(p[1]) for p in parts], [_t(p[2]) for p in parts])
     x = np.random.default_rng(3).standard_normal((rows, k)).astype(np.float16)
