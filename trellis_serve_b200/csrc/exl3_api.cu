@@ -638,11 +638,14 @@ exl3_status exl3_linear_tc(const void* x, int x_dtype, const uint32_t* packed, i
     float* part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(rot) + tc_up((size_t)rows * n_total * sizeof(__half)));
     TcSplit split = {1, 0, 0, 0};
     if (int rc = launch_gemm_tc(x, x_dtype == EXL3_BF16, reinterpret_cast<const __half*>(suh_cat), packed, K, codebook, a.shard_end_blocks,
-                                n_shards, rows, k, n_total, xa, rot, part, &split, reinterpret_cast<int*>(ws), st))
+                                n_shards, rows, k, n_total, xa, rot, part, y, reinterpret_cast<const __half*>(svh_cat), y_dtype == EXL3_BF16,
+                                &split, reinterpret_cast<int*>(ws), st))
         return rc;
-    if (split.parts > 1 && split.tile_slabs)
-        return launch_had_out_tiles(rot, part, split.parts, split.tail_first, split.row_tiles, reinterpret_cast<const __half*>(svh_cat), rows,
+    if (split.tile_slabs) {
+        if (split.parts == 1) return EXL3_OK;
+        return launch_had_out_tiles(part, split.parts, split.tail_first, split.row_tiles, reinterpret_cast<const __half*>(svh_cat), rows,
                                     n_total, y, y_dtype == EXL3_BF16, st);
+    }
     if (split.parts > 1)
         return launch_had_out_sum(part, split.parts, (long long)rows * n_total, reinterpret_cast<const __half*>(svh_cat), rows, n_total, y,
                                   y_dtype == EXL3_BF16, st);

@@ -336,4 +336,48 @@ __device__ __forceinline__ void fwht128_quad(float (&v)[32], int lane)
 
 constexpr float HAD_SCALE = 0.08838834764831845f;   // 1 / sqrt(128)
 
+// 32 consecutive halves (64 bytes, 16-byte aligned) as floats.
+__device__ __forceinline__ void load_half32(const __half* __restrict__ src, float (&v)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+            v[8 * i + 2 * j] = __low2float(h);
+            v[8 * i + 2 * j + 1] = __high2float(h);
+        }
+    }
+}
+
+// A lane's 32 rotated values -> out[at .. at + 31] = fp16(v * (scale * svh[col ..])), or that value converted to bf16: the
+// order of the fused epilogues.
+__device__ __forceinline__ void had_out_finish(const float (&v)[32], const __half* __restrict__ svh, int col, void* __restrict__ out, long long at,
+                                               int out_bf16)
+{
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint4 sraw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);       // ones
+        if (svh) sraw = reinterpret_cast<const uint4*>(svh + col)[i];
+        const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 sh = *reinterpret_cast<const __half2*>(&sw[j]);
+            const __half2 h = __floats2half2_rn(v[8 * i + 2 * j] * (HAD_SCALE * __low2float(sh)), v[8 * i + 2 * j + 1] * (HAD_SCALE * __high2float(sh)));
+            if (out_bf16) {
+                const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(h), __high2float(h));
+                packed[4 * i + j] = *reinterpret_cast<const uint32_t*>(&bb);
+            } else {
+                packed[4 * i + j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + at);
+#pragma unroll
+    for (int i = 0; i < 4; i++) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+}
+
 }  // namespace exl3

@@ -63,7 +63,10 @@ struct GemmTcLaunch {
     long long xa_shard_stride;   // halves between shards
     uint32_t mul, add;
     int ksplit;                  // > 1: the reduction of every tile is cut into this many parts, each on its own CTA
-    int tail_first;              // pair tiling: tiles before this one are not cut
+    int tail_first;              // pair tiling: tiles before this one are not cut ...
+    void* y;                     // ... and leave the kernel rotated: y[rows][n_total] = fp16 or bf16 of Had128(fp16(acc)) * svh
+    const __half* svh;
+    int y_bf16;
     float* part;                 //      which stores its fp32 accumulators into slab [part index][rows][n_total]
     long long part_slab;         //      floats per slab
     // Grouped (routed experts): work items come from a device-side list built after the routing alignment.  Item i =
@@ -535,8 +538,9 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
                 if (lane == 0) ptx::mbar_arrive(&b_full[s]);
             }
             // ---- epilogue: this CTA's 128 rows of both MMAs.  A warp reads the 32 tensor-memory lanes of its quarter and
-            // 128 of the tile's 256 columns; a lane rounds its row to fp16 into the warp's staging slice and sends the 256 bytes
-            // to global memory as one bulk copy, which completes behind the next tile's MMAs.  Tensor memory is handed back
+            // 128 of the tile's 256 columns; a lane rounds its row to fp16 into the warp's staging slice, the warp applies the
+            // output rotation and the svh vector there, and every lane sends its row's 256 bytes to y as one bulk copy, which
+            // completes behind the next tile's MMAs.  Tensor memory is handed back
             // as soon as it has been read.  Parts of a cut tile store their fp32 accumulators directly.
             if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
             tc_fence_after();
@@ -545,7 +549,8 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
 #pragma unroll 1
             for (int mt = 0; mt < TT::M_TILES; mt++) {
                 const int row_in = mt * 256 + (int)rank * 128 + quarter * 32 + lane, row = ms * TT::ROWS + row_in;
-                ptx::bulk_wait_read_all();              // the lane's previous copy has left its staging row
+                ptx::bulk_wait_read_all();              // the lane's previous copy has left its staging row ...
+                __syncwarp();                           // ... and so has every other lane's (a row is rotated by four lanes)
 #pragma unroll 1
                 for (int cc = 0; cc < 4; cc++) {
                     const int col = cgroup * 128 + cc * 32;
@@ -582,10 +587,25 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
                         else ptx::mbar_arrive_cluster(acc_empty, 0);
                     }
                 }
-                if (t < n_whole && row < p.rows) {
-                    fence_async_smem();                 // the lane's own stores -> visible to the copy engine
-                    ptx::bulk_s2g(p.out + (size_t)row * p.n_total + (size_t)ct * 256 + cgroup * 128, my_row, 256);
-                    ptx::bulk_commit();
+                if (t < n_whole) {
+                    // The warp's 32 rows x 128 columns are whole blocks of the output rotation: done here on the staged
+                    // rows, eight rows at a time with four lanes per row (the arithmetic of had_out_kernel, same bits).
+                    __syncwarp();
+#pragma unroll 1
+                    for (int pass = 0; pass < 4; pass++) {
+                        __half* at = reinterpret_cast<__half*>(out_stage + (size_t)warp * TT::OUT_WARP_BYTES + (size_t)(pass * 8 + (lane >> 2)) * TT::OUT_PITCH) +
+                                     32 * (lane & 3);
+                        float v[32];
+                        load_half32(at, v);
+                        fwht128_quad(v, lane);
+                        had_out_finish(v, p.svh, ct * 256 + cgroup * 128 + 32 * (lane & 3), at, 0, p.y_bf16);
+                    }
+                    fence_async_smem();                 // every lane's stores -> visible to the copy engine
+                    __syncwarp();
+                    if (row < p.rows) {
+                        ptx::bulk_s2g(reinterpret_cast<uint16_t*>(p.y) + (size_t)row * p.n_total + (size_t)ct * 256 + cgroup * 128, my_row, 256);
+                        ptx::bulk_commit();
+                    }
                 }
             }
             acc_round++;
@@ -878,7 +898,8 @@ size_t gemm_tc_part_bytes(int rows, int n_total)
 }
 
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
-                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, TcSplit* split_out, int* err, cudaStream_t st)
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, void* y, const __half* svh, int y_bf16, TcSplit* split_out, int* err,
+                   cudaStream_t st)
 {
     const DeviceInfo* d = current_device_info();
     if (!d) return EXL3_ERR_NOT_INITIALISED;
@@ -951,6 +972,9 @@ int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint3
     if (tiling == 3) {
         l.ksplit = (int)pair_parts;
         l.tail_first = (int)pair_whole;
+        l.y = y;
+        l.svh = svh;
+        l.y_bf16 = y_bf16;
         if (split_out) *split_out = TcSplit{l.ksplit, 1, l.tail_first, (rows + TcPair::ROWS - 1) / TcPair::ROWS};
     } else {
         // Few tiles (narrow outputs at small row counts) leave most SMs idle: the reduction of every tile is then cut into

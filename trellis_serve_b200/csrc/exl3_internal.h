@@ -178,9 +178,10 @@ int launch_moe_tc_experts(const void* x, int x_bf16, int top_k, int hidden, int 
                           const int* expert_map, int num_local, const uint32_t* w13, const __half* suh13, const __half* svh13,
                           const uint32_t* w2, const __half* suh2, const __half* svh2, int K, int codebook, __half* yd, unsigned char* ws,
                           cudaStream_t st);
-// How launch_gemm_tc left its result for the output rotation: parts == 1: fp16 in `out`; parts > 1 and !tile_slabs: `parts` fp32
-// slabs [rows][n_total] (launch_had_out_sum); tile_slabs: fp16 in `out` for the 512 x 256 tiles before tail_first, `parts` fp32
-// slabs per tile for the others (launch_had_out_tiles; row_tiles = 512-row tiles per column tile).
+// How launch_gemm_tc left its result: !tile_slabs: parts == 1: fp16 in `out` in the rotated basis (launch_had_out), parts > 1:
+// `parts` fp32 slabs [rows][n_total] (launch_had_out_sum); tile_slabs (the CTA-pair tiling): the 512 x 256 tiles before
+// tail_first are final in y, the others are `parts` fp32 slabs per tile (launch_had_out_tiles; row_tiles = 512-row tiles per
+// column tile; nothing left to do when parts == 1).
 struct TcSplit {
     int parts, tile_slabs, tail_first, row_tiles;
 };
@@ -191,10 +192,10 @@ int gemm_tc_pairs();                        // CTA pairs of the pair tiling that
 size_t gemm_tc_part_bytes(int rows, int n_total);
 void gemm_tc_set_ksplit(int n);             // 0 = choose; n >= 1 = at most n parts of the reduction per tile
 int launch_gemm_tc(const void* x, int x_bf16, const __half* suh_cat, const uint32_t* packed, int K, int codebook, const int* shard_end_blocks,
-                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, TcSplit* split_out, int* err,
+                   int n_shards, int rows, int k, int n_total, __half* xa, __half* out, float* part, void* y, const __half* svh, int y_bf16, TcSplit* split_out, int* err,
                    cudaStream_t st);
-int launch_had_out_tiles(const __half* y, const float* part, int parts, int tail_first, int row_tiles, const __half* svh, int rows, int n,
-                         void* out, int out_bf16, cudaStream_t st);
+int launch_had_out_tiles(const float* part, int parts, int tail_first, int row_tiles, const __half* svh, int rows, int n, void* out,
+                         int out_bf16, cudaStream_t st);
 int launch_had_out_sum(const float* part, int parts, long long slab, const __half* svh, int rows, int n, void* out, int out_bf16,
                        cudaStream_t st);
 

@@ -258,50 +258,6 @@ __device__ __forceinline__ void store_out4(void* out, long long idx, const float
     }
 }
 
-// 32 consecutive halves (64 bytes, 16-byte aligned) as floats.
-__device__ __forceinline__ void load_half32(const __half* __restrict__ src, float (&v)[32])
-{
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
-            v[8 * i + 2 * j] = __low2float(h);
-            v[8 * i + 2 * j + 1] = __high2float(h);
-        }
-    }
-}
-
-// A lane's 32 rotated values -> out[at .. at + 31] = fp16(v * (scale * svh[col ..])), or that value converted to bf16: the
-// order of the fused epilogues.
-__device__ __forceinline__ void had_out_finish(const float (&v)[32], const __half* __restrict__ svh, int col, void* __restrict__ out, long long at,
-                                               int out_bf16)
-{
-    uint32_t packed[16];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint4 sraw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);       // ones
-        if (svh) sraw = reinterpret_cast<const uint4*>(svh + col)[i];
-        const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const __half2 sh = *reinterpret_cast<const __half2*>(&sw[j]);
-            const __half2 h = __floats2half2_rn(v[8 * i + 2 * j] * (HAD_SCALE * __low2float(sh)), v[8 * i + 2 * j + 1] * (HAD_SCALE * __high2float(sh)));
-            if (out_bf16) {
-                const __nv_bfloat162 bb = __floats2bfloat162_rn(__low2float(h), __high2float(h));
-                packed[4 * i + j] = *reinterpret_cast<const uint32_t*>(&bb);
-            } else {
-                packed[4 * i + j] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-        }
-    }
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + at);
-#pragma unroll
-    for (int i = 0; i < 4; i++) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-}
-
 // out[row, col0 + j] = Had128(y[row, :])[j] * svh[j].  y is fp16 (IN_F32 = false) or fp32 [rows, n].  One warp per (group of
 // HAD_OUT_ROWS rows, 128 columns), four lanes per row with 32 columns each (fwht128_quad).
 constexpr int HAD_OUT_ROWS = 8;
@@ -338,30 +294,26 @@ __global__ void had_out_kernel(const void* __restrict__ y, const __half* __restr
     if (live) had_out_finish(v, svh, col, out, (long long)row * out_stride + col, out_bf16);
 }
 
-// The output rotation behind the CTA-pair tiling of the many-row GEMM: tiles (512 rows x 256 columns; tile = column tile x
-// row_tiles + row tile) before `tail_first` are read as fp16 from y, the others as the sum of `parts` fp32 slabs
-// part[(tile - tail_first) * parts + s][512][256], added in part order and rounded to fp16 once, as the kernel rounds the
-// accumulators of a tile it did not cut.
-__global__ void had_out_tiles_kernel(const __half* __restrict__ y, const float* __restrict__ part, int parts, int tail_first, int row_tiles,
+// The output rotation for the cut tiles of the CTA-pair tiling of the many-row GEMM (tiles of 512 rows x 256 columns; tile =
+// column tile x row_tiles + row tile; the tiles before `tail_first` leave that kernel finished): the sum of `parts` fp32
+// slabs part[(tile - tail_first) * parts + s][512][256], added in part order and rounded to fp16 once, as the kernel rounds
+// the accumulators of a tile it did not cut.  One warp per (cut tile, 8 rows, 128 columns).
+__global__ void had_out_tiles_kernel(const float* __restrict__ part, int parts, int tail_first, int row_tiles, int cut_tiles,
                                      const __half* __restrict__ svh, int rows, int n, void* __restrict__ out, int out_bf16)
 {
     const int lane = threadIdx.x & 31;
-    const int nbs = n >> 7;
-    const int groups = (rows + HAD_OUT_ROWS - 1) / HAD_OUT_ROWS;
     long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (long long)groups * nbs) return;
-    const int nb = (int)(item % nbs);
-    const int row = (int)(item / nbs) * HAD_OUT_ROWS + (lane >> 2);
-    const int col = nb * 128 + 32 * (lane & 3);
+    if (item >= (long long)cut_tiles * 128) return;
+    const int j = (int)(item >> 7), rg = (int)(item & 127) >> 1, half = (int)(item & 1);
+    const int tile = tail_first + j;
+    const int row_in = rg * HAD_OUT_ROWS + (lane >> 2), row = (tile % row_tiles) * 512 + row_in;
+    const int col = (tile / row_tiles) * 256 + half * 128 + 32 * (lane & 3);
     const bool live = row < rows;
-    const int tile = (nb >> 1) * row_tiles + (row >> 9);          // the same for the 8 rows of the group
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = 0.f;
-    if (live && tile < tail_first) {
-        load_half32(y + (long long)row * n + col, v);
-    } else if (live) {
-        const float* src = part + (size_t)(tile - tail_first) * parts * (512 * 256) + (size_t)(row & 511) * 256 + (nb & 1) * 128 + 32 * (lane & 3);
+    if (live) {
+        const float* src = part + (size_t)j * parts * (512 * 256) + (size_t)row_in * 256 + half * 128 + 32 * (lane & 3);
         for (int s = 0; s < parts; s++, src += 512 * 256) {
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -497,12 +449,13 @@ int launch_had_out(const void* y, int y_f32, const __half* svh, int rows, int n,
     return cuda_status(cudaGetLastError());
 }
 
-int launch_had_out_tiles(const __half* y, const float* part, int parts, int tail_first, int row_tiles, const __half* svh, int rows, int n,
-                         void* out, int out_bf16, cudaStream_t st)
+int launch_had_out_tiles(const float* part, int parts, int tail_first, int row_tiles, const __half* svh, int rows, int n, void* out,
+                         int out_bf16, cudaStream_t st)
 {
-    long long items = (long long)((rows + HAD_OUT_ROWS - 1) / HAD_OUT_ROWS) * (n / 128);
-    if (items == 0) return EXL3_OK;
-    had_out_tiles_kernel<<<blocks_for(items, 8), 256, 0, st>>>(y, part, parts, tail_first, row_tiles, svh, rows, n, out, out_bf16);
+    const int cut_tiles = row_tiles * (n / 256) - tail_first;
+    if (cut_tiles <= 0) return EXL3_OK;
+    had_out_tiles_kernel<<<blocks_for((long long)cut_tiles * 128, 8), 256, 0, st>>>(part, parts, tail_first, row_tiles, cut_tiles, svh, rows, n, out,
+                                                                                  out_bf16);
     return cuda_status(cudaGetLastError());
 }
 
