@@ -399,7 +399,8 @@ struct TcPair {
     static constexpr int ROWS = 256 * M_TILES;
     static constexpr int STAGES = 3;
     static constexpr int DECODE_WARPS = 8;
-    static constexpr int THREADS = (DECODE_WARPS + 2) * 32;
+    static constexpr int EPILOGUE_WARPS = 8;                                 // two per quarter of the tensor-memory lanes
+    static constexpr int THREADS = (DECODE_WARPS + 2 + EPILOGUE_WARPS) * 32;
     static constexpr uint32_t A_STAGE_BYTES = TC_A_TILE_BYTES * M_TILES;    // this CTA's 128 rows of each MMA
     static constexpr uint32_t B_STAGE_BYTES = 128 * TC_KB * 2;              // this CTA's 128 columns
     static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -407,7 +408,7 @@ struct TcPair {
     // lanes' 16-byte stores fall on different banks.
     static constexpr uint32_t OUT_PITCH = 128 * 2 + 16;
     static constexpr uint32_t OUT_WARP_BYTES = 32 * OUT_PITCH;
-    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)DECODE_WARPS * OUT_WARP_BYTES;
+    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)EPILOGUE_WARPS * OUT_WARP_BYTES;
     static constexpr uint32_t B_LBO = (128 / 8) * 128;
     // fp16 x fp16 -> fp32, both operands K-major, N = 256, M = 256 over the pair
     static constexpr uint32_t IDESC = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
@@ -434,14 +435,15 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
 // remaining tile as p.ksplit parts of its reduction, so that the last wave of a tile count that does not divide by the
 // pairs is short: its parts store fp32 accumulators, slab [(tile - tail_first) * ksplit + part][512][256], which the output
 // rotation adds in part order.  Tile t = column tile t / row tiles, row tile t % row tiles.  Roles
-// per CTA: 8 decode + epilogue warps, an activation producer, and a warp whose first lane issues the MMAs of the pair (rank
-// 0) or reports this CTA's filled stages to rank 0 (rank 1).  Barriers sit at the same offsets in both CTAs; `empty` and
+// per CTA: 8 decode warps, an activation producer, a warp whose first lane issues the MMAs of the pair (rank 0) or reports
+// this CTA's filled stages to rank 0 (rank 1), and 8 epilogue warps, so that the decode of the next tile fills the stages
+// while a tile's accumulators are read out, rotated and sent.  Barriers sit at the same offsets in both CTAs; `empty` and
 // `acc_full` are signalled in both by the tensor core, `peer_full` and `acc_empty` of rank 0 by threads of rank 1.
 template <int K, int FAM>
 __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const GemmTcLaunch p)
 {
     using TT = TcPair;
-    constexpr int DW = TT::DECODE_WARPS, STAGES = TT::STAGES;
+    constexpr int DW = TT::DECODE_WARPS, EW = TT::EPILOGUE_WARPS, STAGES = TT::STAGES;
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* a_full = reinterpret_cast<uint64_t*>(smem);            // [stages]
     uint64_t* b_full = a_full + STAGES;
@@ -463,7 +465,7 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(acc_full, 1);
-        ptx::mbar_init(acc_empty, 2 * DW);
+        ptx::mbar_init(acc_empty, 2 * EW);
         ptx::mbar_fence_init();
     }
     if (warp == DW + 1) {
@@ -496,10 +498,10 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
     };
 
     if (warp < DW) {
-        // ------------------------------------------------------------------ decode + epilogue
+        // ------------------------------------------------------------------ decode
         const int nt = warp;
         const CodebookConst cbc = {p.mul, p.add};
-        uint32_t it = 0, acc_round = 0;
+        uint32_t it = 0;
         auto block_of = [&](long long t) { return (int)(tile_of(t) / MT) * 2 + (int)rank; };
         auto words_ptr = [&](int nb_, int kb) {
             return p.packed + (((((long long)nb_ * p.KG + (kb >> 1)) * 8 + nt) * 2 + (kb & 1)) * K) * 32 + lane;
@@ -511,8 +513,6 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
             for (int i = 0; i < K; i++) Lnext[i] = __ldg(src + i * 32);
         }
         for (long long t = first; t < n_tiles; t += step) {
-            const long long tile = tile_of(t);
-            const int ms = (int)(tile % MT), ct = (int)(tile / MT);
             const int kb0 = kb_begin(t), kb1 = kb_end(t);
             const long long t_next = t + step;
             const int nb_cur = block_of(t), nb_next = t_next < n_tiles ? block_of(t_next) : 0;
@@ -537,15 +537,47 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&b_full[s]);
             }
-            // ---- epilogue: this CTA's 128 rows of both MMAs.  A warp reads the 32 tensor-memory lanes of its quarter and
-            // 128 of the tile's 256 columns; a lane rounds its row to fp16 into the warp's staging slice, the warp applies the
-            // output rotation and the svh vector there, and every lane sends its row's 256 bytes to y as one bulk copy, which
-            // completes behind the next tile's MMAs.  Tensor memory is handed back
-            // as soon as it has been read.  Parts of a cut tile store their fp32 accumulators directly.
+        }
+    } else if (warp == DW) {
+        // ------------------------------------------------------------------ activation producer: rows 128 rank .. + 127 of each MMA
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (long long t = first; t < n_tiles; t += step) {
+                const int ms = (int)(tile_of(t) % MT), nb = (int)(tile_of(t) / MT) * 2;
+                const int kb0 = kb_begin(t), kb1 = kb_end(t);
+                int shard = 0;
+                while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
+                    ptx::mbar_arrive_expect_tx(&a_full[s], TT::A_STAGE_BYTES);
+                    for (int mt = 0; mt < TT::M_TILES; mt++) {
+                        // 128-row tile 2 mt + rank of the 512-row super tile ms
+                        const __half* src = p.xa + shard * p.xa_shard_stride + (((long long)ms * KB + kb) * 4 + 2 * mt + (int)rank) * (TC_A_TILE_BYTES / 2);
+                        ptx::bulk_g2s(stage0 + (size_t)s * TT::STAGE_BYTES + (size_t)mt * TC_A_TILE_BYTES, src, TC_A_TILE_BYTES, &a_full[s]);
+                    }
+                }
+            }
+            // The tensor core's last arrivals on `empty` land in this CTA's shared memory: seen before the CTA may leave.
+            for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++)
+                if (!failed && !ptx::mbar_wait_relaxed(&empty[j % STAGES], (j / STAGES) & 1)) fail();
+        }
+    } else if (warp >= DW + 2) {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp & 3, cgroup = (warp - (DW + 2)) >> 2;
+        unsigned char* slice = out_stage + (size_t)(warp - (DW + 2)) * TT::OUT_WARP_BYTES;
+        unsigned char* my_row = slice + (size_t)lane * TT::OUT_PITCH;
+        uint32_t acc_round = 0;
+        for (long long t = first; t < n_tiles; t += step) {
+            const long long tile = tile_of(t);
+            const int ms = (int)(tile % MT), ct = (int)(tile / MT);
+            // This CTA's 128 rows of both MMAs.  A warp reads the 32 tensor-memory lanes of its quarter and 128 of the tile's
+            // 256 columns; a lane rounds its row to fp16 into the warp's staging slice, the warp applies the output rotation
+            // and the svh vector there, and every lane sends its row's 256 bytes to y as one bulk copy.  Tensor memory is
+            // handed back as soon as it has been read.  Parts of a cut tile store their fp32 accumulators directly.
             if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
             tc_fence_after();
-            const int quarter = warp & 3, cgroup = warp >> 2;
-            unsigned char* my_row = out_stage + (size_t)warp * TT::OUT_WARP_BYTES + (size_t)lane * TT::OUT_PITCH;
 #pragma unroll 1
             for (int mt = 0; mt < TT::M_TILES; mt++) {
                 const int row_in = mt * 256 + (int)rank * 128 + quarter * 32 + lane, row = ms * TT::ROWS + row_in;
@@ -593,7 +625,7 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
                     __syncwarp();
 #pragma unroll 1
                     for (int pass = 0; pass < 4; pass++) {
-                        __half* at = reinterpret_cast<__half*>(out_stage + (size_t)warp * TT::OUT_WARP_BYTES + (size_t)(pass * 8 + (lane >> 2)) * TT::OUT_PITCH) +
+                        __half* at = reinterpret_cast<__half*>(slice + (size_t)(pass * 8 + (lane >> 2)) * TT::OUT_PITCH) +
                                      32 * (lane & 3);
                         float v[32];
                         load_half32(at, v);
@@ -611,31 +643,6 @@ __global__ void __launch_bounds__(TcPair::THREADS, 1) gemm_tc_pair_kernel(const 
             acc_round++;
         }
         ptx::bulk_wait_all();                           // the lane's output copies have completed
-    } else if (warp == DW) {
-        // ------------------------------------------------------------------ activation producer: rows 128 rank .. + 127 of each MMA
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (long long t = first; t < n_tiles; t += step) {
-                const int ms = (int)(tile_of(t) % MT), nb = (int)(tile_of(t) / MT) * 2;
-                const int kb0 = kb_begin(t), kb1 = kb_end(t);
-                int shard = 0;
-                while (shard < p.n_shards - 1 && nb >= p.shard_end_block[shard]) shard++;
-                for (int kb = kb0; kb < kb1; kb++, it++) {
-                    const int s = it % STAGES;
-                    const uint32_t round = it / STAGES;
-                    if (round > 0 && !failed && !ptx::mbar_wait_relaxed(&empty[s], (round - 1) & 1)) fail();
-                    ptx::mbar_arrive_expect_tx(&a_full[s], TT::A_STAGE_BYTES);
-                    for (int mt = 0; mt < TT::M_TILES; mt++) {
-                        // 128-row tile 2 mt + rank of the 512-row super tile ms
-                        const __half* src = p.xa + shard * p.xa_shard_stride + (((long long)ms * KB + kb) * 4 + 2 * mt + (int)rank) * (TC_A_TILE_BYTES / 2);
-                        ptx::bulk_g2s(stage0 + (size_t)s * TT::STAGE_BYTES + (size_t)mt * TC_A_TILE_BYTES, src, TC_A_TILE_BYTES, &a_full[s]);
-                    }
-                }
-            }
-            // The tensor core's last arrivals on `empty` land in this CTA's shared memory: seen before the CTA may leave.
-            for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++)
-                if (!failed && !ptx::mbar_wait_relaxed(&empty[j % STAGES], (j / STAGES) & 1)) fail();
-        }
     } else if (lane == 0) {
         uint32_t it = 0, acc_round = 0;
         if (rank == 0) {
