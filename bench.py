@@ -229,7 +229,8 @@ def run_prefill(args) -> None:
                                  "rows": rows, "l2": "weights 165 MB per layer, larger than L2"},
                       "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
                                    "peak_source": "of measured (burst)", "kernel": "gemm_tc_pair_kernel"},
-                      "gpu_launches": 16 * args.steps, "clocks": clocks.summary()}))
+                      # per layer: 4 input rotations, 4 GEMMs, 3 rotations of cut tiles (q|k|v has none on 74 CTA pairs)
+                      "gpu_launches": 11 * args.steps, "clocks": clocks.summary()}))
 
 
 def run_moe(args) -> None:
