@@ -92,3 +92,26 @@ def test_pair_tiling_with_a_cut_last_wave_matches_the_narrow_tiling(k, n, rows, 
     err = (got - ref).norm() / ref.norm()
     assert err <= 1e-3, float(err)
     assert float((got - ref).abs().max() / ref.pow(2).mean().sqrt()) <= 4e-3
+
+
+@pytest.mark.parametrize("k,n,rows,K,cb,shards", [(640, 768, 777, 4, 1, 1), (1152, 1280, 1500, 2, 0, 1), (2048, 512, 2049, 5, 2, 1),
+                                                  (1024, 1024, 1025, 8, 1, 2), (896, 19200, 1111, 3, 0, 2), (5120, 4352, 700, 7, 2, 2)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_pair_tiling_without_a_cut_has_the_bits_of_the_narrow_tiling(k, n, rows, K, cb, shards, dtype):
+    """The pair kernel rotates inside its epilogue; with no tile cut it adds the same products in the same order as the narrow
+    kernel followed by the rotation kernel, so ragged rows, shard groups, every family and both output types agree exactly."""
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(k + n + rows)
+    w = random_packed(k, n, K, gen, torch.device(DEV))
+    suh, svh = random_signs(k, gen, torch.device(DEV), shards), random_signs(n, gen, torch.device(DEV)).view(-1)
+    ends = [] if shards == 1 else [n // 2]
+    x = torch.randn((rows, k), device=DEV, generator=gen).to(dtype)
+    lin.set_tc_ksplit(1)
+    lin.set_tc_tiling(0)
+    ref = lin.run_tc(x, w, suh, svh, ends, cb)
+    lin.set_tc_tiling(3)
+    got = lin.run_tc(x, w, suh, svh, ends, cb)
+    torch.cuda.synchronize()
+    lin.device_error(torch.device(DEV))
+    assert got.dtype == dtype and torch.equal(got, ref)

@@ -132,36 +132,13 @@ int launch_decode_attention(const void* qkv, int bf16, int rows, int q_heads, in
 // columns four 128-row tiles of 16 KB, each in 8 x 8 fp16 core matrices (k chunk of 8 outermost, then row group of 8).
 constexpr int TC_ROWS = 512;
 constexpr int TC_KB = 64;
-// Element offset of (row, col) for a matrix of KB reduction blocks; col is a multiple of 4, the 4 halves are contiguous.
+// Element offset of (row, col) for a matrix of KB reduction blocks; the halves of an aligned group of 8 columns are contiguous.
 __host__ __device__ inline long long tc_a_offset(int row, int col, int KB)
 {
     const int kb = col >> 6, c = (col & 63) >> 3, e0 = col & 7;
     const int ms = row / TC_ROWS, mt = (row % TC_ROWS) >> 7, j = (row & 127) >> 3, rr = row & 7;
     return ((((((long long)ms * KB + kb) * 4 + mt) * 8 + c) * 16 + j) * 8 + rr) * 8 + e0;
 }
-#ifdef __CUDACC__
-// Rows r and r + 1 of a row group, four columns per lane each, to the A layout as whole 16-byte core-matrix rows: the even lane
-// of a pair takes the eight columns of row r, the odd lane those of row r + 1 (two shuffles), so a warp store covers full
-// 32-byte sectors instead of halves.
-__device__ __forceinline__ void store_a_pair(__half* xa, int p_even, int col, int KB, int lane, const float (&va)[4], const float (&vb)[4])
-{
-    __half ha[4], hb[4];
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-        ha[e] = __float2half_rn(va[e]);
-        hb[e] = __float2half_rn(vb[e]);
-    }
-    const uint2 a = *reinterpret_cast<uint2*>(ha), b = *reinterpret_cast<uint2*>(hb);
-    const bool odd = lane & 1;
-    const uint2 send = odd ? a : b;
-    uint2 recv;
-    recv.x = __shfl_xor_sync(0xFFFFFFFFu, send.x, 1);
-    recv.y = __shfl_xor_sync(0xFFFFFFFFu, send.y, 1);
-    const uint4 out = odd ? make_uint4(recv.x, recv.y, b.x, b.y) : make_uint4(a.x, a.y, recv.x, recv.y);
-    *reinterpret_cast<uint4*>(xa + tc_a_offset(p_even + (odd ? 1 : 0), col & ~7, KB)) = out;
-}
-
-#endif
 
 // The grouped instances: the wide tiling where column blocks pair up inside every shard -- 16 decode warps on a 64 x 256 weight
 // block per step (routed experts have few rows each, so the decode bounds the kernel and needs the warps), items of up to

@@ -66,22 +66,7 @@ __global__ void moe_tc_items_kernel(const int* __restrict__ expert_ids, const in
 
 constexpr int MOE_TC_GROUP = 8;           // positions per warp: one row group of the A layout, four lanes per position (fwht128_quad)
 
-// 32 consecutive halves (64 bytes, 16-byte aligned) as floats, and back.
-__device__ __forceinline__ void load_h32(const __half* __restrict__ src, float (&v)[32])
-{
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
-            v[8 * i + 2 * j] = __low2float(h);
-            v[8 * i + 2 * j + 1] = __high2float(h);
-        }
-    }
-}
-
+// Eight floats rounded to halves, as one 16-byte word.
 __device__ __forceinline__ uint4 pack_h8(const float* v)
 {
     uint32_t o[4];
@@ -124,7 +109,7 @@ __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, con
     float v[32];
     if (slot >= 0 && slot < numel) {
         float sg[32];
-        load_h32(suh + ((long long)ex * shards + s) * hidden + col, sg);
+        load_half32(suh + ((long long)ex * shards + s) * hidden + col, sg);
         const long long at = (long long)(slot / top_k) * hidden + col;
         if (x_bf16) {
 #pragma unroll
@@ -139,7 +124,7 @@ __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, con
                 }
             }
         } else {
-            load_h32(reinterpret_cast<const __half*>(x) + at, v);
+            load_half32(reinterpret_cast<const __half*>(x) + at, v);
         }
 #pragma unroll
         for (int i = 0; i < 32; i++) v[i] *= sg[i];
@@ -157,7 +142,7 @@ __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, con
 __device__ __forceinline__ void unrotate32(float (&v)[32], const __half* __restrict__ svh, int lane)
 {
     float sv[32];
-    load_h32(svh, sv);
+    load_half32(svh, sv);
     fwht128_quad(v, lane);
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __half2float(__float2half_rn(v[i] * (HAD_SCALE * sv[i])));
@@ -184,12 +169,12 @@ __global__ void moe_tc_mid_kernel(const __half* __restrict__ gu_rot, const __hal
     const int slot = sorted_ids[p];
     const bool valid = slot >= 0 && slot < numel;
     float g[32], u[32];
-    load_h32(gu_rot + (long long)p * 2 * inter + col, g);
-    load_h32(gu_rot + (long long)p * 2 * inter + inter + col, u);
+    load_half32(gu_rot + (long long)p * 2 * inter + col, g);
+    load_half32(gu_rot + (long long)p * 2 * inter + inter + col, u);
     unrotate32(g, svh13 + (long long)ex * 2 * inter + col, lane);
     unrotate32(u, svh13 + (long long)ex * 2 * inter + inter + col, lane);
     float s2[32];
-    load_h32(suh2 + (long long)ex * inter + col, s2);
+    load_half32(suh2 + (long long)ex * inter + col, s2);
 #pragma unroll
     for (int i = 0; i < 32; i++) {
         const float act = __half2float(__float2half_rn(g[i] / (1.0f + __expf(-g[i])) * u[i]));
@@ -221,7 +206,7 @@ __global__ void moe_tc_out_kernel(const __half* __restrict__ yd_rot, const __hal
     const int col = nb * 128 + 32 * (lane & 3);
     const int slot = sorted_ids[p];
     float v[32];
-    load_h32(yd_rot + (long long)p * hidden + col, v);
+    load_half32(yd_rot + (long long)p * hidden + col, v);
     unrotate32(v, svh2 + (long long)ex * hidden + col, lane);
     if (slot >= 0 && slot < numel) {
         uint4* dst = reinterpret_cast<uint4*>(yd + (long long)slot * hidden + col);
