@@ -1026,9 +1026,10 @@ static int launch_tc_grouped_k(const GemmTcLaunch& l, int fam, bool wide, int sm
 
 // Routed experts with many rows each: out[position, :] = xa[position, :] @ W_inner[expert of the position's block], for
 // the work items of `items` (see GemmTcLaunch).  xa is in the A-operand layout over positions (blocks of 128 rows of one
-// expert, padding rows zero), `cap512` positions per shard; out is [cap][n_total] fp16 in the rotated basis.  wide: the
-// 256-column tiling with 16 decode warps and items of at most TC_GROUPED_MT blocks (column blocks must pair up inside every
-// shard); otherwise 128-column tiles and items of at most 4 blocks.
+// expert; padding rows may hold anything, a product row depends on its own row only), `cap512` positions per shard; out is
+// [cap][n_total] fp16 in the rotated basis.  wide: the 256-column tiling with 16 decode warps and items of at most
+// TC_GROUPED_MT blocks (column blocks must pair up inside every shard); otherwise 128-column tiles and items of at most 4
+// blocks.
 int launch_gemm_tc_grouped(const uint32_t* packed, long long expert_stride, int K, int codebook, const int* shard_end_blocks, int n_shards,
                            int k, int n_total, const __half* xa, int cap512, __half* out, const int4* items, const int* n_items, bool wide,
                            int* err, cudaStream_t st)

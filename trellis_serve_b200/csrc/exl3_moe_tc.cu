@@ -85,9 +85,9 @@ __device__ __forceinline__ void store_a32(__half* xa, int p, int col, int KB, co
     for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(xa + tc_a_offset(p, col + 8 * i, KB)) = pack_h8(&v[8 * i]);
 }
 
-// xa[shard][position p] = Had128(fp16(x[token(p)]) * suh[expert(p), shard]) in the A-operand layout; zero rows for padding.
-// One warp per (shard, group of 8 positions, 128-block).  Positions at or beyond num_post are left untouched (no work item
-// reads them).
+// xa[shard][position p] = Had128(fp16(x[token(p)]) * suh[expert(p), shard]) in the A-operand layout.  One warp per (shard,
+// group of 8 positions, 128-block).  Padding positions are left as they are: a row of the product depends on its own row of
+// A only, and nothing downstream uses the rows of padding positions.
 __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, const __half* __restrict__ suh, int shards, int hidden,
                                      int top_k, int numel, int cap, const int* __restrict__ sorted_ids, const int* __restrict__ expert_ids,
                                      const int* __restrict__ num_post, __half* __restrict__ xa, long long shard_stride)
@@ -106,8 +106,10 @@ __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, con
     const int ex = expert_ids[p0 / MOE_TC_BLOCK_ROWS];
     const int col = kg * 128 + 32 * (lane & 3);
     const int slot = sorted_ids[p];
+    const bool valid = slot >= 0 && slot < numel;
+    if (__ballot_sync(0xFFFFFFFFu, valid) == 0) return;       // a group of padding rows: nothing reads what the GEMM makes of them
     float v[32];
-    if (slot >= 0 && slot < numel) {
+    if (valid) {
         float sg[32];
         load_half32(suh + ((long long)ex * shards + s) * hidden + col, sg);
         const long long at = (long long)(slot / top_k) * hidden + col;
@@ -135,7 +137,7 @@ __global__ void moe_tc_had_in_kernel(const void* __restrict__ x, int x_bf16, con
     fwht128_quad(v, lane);
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] *= HAD_SCALE;
-    store_a32(xa + s * shard_stride, p, col, kgs * 2, v);
+    if (valid) store_a32(xa + s * shard_stride, p, col, kgs * 2, v);
 }
 
 // 32 columns of a rotated-basis row back in the true basis: Had128(y) * svh, rounded to fp16 like the GEMV's output.
@@ -168,9 +170,14 @@ __global__ void moe_tc_mid_kernel(const __half* __restrict__ gu_rot, const __hal
     const int col = kg * 128 + 32 * (lane & 3);
     const int slot = sorted_ids[p];
     const bool valid = slot >= 0 && slot < numel;
+    if (__ballot_sync(0xFFFFFFFFu, valid) == 0) return;       // a group of padding rows
     float g[32], u[32];
-    load_half32(gu_rot + (long long)p * 2 * inter + col, g);
-    load_half32(gu_rot + (long long)p * 2 * inter + inter + col, u);
+#pragma unroll
+    for (int i = 0; i < 32; i++) g[i] = u[i] = 0.f;
+    if (valid) {
+        load_half32(gu_rot + (long long)p * 2 * inter + col, g);
+        load_half32(gu_rot + (long long)p * 2 * inter + inter + col, u);
+    }
     unrotate32(g, svh13 + (long long)ex * 2 * inter + col, lane);
     unrotate32(u, svh13 + (long long)ex * 2 * inter + inter + col, lane);
     float s2[32];
@@ -183,7 +190,7 @@ __global__ void moe_tc_mid_kernel(const __half* __restrict__ gu_rot, const __hal
     fwht128_quad(g, lane);
 #pragma unroll
     for (int i = 0; i < 32; i++) g[i] *= HAD_SCALE;
-    store_a32(xa2, p, col, kgs * 2, g);
+    if (valid) store_a32(xa2, p, col, kgs * 2, g);
 }
 
 // yd[slot(p), :] = fp16( Had128(yd_rot[p]) * svh2[expert] ) for the valid positions.  One warp per (group of 8 positions,
@@ -205,10 +212,14 @@ __global__ void moe_tc_out_kernel(const __half* __restrict__ yd_rot, const __hal
     const int ex = expert_ids[p0 / MOE_TC_BLOCK_ROWS];
     const int col = nb * 128 + 32 * (lane & 3);
     const int slot = sorted_ids[p];
+    const bool valid = slot >= 0 && slot < numel;
+    if (__ballot_sync(0xFFFFFFFFu, valid) == 0) return;       // a group of padding rows
     float v[32];
-    load_half32(yd_rot + (long long)p * hidden + col, v);
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = 0.f;
+    if (valid) load_half32(yd_rot + (long long)p * hidden + col, v);
     unrotate32(v, svh2 + (long long)ex * hidden + col, lane);
-    if (slot >= 0 && slot < numel) {
+    if (valid) {
         uint4* dst = reinterpret_cast<uint4*>(yd + (long long)slot * hidden + col);
 #pragma unroll
         for (int i = 0; i < 4; i++) dst[i] = pack_h8(&v[8 * i]);
