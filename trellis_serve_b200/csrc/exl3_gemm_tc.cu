@@ -50,6 +50,7 @@ struct TcTile {
 };
 
 enum { TC_ERR_WAIT = 3 };
+constexpr int TC_GROUPED_EPILOGUE_WARPS = 4;       // the grouped instances read their tiles out on warps of their own
 
 struct GemmTcLaunch {
     const uint32_t* packed;      // resident weights [NB][KG][8][2][K][32]
@@ -161,7 +162,7 @@ __device__ __forceinline__ void tc_decode_block(const uint32_t (&L)[K], unsigned
 // SPLIT: the reduction of a tile may be cut into p.ksplit parts (work items); without it the part count is the constant 1
 // and the index arithmetic of the unsplit kernel folds away.
 template <int K, int FAM, int MT_, bool WIDE, bool SPLIT, bool GROUPED = false>
-__global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(const GemmTcLaunch p)
+__global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS + (GROUPED ? TC_GROUPED_EPILOGUE_WARPS * 32 : 0), 1) gemm_tc_kernel(const GemmTcLaunch p)
 {
     static_assert(!GROUPED || !SPLIT, "grouped work items carry whole reductions");
     using TT = TcTile<MT_, WIDE>;
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(acc_full, 1);
-        ptx::mbar_init(acc_empty, DW);
+        ptx::mbar_init(acc_empty, GROUPED ? TC_GROUPED_EPILOGUE_WARPS : DW);
         ptx::mbar_fence_init();
     }
     if (warp == DW + 1) {
@@ -210,6 +211,50 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
             failed = true;
             atomicExch(p.err, TC_ERR_WAIT);
         }
+    };
+
+    // Accumulators of a finished tile -> fp16 rows (or fp32 slabs of a split reduction).  `eq` = which of `ew` epilogue warps
+    // this is: column group eq / 4 of ew / 4; a warp can only read the quarter warp % 4 of the tensor-memory lanes.
+    auto epilogue = [&](int eq, int ew, int row0, int ct, int sp, int present, uint32_t acc_round) {
+        const int cgroups = ew >> 2, ccols = TT::NCOLS / cgroups;
+        if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
+        tc_fence_after();
+        const int quarter = warp & 3, cgroup = eq >> 2;
+#pragma unroll 1
+        for (int mt = 0; mt < present; mt++) {
+            const int row = row0 + mt * 128 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < ccols / 32; cc++) {
+                const int col = cgroup * ccols + cc * 32;
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * TT::NCOLS + col), r);
+                if (row < p.rows && KS > 1) {
+                    // part of a split reduction: fp32 accumulators into this part's slab; the output rotation adds the slabs
+                    float* dst = p.part + (size_t)sp * p.part_slab + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
+#pragma unroll
+                    for (int v = 0; v < 32; v += 4)
+                        *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
+                } else if (GROUPED || row < p.rows) {
+                    __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
+#pragma unroll
+                    for (int v = 0; v < 32; v += 8) {
+                        uint4 o;
+                        __half2 h0 = __floats2half2_rn(__uint_as_float(r[v]), __uint_as_float(r[v + 1]));
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(r[v + 2]), __uint_as_float(r[v + 3]));
+                        __half2 h2 = __floats2half2_rn(__uint_as_float(r[v + 4]), __uint_as_float(r[v + 5]));
+                        __half2 h3 = __floats2half2_rn(__uint_as_float(r[v + 6]), __uint_as_float(r[v + 7]));
+                        o.x = *reinterpret_cast<uint32_t*>(&h0);
+                        o.y = *reinterpret_cast<uint32_t*>(&h1);
+                        o.z = *reinterpret_cast<uint32_t*>(&h2);
+                        o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(dst + v) = o;
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty);
     };
 
     if (warp < DW) {
@@ -273,46 +318,9 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&b_full[s]);
             }
-            // ---- epilogue of this tile: accumulators -> fp16 rows.  A warp reads the 32 tensor-memory lanes of its
-            // quarter (warp % 4) and 64 of the tile's columns.
-            if (!failed && !ptx::mbar_wait(acc_full, acc_round & 1)) fail();
-            tc_fence_after();
-            const int quarter = warp & 3, cgroup = warp >> 2;
-#pragma unroll 1
-            for (int mt = 0; mt < present; mt++) {
-                const int row = row0 + mt * 128 + quarter * 32 + lane;
-#pragma unroll 1
-                for (int cc = 0; cc < 2; cc++) {
-                    const int col = cgroup * 64 + cc * 32;
-                    uint32_t r[32];
-                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * TT::NCOLS + col), r);
-                    if (row < p.rows && KS > 1) {
-                        // part of a split reduction: fp32 accumulators into this part's slab; the output rotation adds the slabs
-                        float* dst = p.part + (size_t)sp * p.part_slab + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
-#pragma unroll
-                        for (int v = 0; v < 32; v += 4)
-                            *reinterpret_cast<uint4*>(dst + v) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
-                    } else if (GROUPED || row < p.rows) {
-                        __half* dst = p.out + (size_t)row * p.n_total + (size_t)ct * TT::NCOLS + col;
-#pragma unroll
-                        for (int v = 0; v < 32; v += 8) {
-                            uint4 o;
-                            __half2 h0 = __floats2half2_rn(__uint_as_float(r[v]), __uint_as_float(r[v + 1]));
-                            __half2 h1 = __floats2half2_rn(__uint_as_float(r[v + 2]), __uint_as_float(r[v + 3]));
-                            __half2 h2 = __floats2half2_rn(__uint_as_float(r[v + 4]), __uint_as_float(r[v + 5]));
-                            __half2 h3 = __floats2half2_rn(__uint_as_float(r[v + 6]), __uint_as_float(r[v + 7]));
-                            o.x = *reinterpret_cast<uint32_t*>(&h0);
-                            o.y = *reinterpret_cast<uint32_t*>(&h1);
-                            o.z = *reinterpret_cast<uint32_t*>(&h2);
-                            o.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(dst + v) = o;
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(acc_empty);
+            // Dense: the decode warps read out the tile themselves (each the 32 tensor-memory lanes of its quarter and 64 of
+            // the tile's columns).  Grouped: warps of their own do, and these go on to the next item's weights.
+            if constexpr (!GROUPED) epilogue(warp, DW, row0, ct, sp, present, acc_round);
             acc_round++;
         }
     } else if (warp == DW) {
@@ -348,7 +356,16 @@ __global__ void __launch_bounds__(TcTile<MT_, WIDE>::THREADS, 1) gemm_tc_kernel(
                 }
             }
         }
-    } else {
+    } else if (GROUPED && warp >= DW + 2) {
+        // ------------------------------------------------------------------ epilogue warps of the grouped instances: routed
+        // experts' tiles are short (8 reduction blocks in a down projection), so reading a tile out while the next one
+        // is being decoded matters
+        uint32_t acc_round = 0;
+        for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x, acc_round++) {
+            const int4 item = p.items[t / NT];
+            epilogue(warp - (DW + 2), TC_GROUPED_EPILOGUE_WARPS, item.y * 128, (int)(t % NT), 0, item.z, acc_round);
+        }
+    } else if (warp == DW + 1) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             uint32_t it = 0, acc_round = 0;
@@ -1014,13 +1031,13 @@ static int launch_tc_grouped_k(const GemmTcLaunch& l, int fam, bool wide, int sm
 {
     if (!wide) {
         using TN = TcTile<4, false>;
-        if (fam == FAM_HASH) gemm_tc_kernel<K, FAM_HASH, 4, false, false, true><<<sm_count, TN::THREADS, TN::SMEM_BYTES, st>>>(l);
-        else gemm_tc_kernel<K, FAM_MUL1, 4, false, false, true><<<sm_count, TN::THREADS, TN::SMEM_BYTES, st>>>(l);
+        if (fam == FAM_HASH) gemm_tc_kernel<K, FAM_HASH, 4, false, false, true><<<sm_count, TN::THREADS + TC_GROUPED_EPILOGUE_WARPS * 32, TN::SMEM_BYTES, st>>>(l);
+        else gemm_tc_kernel<K, FAM_MUL1, 4, false, false, true><<<sm_count, TN::THREADS + TC_GROUPED_EPILOGUE_WARPS * 32, TN::SMEM_BYTES, st>>>(l);
         return cuda_status(cudaGetLastError());
     }
     using TT = TcTile<TC_GROUPED_MT, true>;
-    if (fam == FAM_HASH) gemm_tc_kernel<K, FAM_HASH, TC_GROUPED_MT, true, false, true><<<sm_count, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
-    else gemm_tc_kernel<K, FAM_MUL1, TC_GROUPED_MT, true, false, true><<<sm_count, TT::THREADS, TT::SMEM_BYTES, st>>>(l);
+    if (fam == FAM_HASH) gemm_tc_kernel<K, FAM_HASH, TC_GROUPED_MT, true, false, true><<<sm_count, TT::THREADS + TC_GROUPED_EPILOGUE_WARPS * 32, TT::SMEM_BYTES, st>>>(l);
+    else gemm_tc_kernel<K, FAM_MUL1, TC_GROUPED_MT, true, false, true><<<sm_count, TT::THREADS + TC_GROUPED_EPILOGUE_WARPS * 32, TT::SMEM_BYTES, st>>>(l);
     return cuda_status(cudaGetLastError());
 }
 

@@ -144,7 +144,6 @@ __global__ void __launch_bounds__(MOE_THREADS, MOE_CTAS_PER_SM) moe_gemm_kernel(
     const int nt = warp & 7, kq = warp >> 3;
     const int g = lane >> 2, q = lane & 3;
     const CodebookConst cbc = {p.mul, p.add};
-    const int KT = p.KG * 8;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t stage0_addr = ptx::smem_addr(stage0);
     const uint32_t w_off = (uint32_t)((nt * 2 + kq) * K) * 128u + lane * 4u;
