@@ -204,9 +204,11 @@ exl3_status exl3_rope_decode_attention(const void *qkv, int dtype, int rows, int
 /* ---- fused linear for many rows (prefill) on the tcgen05 tensor cores -----------------------------------
  * Same contract as exl3_linear (fused group, dtypes, shard ends); built for hundreds to thousands of rows: the
  * weights are decoded once per 512 rows straight into the shared-memory operand of tcgen05.mma, accumulators live in
- * tensor memory.  The reference has no fused many-row kernel; this replaces its decode + library GEMM sequence
- * `dense_group` (cuda/src/sglang_exl3/runtime/ops.py:36-59).  The workspace (exl3_gemm_tc_workspace_bytes) holds the
- * rotated activations and the rotated-basis product; its first 256 bytes must be zero (error word). */
+ * tensor memory; above 256 rows two CTAs of a cluster share a 512 x 256 tile (cta_group::2) and apply the output
+ * rotation and svh inside their epilogue.  The reference has no fused many-row kernel; this replaces its decode +
+ * library GEMM sequence `dense_group` (cuda/src/sglang_exl3/runtime/ops.py:36-59).  The workspace
+ * (exl3_gemm_tc_workspace_bytes) holds the rotated activations, the rotated-basis product and the fp32 slabs of cut
+ * reductions; its first 256 bytes must be zero (error word).  x, suh_cat, svh_cat and y must be 16-byte aligned. */
 size_t exl3_gemm_tc_workspace_bytes(int rows, int k, int n_total, int n_shards);
 exl3_status exl3_linear_tc(const void *x, int x_dtype, const uint32_t *packed, int K, int codebook, const uint16_t *suh_cat,
                            const uint16_t *svh_cat, const int *shard_ends, int n_shards, int rows, int k, int n_total, void *y,
