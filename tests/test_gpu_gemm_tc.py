@@ -115,3 +115,31 @@ def test_pair_tiling_without_a_cut_has_the_bits_of_the_narrow_tiling(k, n, rows,
     torch.cuda.synchronize()
     lin.device_error(torch.device(DEV))
     assert got.dtype == dtype and torch.equal(got, ref)
+
+
+def test_pair_tiling_replays_from_a_cuda_graph_with_fresh_input():
+    """Cluster launches, the cut last wave and its rotation launch inside one captured graph; replay on new activations."""
+    from trellis_serve_b200.runtime.layerset import random_packed, random_signs
+    k, n, rows, K, cb = 1024, 10240, 1024, 3, 0
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(99)
+    w = random_packed(k, n, K, gen, torch.device(DEV))
+    suh, svh = random_signs(k, gen, torch.device(DEV), 1), random_signs(n, gen, torch.device(DEV)).view(-1)
+    x = torch.randn((rows, k), device=DEV, generator=gen).half()
+    out = torch.empty((rows, n), dtype=torch.float16, device=DEV)
+    lin.set_tc_tiling(3)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        lin.run_tc(x, w, suh, svh, [], cb, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        lin.run_tc(x, w, suh, svh, [], cb, out=out)
+    x2 = torch.randn((rows, k), device=DEV, generator=gen).half()
+    eager = lin.run_tc(x2, w, suh, svh, [], cb).clone()
+    x.copy_(x2)
+    g.replay()
+    torch.cuda.synchronize()
+    lin.device_error(torch.device(DEV))
+    assert torch.equal(out, eager)
