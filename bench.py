@@ -227,7 +227,11 @@ def run_prefill(args) -> None:
                       "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                       "config": {"workload": f"one 27B-shape layer (qkv, o, gate_up, down), {rows} rows, K=4 MCG, fused tcgen05 GEMM",
                                  "rows": rows, "l2": "weights 165 MB per layer, larger than L2"},
-                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                                   # DRAM bytes of the largest launch (gate|up at 2048 rows) from one ncu capture
+                                   "traffic": 264.6e6 if rows == 2048 else None,
+                                   "traffic_unit": "bytes of the gate|up launch, one ncu capture",
+                                   "traffic_source": "profiles/gemm_tc_pair_kernel_27b_prefill_m2048_k4.md",
                                    "peak_source": "of measured (burst)", "kernel": "gemm_tc_pair_kernel"},
                       # per layer: 4 input rotations, 4 GEMMs, 3 rotations of cut tiles (q|k|v has none on 74 CTA pairs)
                       "gpu_launches": 11 * args.steps, "clocks": clocks.summary()}))
