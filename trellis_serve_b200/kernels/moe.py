@@ -26,7 +26,7 @@ from .linear import _dtype_code, _ptr, _require_cuda, _stream, prepare_matrix
 BLOCK_SIZES = (8, 128)
 # Average routed rows per expert from which a class goes through the grouped tensor-core GEMM (128-row blocks, every
 # expert decoded once per up to 512 rows) instead of the grouped GEMV (8-row blocks, decoded once per block).
-TC_ROWS_PER_EXPERT = 12
+TC_ROWS_PER_EXPERT = 10
 _workspace: dict[int, torch.Tensor] = {}
 
 
